@@ -1,0 +1,74 @@
+"""ctypes binding of libptv3_b200.so (the C ABI declared in include/ptv3_b200.h).
+
+There is no fallback: if the shared library is missing or a call fails, an
+exception is raised."""
+import ctypes
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "csrc", "libptv3_b200.so")
+
+c_i64 = ctypes.c_int64
+c_int = ctypes.c_int
+c_f32 = ctypes.c_float
+c_sz = ctypes.c_size_t
+c_ptr = ctypes.c_void_p
+
+# name -> (restype, argtypes); must list every symbol of include/ptv3_b200.h
+SIGNATURES = {
+    "ptv3_last_error": (ctypes.c_char_p, []),
+    "ptv3_version": (c_int, []),
+    "ptv3_encode": (c_int, [c_ptr, c_ptr, c_i64, c_int, ctypes.POINTER(c_int), c_int, c_ptr, c_ptr]),
+    "ptv3_argsort_workspace_bytes": (c_sz, [c_int, c_i64, c_int]),
+    "ptv3_argsort_inverse": (c_int, [c_ptr, c_int, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+}
+
+_lib = None
+
+
+class Ptv3Error(RuntimeError):
+    pass
+
+
+def load():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise Ptv3Error(
+                "CUDA library %s is not built; run `python -m pointtransformerv3_b200.build` "
+                "(there is no CPU fallback)" % LIB_PATH)
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = lib
+    return _lib
+
+
+def check(rc, what):
+    if rc != 0:
+        raise Ptv3Error("%s failed (%d): %s" % (what, rc, load().ptv3_last_error().decode()))
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    if t is None:
+        return None
+    return t.data_ptr()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def require_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise Ptv3Error("tensor on %s: this library has CUDA kernels only, no CPU path" % t.device)
+
+
+def workspace(nbytes, device):
+    return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)

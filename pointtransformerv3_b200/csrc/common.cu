@@ -1,0 +1,30 @@
+#include "common.cuh"
+#include <stdarg.h>
+#include "../../include/ptv3_b200.h"
+
+namespace ptv3 {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int check_launch(const char* what)
+{
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        set_error("%s: %s", what, cudaGetErrorString(e));
+        return PTV3_ERR_CUDA;
+    }
+    return PTV3_OK;
+}
+
+}  // namespace ptv3
+
+extern "C" const char* ptv3_last_error(void) { return ptv3::g_err; }
+extern "C" int ptv3_version(void) { return 1; }

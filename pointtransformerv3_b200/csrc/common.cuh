@@ -1,0 +1,54 @@
+// Shared helpers of the sm_100a kernel library: status codes, the thread-local
+// error string behind ptv3_last_error(), launch checking and small device
+// utilities.  The library never allocates device memory (one documented entry
+// point uses a static device array instead); callers pass outputs and
+// workspaces.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define PTV3_OK 0
+#define PTV3_ERR_INVALID_ARGUMENT (-1)
+#define PTV3_ERR_UNSUPPORTED (-2)
+#define PTV3_ERR_WORKSPACE (-3)
+#define PTV3_ERR_CUDA (-4)
+#define PTV3_ERR_DEVICE_STATUS (-5)
+
+// bits of the device status word (written by kernels, never trapped on)
+#define PTV3_STATUS_BAD_INDEX 1u
+#define PTV3_STATUS_PROBE_LIMIT 2u
+#define PTV3_STATUS_WAIT_LIMIT 4u
+
+namespace ptv3 {
+
+void set_error(const char* fmt, ...);
+int check_launch(const char* what);
+
+#define PTV3_REQUIRE(cond, code, ...)            \
+    do {                                         \
+        if (!(cond)) {                           \
+            ::ptv3::set_error(__VA_ARGS__);      \
+            return (code);                       \
+        }                                        \
+    } while (0)
+
+static inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Carves a caller-provided workspace into 256-byte aligned pieces.
+struct Carver {
+    char* base;
+    size_t off;
+    explicit Carver(void* p) : base(static_cast<char*>(p)), off(0) {}
+    template <typename T>
+    T* take(size_t count) {
+        T* p = reinterpret_cast<T*>(base + off);
+        off += align_up(count * sizeof(T), 256);
+        return p;
+    }
+};
+
+static inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace ptv3

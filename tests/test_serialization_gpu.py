@@ -1,0 +1,81 @@
+"""Bit-exact parity of the CUDA serialization stage (codes, stable sort order,
+inverse) with the CPU oracle, through the C ABI."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cenc
+from pointtransformerv3_b200 import ops, synthetic
+
+pytestmark = pytest.mark.gpu
+ORDERS = ["z", "z-trans", "hilbert", "hilbert-trans"]
+
+
+def _check_sorted(codes, order, inverse):
+    k, n = codes.shape
+    ar = torch.arange(n, device=codes.device)
+    for r in range(k):
+        sc = codes[r][order[r]]
+        assert bool((sc[1:] >= sc[:-1]).all())
+        tie = sc[1:] == sc[:-1]
+        assert bool((order[r][1:][tie] > order[r][:-1][tie]).all()), "ties must keep index order"
+        assert bool((inverse[r][order[r]] == ar).all())
+
+
+@pytest.mark.parametrize("depth", [1, 2, 5, 8, 9, 11, 16])
+def test_encode_matches_oracle(depth):
+    rng = np.random.default_rng(depth)
+    g = rng.integers(-3, (1 << depth) + 3, size=(5000, 3)).astype(np.int32)
+    b = rng.integers(0, 5, size=5000).astype(np.int64)
+    got = ops.encode(torch.from_numpy(g).cuda(), torch.from_numpy(b).cuda(), depth, ORDERS).cpu().numpy()
+    for r, o in enumerate(ORDERS):
+        assert (got[r] == cenc.encode(g, b, depth, o)).all(), o
+
+
+def test_encode_edge_sizes():
+    for n in (0, 1, 2, 31, 257):
+        g = torch.randint(0, 1 << 16, (n, 3), dtype=torch.int32)
+        got = ops.encode(g.cuda(), None, 16, ORDERS).cpu().numpy()
+        assert got.shape == (4, n)
+        for r, o in enumerate(ORDERS):
+            assert (got[r] == cenc.encode(g.numpy(), None, 16, o)).all()
+
+
+def test_config1_bit_exact():
+    """100 000 uniform points, depth 16, four orders: codes, order, inverse."""
+    _, gc = synthetic.uniform_cloud(100_000, seed=0)
+    batch = torch.zeros(gc.shape[0], dtype=torch.int64)
+    codes = ops.encode(gc.cuda(), batch.cuda(), 16, ORDERS)
+    order, inverse = ops.argsort_inverse(codes, 48 + 1)
+    c = codes.cpu().numpy()
+    for r, o in enumerate(ORDERS):
+        ref = cenc.encode(gc.numpy(), batch.numpy(), 16, o)
+        assert (c[r] == ref).all()
+        ro = cenc.argsort_stable(ref)
+        assert (order[r].cpu().numpy() == ro).all()
+        assert (inverse[r].cpu().numpy() == cenc.inverse(ro)).all()
+
+
+@pytest.mark.parametrize("n,bits", [(1, 8), (2, 3), (33, 1), (2048, 16), (2049, 17), (70_001, 30),
+                                    (300_000, 38), (1_000_000, 63)])
+def test_argsort_sizes_and_ties(n, bits):
+    g = torch.Generator().manual_seed(n)
+    hi = (1 << bits) - 1
+    codes = torch.randint(0, min(hi, 1 << 62) + 1, (3, n), generator=g, dtype=torch.int64)
+    codes[1] = codes[1] % 7          # heavy ties
+    codes[2] = torch.sort(codes[2], descending=True).values
+    order, inverse = ops.argsort_inverse(codes.cuda(), bits)
+    _check_sorted(codes.cuda(), order, inverse)
+    for r in range(3):
+        assert (order[r].cpu().numpy() == np.argsort(codes[r].numpy(), kind="stable")).all()
+
+
+def test_large_sort_properties():
+    """4 M points x 4 orders: sortedness, stability and inverse, checked on device."""
+    n = 4_000_000
+    g = torch.Generator(device="cuda").manual_seed(0)
+    gc = torch.randint(0, 2048, (n, 3), generator=g, device="cuda", dtype=torch.int32)
+    batch = torch.randint(0, 16, (n,), generator=g, device="cuda").sort().values
+    codes = ops.encode(gc, batch, 11, ORDERS)
+    order, inverse = ops.argsort_inverse(codes, 33 + 4)
+    _check_sorted(codes, order, inverse)
