@@ -38,6 +38,19 @@ extern "C" {
 #define PTV3_DTYPE_F32 0
 #define PTV3_DTYPE_BF16 1
 
+/* status codes */
+#define PTV3_OK 0
+#define PTV3_ERR_INVALID_ARGUMENT (-1)
+#define PTV3_ERR_UNSUPPORTED (-2)
+#define PTV3_ERR_WORKSPACE (-3)
+#define PTV3_ERR_CUDA (-4)
+#define PTV3_ERR_DEVICE_STATUS (-5)
+
+/* bits kernels OR into a caller-provided device status word instead of trapping */
+#define PTV3_STATUS_BAD_INDEX 1u
+#define PTV3_STATUS_PROBE_LIMIT 2u
+#define PTV3_STATUS_WAIT_LIMIT 4u
+
 const char* ptv3_last_error(void);
 int ptv3_version(void);
 
@@ -65,6 +78,112 @@ int ptv3_encode(const int32_t* grid_coord, const int64_t* batch, int64_t n, int 
 size_t ptv3_argsort_workspace_bytes(int k, int64_t n, int sig_bits);
 int ptv3_argsort_inverse(const int64_t* codes, int k, int64_t n, int sig_bits, int64_t* order,
                          int64_t* inverse, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Patch padding plan of serialized attention.
+ * Replaces model.py:382-438 (SerializedAttention.get_padding_and_inverse).
+ * A scene with c > patch points is padded to a multiple of `patch`; the tail of
+ * its last patch re-uses the ranks one patch earlier.
+ *   offset      n_scenes int64, cumulative point counts
+ *   n, n_pad, n_seq   totals the caller derived from the same offsets (checked
+ *               on the device; a mismatch sets PTV3_STATUS_BAD_INDEX in *status
+ *               and leaves the outputs unwritten)
+ *   pad         n_pad int64: serialized rank feeding padded row p
+ *   unpad       n int64: padded row owned by serialized rank j
+ *   cu_seqlens  n_seq + 1 int32: first padded row of every patch, then n_pad
+ *   status      one uint32, OR-ed with PTV3_STATUS_* bits (never cleared here)
+ */
+int ptv3_pad_plan(const int64_t* offset, int n_scenes, int patch, int64_t n, int64_t n_pad,
+                  int n_seq, int64_t* pad, int64_t* unpad, int32_t* cu_seqlens, uint32_t* status,
+                  void* stream);
+
+/*
+ * Patch attention core: out[p] = softmax(q k^T * scale) v within each patch.
+ * Replaces model.py:452-484 (row gather qkv[order[pad]], non-flash attention
+ * :458-474, gather feat[unpad[inverse]]); the two Linear layers stay outside.
+ *   qkv         n x 3*channels, channel split (3, heads, head_dim) (model.py:461)
+ *   order       n int64, ONE row of serialized_order
+ *   pad, unpad, cu_seqlens   as written by ptv3_pad_plan
+ *   out         n x channels, every row written exactly once
+ *   max_seqlen  longest patch (rows); head_dim = channels / heads in {8,16,32,64}
+ *   dtype       PTV3_DTYPE_*; algo 0 = automatic, 1 = CUDA-core path,
+ *               2 = tensor-core path (bf16 only)
+ */
+int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
+                       const int64_t* unpad, const int32_t* cu_seqlens, void* out, int64_t n,
+                       int n_seq, int max_seqlen, int channels, int heads, float scale, int dtype,
+                       int algo, void* stream);
+
+/*
+ * Kernel map of a submanifold convolution.
+ * Replaces spconv's indice-pair build behind model.py:546-552 and :767-774.
+ *   indices     n x 4 int32 rows (batch, x, y, z), 16-byte aligned, each field
+ *               in [0, 65535]
+ *   nbr         ksize^3 x n int32, OFFSET-major: nbr[o][i] = row of the voxel at
+ *               coordinate(i) + offset o, or -1; o = ((dx+r)*k + (dy+r))*k + (dz+r)
+ *               with r = ksize/2.  Duplicate rows resolve to the lowest row.
+ */
+size_t ptv3_kmap_workspace_bytes(int64_t n);
+int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int32_t* nbr, uint32_t* status,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Submanifold convolution over a kernel map:
+ *   out[i] = bias + sum_o weight[:, o, :] . feat[nbr[o][i]]
+ * Replaces spconv.SubMConv3d.forward at model.py:546-552 and :767-774.
+ *   weight      c_out x kernel_volume x c_in (the [C_out, k, k, k, C_in] layout)
+ *   bias        c_out or NULL
+ *   algo        0 = automatic, 1 = CUDA-core path, 2 = tensor-core path
+ */
+int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight, const void* bias,
+                       void* out, int64_t n, int c_in, int c_out, int kernel_volume, int dtype,
+                       int algo, void* stream);
+
+/*
+ * Cluster and order bookkeeping of serialized pooling.
+ * Replaces the index part of model.py:639-695 (unique, sort, cumsum, head
+ * gather, argsort + scatter_ of the pooled codes, row shuffle).
+ *   code, order k x n int64 rows of the fine level, in its current row order
+ *   row_perm    HOST array of k ints or NULL: pooled row r is built from fine
+ *               row row_perm[r] (the reference's code[perm], model.py:676-680)
+ *   cluster     n int64: rank of (code[0] >> 3*pooling_depth) among its unique
+ *               values (= pooling_inverse)
+ *   idx_ptr     n + 1 int64 (m + 1 used): run starts of the clusters in order[0]
+ *   head        n int64 (m used): one member point of every cluster
+ *   pooled_*    outputs sized for m = n, row stride n for the k-row tensors
+ *   meta        1 + n_scenes int64: m, then the number of clusters per scene
+ */
+size_t ptv3_pool_plan_workspace_bytes(int k, int64_t n, int n_scenes);
+int ptv3_pool_plan(const int64_t* code, const int64_t* order, const int32_t* grid_coord,
+                   const int64_t* batch, int k, int64_t n, int n_scenes, int pooling_depth,
+                   const int* row_perm, int64_t* cluster, int64_t* idx_ptr, int64_t* head,
+                   int64_t* pooled_code, int64_t* pooled_order, int64_t* pooled_inverse,
+                   int32_t* pooled_grid_coord, int64_t* pooled_batch, int64_t* meta,
+                   uint32_t* status, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Segment max over clusters fused with BatchNorm(eval) + GELU, and the mean
+ * coordinate.  Replaces torch_scatter.segment_csr at model.py:684-689 and the
+ * norm/act at model.py:707-710.
+ *   x           (points) x channels, already projected (model.py:685)
+ *   indices     points sorted by cluster (order[0] of the fine level)
+ *   bn_scale/shift   per-channel fp32 (weight/sqrt(var+eps), bias-mean*scale),
+ *               or both NULL for a plain max
+ *   coord/coord_out  fp32 x 3, or NULL to skip the mean
+ */
+int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* indices, const int64_t* idx_ptr,
+                  int64_t m, int channels, const float* bn_scale, const float* bn_shift, void* out,
+                  float* coord_out, int dtype, void* stream);
+
+/*
+ * out[i] = GELU(BN(skip[i])) + GELU(BN(child[cluster[i]])); skip_act (optional)
+ * receives the first term alone.  Replaces model.py:726-735,744-746 after the
+ * two Linear layers.
+ */
+int ptv3_unpool_fwd(const void* skip, const void* child, const int64_t* cluster, int64_t n,
+                    int channels, const float* skip_scale, const float* skip_shift,
+                    const float* child_scale, const float* child_shift, void* out, void* skip_act,
+                    int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -23,6 +23,21 @@ SIGNATURES = {
     "ptv3_encode": (c_int, [c_ptr, c_ptr, c_i64, c_int, ctypes.POINTER(c_int), c_int, c_ptr, c_ptr]),
     "ptv3_argsort_workspace_bytes": (c_sz, [c_int, c_i64, c_int]),
     "ptv3_argsort_inverse": (c_int, [c_ptr, c_int, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+    "ptv3_pad_plan": (c_int, [c_ptr, c_int, c_int, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr]),
+    "ptv3_attention_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int,
+                                   c_int, c_f32, c_int, c_int, c_ptr]),
+    "ptv3_kmap_workspace_bytes": (c_sz, [c_i64]),
+    "ptv3_kmap_build": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+    "ptv3_subm_conv_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int, c_int,
+                                   c_int, c_ptr]),
+    "ptv3_pool_plan_workspace_bytes": (c_sz, [c_int, c_i64, c_int]),
+    "ptv3_pool_plan": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_i64, c_int, c_int,
+                               ctypes.POINTER(c_int), c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+                               c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+    "ptv3_pool_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_int,
+                              c_ptr]),
+    "ptv3_unpool_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
+                                c_ptr, c_int, c_ptr]),
 }
 
 _lib = None
@@ -72,3 +87,24 @@ def require_cuda(*tensors):
 
 def workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 1), dtype=torch.uint8, device=device)
+
+
+DTYPE_IDS = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def dtype_id(t):
+    try:
+        return DTYPE_IDS[t.dtype]
+    except KeyError:
+        raise Ptv3Error("feature dtype %s is not supported (float32 or bfloat16)" % t.dtype)
+
+
+STATUS_BITS = {1: "index or size out of range", 2: "hash probe limit reached", 4: "device wait limit reached"}
+
+
+def raise_on_status(status, what):
+    """Reads the device status word (one host sync) and raises if a bit is set."""
+    v = int(status.item())
+    if v:
+        msg = ", ".join(m for b, m in STATUS_BITS.items() if v & b)
+        raise Ptv3Error("%s: device status 0x%x (%s)" % (what, v, msg))

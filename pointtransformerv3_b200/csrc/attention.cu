@@ -1,0 +1,149 @@
+// Patch attention over a serialized order: for every sequence (patch) of the
+// padded serialized layout and every head, softmax(q k^T * scale) v, with rows
+// gathered straight from the point-major qkv tensor and results scattered
+// straight back to point-major rows.
+//
+// Replaces model.py:452-484 of SerializedAttention.forward (the row gather
+// qkv[order[pad]], the per-patch attention, and the un-pad/un-serialize gather
+// feat[unpad[inverse]]).  Row P of the padded layout reads point
+// order[pad[P]]; it owns that point's output iff unpad[pad[P]] == P (borrowed
+// rows of a last patch take part as keys and queries but write nothing).
+//
+// This file holds the CUDA-core path (fp32 arithmetic for either element type):
+// one thread per query row, keys/values staged through shared memory in chunks
+// with a per-chunk running-max rescale, so any sequence length works.
+#include "common.cuh"
+#include "convert.cuh"
+#include "../../include/ptv3_b200.h"
+
+namespace ptv3 {
+
+constexpr int AF_QT = 128;   // queries (threads) per CTA
+
+template <typename T, int D>
+__global__ void __launch_bounds__(AF_QT) attn_fma_kernel(
+    const T* __restrict__ qkv, const int64_t* __restrict__ order, const int64_t* __restrict__ pad,
+    const int64_t* __restrict__ unpad, const int32_t* __restrict__ cu_seqlens, T* __restrict__ out,
+    int C, float scale)
+{
+    constexpr int AF_KC = D <= 32 ? 128 : 64;   // keys per staged chunk
+    __shared__ float Ks[AF_KC][D];
+    __shared__ float Vs[AF_KC][D];
+    __shared__ int64_t ksrc[AF_KC];
+    const int seq = blockIdx.y, h = blockIdx.z, tid = threadIdx.x;
+    const int64_t start = cu_seqlens[seq];
+    const int L = (int)(cu_seqlens[seq + 1] - start);
+    const int q0 = blockIdx.x * AF_QT;
+    if (q0 >= L) return;
+    const int qi = q0 + tid;
+    const bool valid = qi < L;
+    int64_t src = 0;
+    bool primary = false;
+    float q[D], acc[D];
+    if (valid) {
+        const int64_t P = start + qi;
+        const int64_t pd = pad[P];
+        src = order[pd];
+        primary = unpad[pd] == P;
+        const T* qp = qkv + src * (3 * (int64_t)C) + h * D;
+#pragma unroll
+        for (int d = 0; d < D; ++d) q[d] = to_f<T>(qp[d]) * scale;
+    } else {
+#pragma unroll
+        for (int d = 0; d < D; ++d) q[d] = 0.f;
+    }
+#pragma unroll
+    for (int d = 0; d < D; ++d) acc[d] = 0.f;
+    float m = -INFINITY, l = 0.f;
+
+    for (int c0 = 0; c0 < L; c0 += AF_KC) {
+        const int nk = min(AF_KC, L - c0);
+        __syncthreads();
+        if (tid < nk) ksrc[tid] = order[pad[start + c0 + tid]];
+        __syncthreads();
+        for (int idx = tid; idx < nk * D; idx += AF_QT) {
+            const int j = idx / D, d = idx % D;
+            const T* base = qkv + ksrc[j] * (3 * (int64_t)C) + h * D + d;
+            Ks[j][d] = to_f<T>(base[C]);
+            Vs[j][d] = to_f<T>(base[2 * C]);
+        }
+        __syncthreads();
+        float cm = -INFINITY;
+        for (int j = 0; j < nk; ++j) {
+            float s = 0.f;
+#pragma unroll
+            for (int d = 0; d < D; ++d) s = fmaf(q[d], Ks[j][d], s);
+            cm = fmaxf(cm, s);
+        }
+        const float mn = fmaxf(m, cm);
+        const float corr = __expf(m - mn);   // m = -inf on the first chunk -> 0
+        l *= corr;
+#pragma unroll
+        for (int d = 0; d < D; ++d) acc[d] *= corr;
+        for (int j = 0; j < nk; ++j) {
+            float s = 0.f;
+#pragma unroll
+            for (int d = 0; d < D; ++d) s = fmaf(q[d], Ks[j][d], s);
+            const float p = __expf(s - mn);
+            l += p;
+#pragma unroll
+            for (int d = 0; d < D; ++d) acc[d] = fmaf(p, Vs[j][d], acc[d]);
+        }
+        m = mn;
+    }
+    if (valid && primary) {
+        const float inv = 1.f / l;
+        T* op = out + src * (int64_t)C + h * D;
+#pragma unroll
+        for (int d = 0; d < D; ++d) op[d] = from_f<T>(acc[d] * inv);
+    }
+}
+
+template <typename T>
+static int launch_attn_fma(const void* qkv, const int64_t* order, const int64_t* pad,
+                           const int64_t* unpad, const int32_t* cu, void* out, int n_seq,
+                           int max_seqlen, int C, int H, float scale, cudaStream_t stream)
+{
+    const int D = C / H;
+    const dim3 grid((max_seqlen + AF_QT - 1) / AF_QT, n_seq, H);
+#define AF_LAUNCH(DD)                                                                         \
+    attn_fma_kernel<T, DD><<<grid, AF_QT, 0, stream>>>((const T*)qkv, order, pad, unpad, cu, \
+                                                       (T*)out, C, scale)
+    switch (D) {
+        case 8: AF_LAUNCH(8); break;
+        case 16: AF_LAUNCH(16); break;
+        case 32: AF_LAUNCH(32); break;
+        case 64: AF_LAUNCH(64); break;
+        default:
+            set_error("ptv3_attention_fwd: head dim %d (supported: 8, 16, 32, 64)", D);
+            return PTV3_ERR_UNSUPPORTED;
+    }
+#undef AF_LAUNCH
+    return check_launch("ptv3_attention_fwd");
+}
+
+}  // namespace ptv3
+
+extern "C" int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
+                                  const int64_t* unpad, const int32_t* cu_seqlens, void* out,
+                                  int64_t n, int n_seq, int max_seqlen, int channels, int heads,
+                                  float scale, int dtype, int algo, void* stream)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0 && n_seq >= 0 && max_seqlen >= 1 && channels >= 1 && heads >= 1 &&
+                     channels % heads == 0,
+                 PTV3_ERR_INVALID_ARGUMENT, "ptv3_attention_fwd: bad sizes");
+    PTV3_REQUIRE(dtype == PTV3_DTYPE_F32 || dtype == PTV3_DTYPE_BF16, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_attention_fwd: dtype %d", dtype);
+    PTV3_REQUIRE(heads <= 65535 && n_seq <= 65535, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_attention_fwd: more than 65535 sequences or heads");
+    if (n == 0 || n_seq == 0) return PTV3_OK;
+    PTV3_REQUIRE(qkv && order && pad && unpad && cu_seqlens && out, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_attention_fwd: null pointer");
+    (void)algo;
+    if (dtype == PTV3_DTYPE_F32)
+        return launch_attn_fma<float>(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen,
+                                      channels, heads, scale, (cudaStream_t)stream);
+    return launch_attn_fma<__nv_bfloat16>(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen,
+                                          channels, heads, scale, (cudaStream_t)stream);
+}

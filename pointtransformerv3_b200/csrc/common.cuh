@@ -9,17 +9,7 @@
 #include <stdint.h>
 #include <stdio.h>
 
-#define PTV3_OK 0
-#define PTV3_ERR_INVALID_ARGUMENT (-1)
-#define PTV3_ERR_UNSUPPORTED (-2)
-#define PTV3_ERR_WORKSPACE (-3)
-#define PTV3_ERR_CUDA (-4)
-#define PTV3_ERR_DEVICE_STATUS (-5)
-
-// bits of the device status word (written by kernels, never trapped on)
-#define PTV3_STATUS_BAD_INDEX 1u
-#define PTV3_STATUS_PROBE_LIMIT 2u
-#define PTV3_STATUS_WAIT_LIMIT 4u
+#include "../../include/ptv3_b200.h"
 
 namespace ptv3 {
 

@@ -1,0 +1,136 @@
+// Kernel map of a submanifold convolution: for every active voxel and every
+// kernel offset, the row of the active voxel at (coordinate + offset), or -1.
+// Built with an open-addressing hash table in a caller-provided workspace.
+//
+// Replaces the indice-pair construction spconv.SubMConv3d performs for the call
+// sites model.py:546-552 (3x3x3, cached per indice_key) and model.py:767-774
+// (5x5x5 stem).  The table is offset-major, nbr[o][i], so that a tile of
+// consecutive voxels reads each offset's neighbour rows coalesced.
+// Offset index o = ((dx+r)*k + (dy+r))*k + (dz+r), r = k/2.
+#include "common.cuh"
+#include "../../include/ptv3_b200.h"
+
+namespace ptv3 {
+
+constexpr uint64_t KM_EMPTY = ~0ull;
+
+__device__ __forceinline__ uint64_t km_mix(uint64_t h)
+{
+    h ^= h >> 33;
+    h *= 0xff51afd7ed558ccdull;
+    h ^= h >> 33;
+    h *= 0xc4ceb9fe1a85ec53ull;
+    h ^= h >> 33;
+    return h;
+}
+
+__device__ __forceinline__ bool km_key(int b, int x, int y, int z, uint64_t& key)
+{
+    if ((unsigned)b > 0xfffeu || (unsigned)x > 0xffffu || (unsigned)y > 0xffffu || (unsigned)z > 0xffffu)
+        return false;
+    key = ((uint64_t)b << 48) | ((uint64_t)x << 32) | ((uint64_t)y << 16) | (uint64_t)z;
+    return true;
+}
+
+__global__ void __launch_bounds__(256) km_insert_kernel(const int32_t* __restrict__ indices, int64_t n,
+                                                        unsigned long long* __restrict__ keys,
+                                                        uint32_t* __restrict__ vals, uint64_t cap_mask,
+                                                        uint32_t* __restrict__ status)
+{
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int4 v = reinterpret_cast<const int4*>(indices)[i];
+    uint64_t key;
+    if (!km_key(v.x, v.y, v.z, v.w, key)) {
+        atomicOr(status, PTV3_STATUS_BAD_INDEX);
+        return;
+    }
+    uint64_t slot = km_mix(key) & cap_mask;
+    for (uint64_t probe = 0; probe <= cap_mask; ++probe) {
+        const unsigned long long prev = atomicCAS(&keys[slot], KM_EMPTY, key);
+        if (prev == KM_EMPTY || prev == key) {
+            atomicMin(&vals[slot], (uint32_t)i);   // duplicates: lowest row wins
+            return;
+        }
+        slot = (slot + 1) & cap_mask;
+    }
+    atomicOr(status, PTV3_STATUS_PROBE_LIMIT);
+}
+
+__global__ void __launch_bounds__(256) km_probe_kernel(const int32_t* __restrict__ indices, int64_t n,
+                                                       int ksize,
+                                                       const unsigned long long* __restrict__ keys,
+                                                       const uint32_t* __restrict__ vals,
+                                                       uint64_t cap_mask, int32_t* __restrict__ nbr,
+                                                       uint32_t* __restrict__ status)
+{
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int o = blockIdx.y;
+    const int r = ksize / 2;
+    const int dz = o % ksize - r, dy = (o / ksize) % ksize - r, dx = o / (ksize * ksize) - r;
+    const int4 v = reinterpret_cast<const int4*>(indices)[i];
+    int32_t found = -1;
+    uint64_t key;
+    if (km_key(v.x, v.y + dx, v.z + dy, v.w + dz, key)) {
+        uint64_t slot = km_mix(key) & cap_mask;
+        uint64_t probe = 0;
+        for (; probe <= cap_mask; ++probe) {
+            const unsigned long long kk = keys[slot];
+            if (kk == key) {
+                found = (int32_t)vals[slot];
+                break;
+            }
+            if (kk == KM_EMPTY) break;
+            slot = (slot + 1) & cap_mask;
+        }
+        if (probe > cap_mask) atomicOr(status, PTV3_STATUS_PROBE_LIMIT);
+    }
+    nbr[(int64_t)o * n + i] = found;
+}
+
+static uint64_t km_capacity(int64_t n)
+{
+    uint64_t c = 1024;
+    while (c < (uint64_t)n * 2) c <<= 1;
+    return c;
+}
+
+}  // namespace ptv3
+
+extern "C" size_t ptv3_kmap_workspace_bytes(int64_t n)
+{
+    if (n <= 0) return 0;
+    const uint64_t cap = ptv3::km_capacity(n);
+    return ptv3::align_up(cap * sizeof(uint64_t), 256) + ptv3::align_up(cap * sizeof(uint32_t), 256);
+}
+
+extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int32_t* nbr,
+                               uint32_t* status, void* workspace, size_t workspace_bytes,
+                               void* stream_)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0 && n < (1ll << 31), PTV3_ERR_INVALID_ARGUMENT, "ptv3_kmap_build: bad n");
+    PTV3_REQUIRE(ksize == 1 || ksize == 3 || ksize == 5 || ksize == 7, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_kmap_build: kernel size %d (supported: 1, 3, 5, 7)", ksize);
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(indices && nbr && status && workspace, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_kmap_build: null pointer");
+    PTV3_REQUIRE(((uintptr_t)indices & 15) == 0, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_kmap_build: indices must be 16-byte aligned");
+    const size_t need = ptv3_kmap_workspace_bytes(n);
+    PTV3_REQUIRE(workspace_bytes >= need, PTV3_ERR_WORKSPACE,
+                 "ptv3_kmap_build: workspace %zu < %zu bytes", workspace_bytes, need);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const uint64_t cap = km_capacity(n);
+    Carver cv(workspace);
+    unsigned long long* keys = cv.take<unsigned long long>(cap);
+    uint32_t* vals = cv.take<uint32_t>(cap);
+    cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
+    cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream);
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
+    km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(
+        indices, n, ksize, keys, vals, cap - 1, nbr, status);
+    return check_launch("ptv3_kmap_build");
+}

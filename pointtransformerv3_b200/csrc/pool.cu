@@ -1,0 +1,206 @@
+// Feature side of serialized pooling / unpooling.
+//
+// pool:   out[c] = GELU(BN(max over the points of cluster c of x))   and the
+//         mean coordinate of the cluster.  Replaces torch_scatter.segment_csr at
+//         model.py:684-689 together with the BatchNorm1d(eval) + GELU that follow
+//         (model.py:707-710).  The points of a cluster are contiguous in the
+//         sorted order the plan was built from, so a segment is a run of that
+//         order; one warp owns a cluster and reads whole rows with 16-byte loads.
+// unpool: out[i] = GELU(BN_s(skip[i])) + GELU(BN_c(child[cluster[i]])), and the
+//         first term alone as a second output.  Replaces model.py:726-735,
+//         :744-746 after the two Linear layers.
+// BatchNorm in eval mode is passed as per-channel scale/shift (fp32).
+#include "common.cuh"
+#include "convert.cuh"
+#include "../../include/ptv3_b200.h"
+
+namespace ptv3 {
+
+__device__ __forceinline__ float gelu_exact(float x)
+{
+    return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
+}
+
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    using Raw = float4;
+    __device__ static void unpack(const Raw& r, float* f) { f[0] = r.x; f[1] = r.y; f[2] = r.z; f[3] = r.w; }
+    __device__ static Raw pack(const float* f) { return make_float4(f[0], f[1], f[2], f[3]); }
+};
+template <> struct Vec<__nv_bfloat16> {
+    static constexpr int N = 8;
+    using Raw = uint4;
+    __device__ static void unpack(const Raw& r, float* f)
+    {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float2 v = __bfloat1622float2(h[i]);
+            f[2 * i] = v.x;
+            f[2 * i + 1] = v.y;
+        }
+    }
+    __device__ static Raw pack(const float* f)
+    {
+        Raw r;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+        return r;
+    }
+};
+
+// C must be a multiple of Vec<T>::N.
+template <typename T>
+__global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x,
+                                                       const int64_t* __restrict__ indices,
+                                                       const int64_t* __restrict__ idx_ptr, int64_t m,
+                                                       int C, const float* __restrict__ scale,
+                                                       const float* __restrict__ shift,
+                                                       T* __restrict__ out)
+{
+    using V = Vec<T>;
+    const int lane = threadIdx.x & 31;
+    const int64_t c = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    if (c >= m) return;
+    const int64_t lo = idx_ptr[c], hi = idx_ptr[c + 1];
+    for (int ch = lane * V::N; ch < C; ch += 32 * V::N) {
+        float best[V::N];
+#pragma unroll
+        for (int i = 0; i < V::N; ++i) best[i] = -INFINITY;
+        for (int64_t j = lo; j < hi; ++j) {
+            const int64_t p = indices[j];
+            const typename V::Raw raw = *reinterpret_cast<const typename V::Raw*>(x + p * C + ch);
+            float f[V::N];
+            V::unpack(raw, f);
+#pragma unroll
+            for (int i = 0; i < V::N; ++i) best[i] = fmaxf(best[i], f[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < V::N; ++i) {
+            float v = best[i];
+            if (scale) v = gelu_exact(fmaf(v, scale[ch + i], shift[ch + i]));
+            best[i] = v;
+        }
+        *reinterpret_cast<typename V::Raw*>(out + c * C + ch) = V::pack(best);
+    }
+}
+
+__global__ void __launch_bounds__(256) pool_coord_mean_kernel(const float* __restrict__ coord,
+                                                              const int64_t* __restrict__ indices,
+                                                              const int64_t* __restrict__ idx_ptr,
+                                                              int64_t m, float* __restrict__ out)
+{
+    const int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (c >= m) return;
+    const int64_t lo = idx_ptr[c], hi = idx_ptr[c + 1];
+    float sx = 0.f, sy = 0.f, sz = 0.f;
+    for (int64_t j = lo; j < hi; ++j) {
+        const int64_t p = indices[j];
+        sx += coord[3 * p + 0];
+        sy += coord[3 * p + 1];
+        sz += coord[3 * p + 2];
+    }
+    const float inv = 1.f / (float)(hi - lo);
+    out[3 * c + 0] = sx * inv;
+    out[3 * c + 1] = sy * inv;
+    out[3 * c + 2] = sz * inv;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) unpool_kernel(const T* __restrict__ skip,
+                                                     const T* __restrict__ child,
+                                                     const int64_t* __restrict__ cluster, int64_t n,
+                                                     int C, const float* __restrict__ s_scale,
+                                                     const float* __restrict__ s_shift,
+                                                     const float* __restrict__ c_scale,
+                                                     const float* __restrict__ c_shift,
+                                                     T* __restrict__ out, T* __restrict__ skip_act)
+{
+    using V = Vec<T>;
+    const int vec_per_row = C / V::N;
+    const int64_t total = n * vec_per_row;
+    for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
+         t += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t i = t / vec_per_row;
+        const int ch = (int)(t % vec_per_row) * V::N;
+        const int64_t cl = cluster[i];
+        float a[V::N], b[V::N], o[V::N];
+        V::unpack(*reinterpret_cast<const typename V::Raw*>(skip + i * C + ch), a);
+        V::unpack(*reinterpret_cast<const typename V::Raw*>(child + cl * C + ch), b);
+#pragma unroll
+        for (int k = 0; k < V::N; ++k) {
+            a[k] = gelu_exact(fmaf(a[k], s_scale[ch + k], s_shift[ch + k]));
+            // both branches are rounded to the element type before the sum, as
+            // two separate modules would
+            a[k] = to_f<T>(from_f<T>(a[k]));
+            const float bb = to_f<T>(from_f<T>(gelu_exact(fmaf(b[k], c_scale[ch + k], c_shift[ch + k]))));
+            o[k] = a[k] + bb;
+        }
+        *reinterpret_cast<typename V::Raw*>(out + i * C + ch) = V::pack(o);
+        if (skip_act) *reinterpret_cast<typename V::Raw*>(skip_act + i * C + ch) = V::pack(a);
+    }
+}
+
+}  // namespace ptv3
+
+extern "C" int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* indices,
+                             const int64_t* idx_ptr, int64_t m, int channels, const float* bn_scale,
+                             const float* bn_shift, void* out, float* coord_out, int dtype,
+                             void* stream_)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(m >= 0 && channels >= 1, PTV3_ERR_INVALID_ARGUMENT, "ptv3_pool_fwd: bad sizes");
+    PTV3_REQUIRE(dtype == PTV3_DTYPE_F32 || dtype == PTV3_DTYPE_BF16, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_pool_fwd: dtype %d", dtype);
+    const int vn = dtype == PTV3_DTYPE_F32 ? 4 : 8;
+    PTV3_REQUIRE(channels % vn == 0, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_pool_fwd: channels %d not a multiple of %d", channels, vn);
+    PTV3_REQUIRE((bn_scale == nullptr) == (bn_shift == nullptr), PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_pool_fwd: bn_scale and bn_shift go together");
+    if (m == 0) return PTV3_OK;
+    PTV3_REQUIRE(x && indices && idx_ptr && out, PTV3_ERR_INVALID_ARGUMENT, "ptv3_pool_fwd: null pointer");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    const unsigned blocks = (unsigned)((m * 32 + 255) / 256);
+    if (dtype == PTV3_DTYPE_F32)
+        pool_max_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, indices, idx_ptr, m, channels,
+                                                           bn_scale, bn_shift, (float*)out);
+    else
+        pool_max_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)x, indices, idx_ptr, m, channels, bn_scale, bn_shift,
+            (__nv_bfloat16*)out);
+    if (coord && coord_out)
+        pool_coord_mean_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(coord, indices, idx_ptr,
+                                                                               m, coord_out);
+    return check_launch("ptv3_pool_fwd");
+}
+
+extern "C" int ptv3_unpool_fwd(const void* skip, const void* child, const int64_t* cluster, int64_t n,
+                               int channels, const float* skip_scale, const float* skip_shift,
+                               const float* child_scale, const float* child_shift, void* out,
+                               void* skip_act, int dtype, void* stream_)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0 && channels >= 1, PTV3_ERR_INVALID_ARGUMENT, "ptv3_unpool_fwd: bad sizes");
+    PTV3_REQUIRE(dtype == PTV3_DTYPE_F32 || dtype == PTV3_DTYPE_BF16, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_unpool_fwd: dtype %d", dtype);
+    const int vn = dtype == PTV3_DTYPE_F32 ? 4 : 8;
+    PTV3_REQUIRE(channels % vn == 0, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_unpool_fwd: channels %d not a multiple of %d", channels, vn);
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(skip && child && cluster && skip_scale && skip_shift && child_scale && child_shift && out,
+                 PTV3_ERR_INVALID_ARGUMENT, "ptv3_unpool_fwd: null pointer");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    int64_t blocks = (n * (channels / vn) + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == PTV3_DTYPE_F32)
+        unpool_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(
+            (const float*)skip, (const float*)child, cluster, n, channels, skip_scale, skip_shift,
+            child_scale, child_shift, (float*)out, (float*)skip_act);
+    else
+        unpool_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
+            (const __nv_bfloat16*)skip, (const __nv_bfloat16*)child, cluster, n, channels, skip_scale,
+            skip_shift, child_scale, child_shift, (__nv_bfloat16*)out, (__nv_bfloat16*)skip_act);
+    return check_launch("ptv3_unpool_fwd");
+}

@@ -46,3 +46,170 @@ def argsort_inverse(codes, sig_bits):
                                         _lib.ptr(inverse), _lib.ptr(ws), nbytes, _lib.stream()),
                "ptv3_argsort_inverse")
     return order, inverse
+
+
+def new_status(device):
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def pad_layout(counts, patch):
+    """Host arithmetic of model.py:392-404: (n_pad, n_seq) from per-scene counts."""
+    n_pad = n_seq = 0
+    for c in counts:
+        cp = (c + patch - 1) // patch * patch if c > patch else c
+        n_pad += cp
+        n_seq += (cp + patch - 1) // patch
+    return n_pad, n_seq
+
+
+def pad_plan(offset, counts, patch, status=None):
+    """offset (B,) int64 CUDA, counts: the same as host ints -> (pad, unpad, cu_seqlens)."""
+    _lib.require_cuda(offset)
+    lib = _lib.load()
+    offset = offset.to(torch.int64).contiguous()
+    n = int(sum(counts))
+    n_pad, n_seq = pad_layout(counts, patch)
+    dev = offset.device
+    pad = torch.empty(n_pad, dtype=torch.int64, device=dev)
+    unpad = torch.empty(n, dtype=torch.int64, device=dev)
+    cu = torch.empty(n_seq + 1, dtype=torch.int32, device=dev)
+    own = status is None
+    if own:
+        status = new_status(dev)
+    _lib.check(lib.ptv3_pad_plan(_lib.ptr(offset), len(counts), int(patch), n, n_pad, n_seq,
+                                 _lib.ptr(pad), _lib.ptr(unpad), _lib.ptr(cu), _lib.ptr(status),
+                                 _lib.stream()), "ptv3_pad_plan")
+    if own:
+        _lib.raise_on_status(status, "ptv3_pad_plan")
+    return pad, unpad, cu
+
+
+def attention(qkv, order_row, pad, unpad, cu_seqlens, heads, max_seqlen, scale, algo=0):
+    """qkv (N, 3C) -> (N, C): the attention core between the two Linear layers."""
+    _lib.require_cuda(qkv, order_row, pad, unpad, cu_seqlens)
+    lib = _lib.load()
+    qkv = qkv.contiguous()
+    n, c3 = qkv.shape
+    C = c3 // 3
+    out = torch.empty((n, C), dtype=qkv.dtype, device=qkv.device)
+    _lib.check(lib.ptv3_attention_fwd(_lib.ptr(qkv), _lib.ptr(order_row.contiguous()), _lib.ptr(pad),
+                                      _lib.ptr(unpad), _lib.ptr(cu_seqlens), _lib.ptr(out), n,
+                                      cu_seqlens.numel() - 1, int(max_seqlen), C, int(heads),
+                                      float(scale), _lib.dtype_id(qkv), int(algo), _lib.stream()),
+               "ptv3_attention_fwd")
+    return out
+
+
+def kmap_build(indices, ksize, status=None):
+    """indices (N,4) int32 (b,x,y,z) -> nbr (ksize^3, N) int32, offset-major."""
+    _lib.require_cuda(indices)
+    lib = _lib.load()
+    indices = indices.to(torch.int32).contiguous()
+    n = indices.shape[0]
+    nbr = torch.empty((ksize ** 3, n), dtype=torch.int32, device=indices.device)
+    nbytes = lib.ptv3_kmap_workspace_bytes(n)
+    ws = _lib.workspace(nbytes, indices.device)
+    own = status is None
+    if own:
+        status = new_status(indices.device)
+    _lib.check(lib.ptv3_kmap_build(_lib.ptr(indices), n, int(ksize), _lib.ptr(nbr), _lib.ptr(status),
+                                   _lib.ptr(ws), nbytes, _lib.stream()), "ptv3_kmap_build")
+    if own:
+        _lib.raise_on_status(status, "ptv3_kmap_build")
+    return nbr
+
+
+def subm_conv(feat, nbr, weight, bias=None, algo=0):
+    """feat (N,Cin), nbr (k^3,N) int32, weight (Cout,k,k,k,Cin) -> (N,Cout)."""
+    _lib.require_cuda(feat, nbr, weight, bias)
+    lib = _lib.load()
+    feat = feat.contiguous()
+    n, cin = feat.shape
+    cout = weight.shape[0]
+    kvol = nbr.shape[0]
+    if weight.numel() != cout * kvol * cin or weight.dtype != feat.dtype:
+        raise ValueError("weight %s/%s does not match feat %s/%s and %d offsets" % (
+            tuple(weight.shape), weight.dtype, tuple(feat.shape), feat.dtype, kvol))
+    if bias is not None and bias.dtype != feat.dtype:
+        raise ValueError("bias dtype %s != feature dtype %s" % (bias.dtype, feat.dtype))
+    out = torch.empty((n, cout), dtype=feat.dtype, device=feat.device)
+    _lib.check(lib.ptv3_subm_conv_fwd(_lib.ptr(feat), _lib.ptr(nbr), _lib.ptr(weight.contiguous()),
+                                      _lib.ptr(bias), _lib.ptr(out), n, cin, cout, kvol,
+                                      _lib.dtype_id(feat), int(algo), _lib.stream()),
+               "ptv3_subm_conv_fwd")
+    return out
+
+
+def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=None):
+    """Builds the pooled level's index tensors; one host sync to learn its size.
+
+    Returns dict(cluster, idx_ptr, head, code, order, inverse, grid_coord, batch, counts)."""
+    _lib.require_cuda(code, order, grid_coord, batch)
+    lib = _lib.load()
+    code, order = code.contiguous(), order.contiguous()
+    grid_coord = grid_coord.to(torch.int32).contiguous()
+    batch = batch.to(torch.int64).contiguous()
+    k, n = code.shape
+    dev = code.device
+    i64 = dict(dtype=torch.int64, device=dev)
+    cluster = torch.empty(n, **i64)
+    idx_ptr = torch.empty(n + 1, **i64)
+    head = torch.empty(n, **i64)
+    pcode = torch.empty((k, n), **i64)
+    porder = torch.empty((k, n), **i64)
+    pinv = torch.empty((k, n), **i64)
+    pgrid = torch.empty((n, 3), dtype=torch.int32, device=dev)
+    pbatch = torch.empty(n, **i64)
+    meta = torch.empty(1 + n_scenes, **i64)
+    status = new_status(dev)
+    nbytes = lib.ptv3_pool_plan_workspace_bytes(k, n, n_scenes)
+    ws = _lib.workspace(nbytes, dev)
+    perm = None
+    if row_perm is not None:
+        perm = (ctypes.c_int * k)(*[int(v) for v in row_perm])
+    _lib.check(lib.ptv3_pool_plan(_lib.ptr(code), _lib.ptr(order), _lib.ptr(grid_coord), _lib.ptr(batch),
+                                  k, n, n_scenes, int(pooling_depth), perm, _lib.ptr(cluster),
+                                  _lib.ptr(idx_ptr), _lib.ptr(head), _lib.ptr(pcode), _lib.ptr(porder),
+                                  _lib.ptr(pinv), _lib.ptr(pgrid), _lib.ptr(pbatch), _lib.ptr(meta),
+                                  _lib.ptr(status), _lib.ptr(ws), nbytes, _lib.stream()),
+               "ptv3_pool_plan")
+    host = torch.cat([meta, status.to(torch.int64)]).tolist()     # the one sync
+    if host[-1]:
+        raise _lib.Ptv3Error("ptv3_pool_plan: device status 0x%x" % host[-1])
+    m = host[0]
+    return dict(cluster=cluster, idx_ptr=idx_ptr[: m + 1], head=head[:m],
+                code=pcode[:, :m].contiguous(), order=porder[:, :m].contiguous(),
+                inverse=pinv[:, :m].contiguous(), grid_coord=pgrid[:m], batch=pbatch[:m],
+                counts=host[1:-1], m=m)
+
+
+def pool(x, coord, indices, idx_ptr, bn_scale=None, bn_shift=None):
+    """Segment max (+ BN + GELU) of x and mean of coord over clusters."""
+    _lib.require_cuda(x, indices, idx_ptr)
+    lib = _lib.load()
+    x = x.contiguous()
+    m = idx_ptr.numel() - 1
+    C = x.shape[1]
+    out = torch.empty((m, C), dtype=x.dtype, device=x.device)
+    cout = None
+    if coord is not None:
+        coord = coord.to(torch.float32).contiguous()
+        cout = torch.empty((m, 3), dtype=torch.float32, device=x.device)
+    _lib.check(lib.ptv3_pool_fwd(_lib.ptr(x), _lib.ptr(coord), _lib.ptr(indices), _lib.ptr(idx_ptr), m, C,
+                                 _lib.ptr(bn_scale), _lib.ptr(bn_shift), _lib.ptr(out), _lib.ptr(cout),
+                                 _lib.dtype_id(x), _lib.stream()), "ptv3_pool_fwd")
+    return out, cout
+
+
+def unpool(skip, child, cluster, skip_scale, skip_shift, child_scale, child_shift, want_skip_act=True):
+    _lib.require_cuda(skip, child, cluster)
+    lib = _lib.load()
+    skip, child = skip.contiguous(), child.contiguous()
+    n, C = skip.shape
+    out = torch.empty_like(skip)
+    act = torch.empty_like(skip) if want_skip_act else None
+    _lib.check(lib.ptv3_unpool_fwd(_lib.ptr(skip), _lib.ptr(child), _lib.ptr(cluster), n, C,
+                                   _lib.ptr(skip_scale), _lib.ptr(skip_shift), _lib.ptr(child_scale),
+                                   _lib.ptr(child_shift), _lib.ptr(out), _lib.ptr(act),
+                                   _lib.dtype_id(skip), _lib.stream()), "ptv3_unpool_fwd")
+    return out, act

@@ -1,0 +1,171 @@
+"""Parity of every C-ABI operator with the CPU oracle on identical seeded
+inputs: bit-exact for index work, within the stated tolerance for features."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from helpers import TOL, assert_close, rel_l2, small_batch
+from oracle import ptv3_oracle as O
+from pointtransformerv3_b200 import ops
+
+pytestmark = pytest.mark.gpu
+ORDERS = ["z", "z-trans", "hilbert", "hilbert-trans"]
+
+
+@pytest.mark.parametrize("counts,K", [([5000], 1024), ([1024], 1024), ([1025], 1024), ([2048, 2049], 1024),
+                                      ([300, 70, 4000], 128), ([70, 56], 56), ([10], 1024),
+                                      ([999, 1, 3000], 1000)])
+def test_pad_plan(counts, K):
+    offset = torch.cumsum(torch.tensor(counts), 0)
+    pad, unpad, cu = O.pad_plan(offset, K)
+    gp, gu, gc = ops.pad_plan(offset.cuda(), counts, K)
+    assert torch.equal(gp.cpu(), pad) and torch.equal(gu.cpu(), unpad) and torch.equal(gc.cpu(), cu)
+
+
+def _attention_case(sizes, C, H, K, dtype, seed=0):
+    data = small_batch(sizes, seed)
+    offset = data["offset"]
+    batch = O.offset_to_batch(offset)
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ["hilbert"])
+    g = torch.Generator().manual_seed(seed)
+    n = batch.shape[0]
+    feat = torch.randn(n, C, generator=g)
+    wq = torch.randn(3 * C, C, generator=g) / C ** 0.5
+    bq = torch.randn(3 * C, generator=g) * 0.1
+    wp = torch.randn(C, C, generator=g) / C ** 0.5
+    bp = torch.randn(C, generator=g) * 0.1
+    ref32 = O.attention(feat, wq, bq, wp, bp, order[0], inverse[0], offset, H, K)
+    cast = lambda t: t.to(dtype)
+    ref = O.attention(cast(feat), cast(wq), cast(bq), cast(wp), cast(bp), order[0], inverse[0], offset, H, K)
+    counts = O.offset_to_counts(offset).tolist()
+    Ke = min(min(counts), K)
+    pad, unpad, cu = ops.pad_plan(offset.cuda(), counts, Ke)
+    dev = lambda t: cast(t).cuda()
+    qkv = F.linear(dev(feat), dev(wq), dev(bq))
+    core = ops.attention(qkv, order[0].cuda(), pad, unpad, cu, H, Ke, (C // H) ** -0.5)
+    got = F.linear(core, dev(wp), dev(bp))
+    return got, ref, ref32
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes,C,H,K", [([3000], 64, 4, 1024), ([1500, 700], 32, 2, 128),
+                                         ([400, 90], 64, 4, 1024), ([2500], 128, 2, 512)])
+def test_attention_matches_oracle(sizes, C, H, K, dtype):
+    got, ref, ref32 = _attention_case(sizes, C, H, K, dtype)
+    assert got.dtype == dtype
+    assert_close(got, ref, what="attention", **TOL[dtype])
+    if dtype == torch.bfloat16:
+        # the kernel must be about as close to fp32 as the reference's own bf16 path
+        assert rel_l2(got, ref32) <= 2.0 * rel_l2(ref, ref32) + 1e-3
+    else:
+        assert rel_l2(got, ref) < 1e-5
+
+
+def test_kernel_map_matches_oracle_and_is_symmetric():
+    data = small_batch([4000, 2500], 1)
+    batch = O.offset_to_batch(data["offset"])
+    ind = O.sparse_indices(batch, data["grid_coord"])
+    for k in (3, 5):
+        ref = O.kernel_map(ind, k)
+        got = ops.kmap_build(ind.cuda(), k).cpu()
+        assert torch.equal(got.t().long(), ref)
+        kv = k ** 3
+        n = ind.shape[0]
+        ar = torch.arange(n)
+        for o in range(kv):
+            j = got[o].long()
+            m = j >= 0
+            assert torch.equal(got[kv - 1 - o][j[m]].long(), ar[m])
+        assert torch.equal(got[kv // 2].long(), ar)
+
+
+def test_kernel_map_duplicates_and_edges():
+    ind = torch.tensor([[0, 0, 0, 0], [0, 1, 0, 0], [0, 0, 0, 0], [1, 0, 0, 0], [0, 65535, 65535, 65535]],
+                       dtype=torch.int32)
+    ref = O.kernel_map(ind, 3)
+    got = ops.kmap_build(ind.cuda(), 3).cpu()
+    assert torch.equal(got.t().long(), ref)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("k,cin,cout", [(3, 32, 32), (3, 64, 64), (3, 128, 128), (5, 6, 32), (5, 4, 32),
+                                        (3, 48, 80)])
+def test_subm_conv_matches_oracle(k, cin, cout, dtype):
+    data = small_batch([3000, 1200], 2)
+    batch = O.offset_to_batch(data["offset"])
+    ind = O.sparse_indices(batch, data["grid_coord"])
+    n = ind.shape[0]
+    g = torch.Generator().manual_seed(k * 1000 + cin)
+    feat = torch.randn(n, cin, generator=g).to(dtype)
+    w = (torch.randn(cout, k, k, k, cin, generator=g) / (k ** 3 * cin) ** 0.5 * 3).to(dtype)
+    b = (torch.randn(cout, generator=g) * 0.1).to(dtype)
+    nbr_ref = O.kernel_map(ind, k)
+    ref = O.subm_conv(feat, nbr_ref, w, b)
+    nbr = ops.kmap_build(ind.cuda(), k)
+    got = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda())
+    assert_close(got, ref, what="conv", **TOL[dtype])
+    got_nb = ops.subm_conv(feat.cuda(), nbr, w.cuda(), None)
+    assert_close(got_nb, O.subm_conv(feat, nbr_ref, w, None), what="conv no bias", **TOL[dtype])
+
+
+@pytest.mark.parametrize("sizes", [[5000], [3000, 800, 1500]])
+@pytest.mark.parametrize("perm", [None, [2, 0, 3, 1]])
+def test_pool_plan_matches_oracle(sizes, perm):
+    data = small_batch(sizes, 3)
+    offset = data["offset"]
+    batch = O.offset_to_batch(offset)
+    fine_perm = torch.tensor([1, 3, 0, 2])
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ORDERS, perm=fine_perm)
+    # walk three levels, feeding each level's oracle outputs to both sides
+    grid, b = data["grid_coord"], batch
+    for level in range(3):
+        p = None if perm is None else torch.tensor(perm)
+        ref = O.pooling_plan(code, depth, 2, p)
+        got = ops.pool_plan(code.cuda(), order.cuda(), grid.cuda(), b.cuda(), len(sizes),
+                            ref["pooling_depth"], perm)
+        m = ref["code"].shape[1]
+        assert got["m"] == m
+        assert torch.equal(got["cluster"].cpu(), ref["cluster"])
+        assert torch.equal(got["code"].cpu(), ref["code"])
+        assert torch.equal(got["order"].cpu(), ref["order"])
+        assert torch.equal(got["inverse"].cpu(), ref["inverse"])
+        assert torch.equal(got["idx_ptr"].cpu(), ref["idx_ptr"])
+        rg = grid[ref["head"]] >> ref["pooling_depth"]
+        assert torch.equal(got["grid_coord"].cpu(), rg)
+        rb = b[ref["head"]]
+        assert torch.equal(got["batch"].cpu(), rb)
+        assert got["counts"] == torch.bincount(rb, minlength=len(sizes)).tolist()
+        # every head is a member of its cluster
+        assert torch.equal(ref["cluster"][got["head"].cpu()], torch.arange(m))
+        code, order, depth, grid, b = ref["code"], ref["order"], ref["depth"], rg, rb
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_pool_and_unpool_features(dtype):
+    data = small_batch([4000, 1000], 4)
+    batch = O.offset_to_batch(data["offset"])
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ORDERS)
+    plan = O.pooling_plan(code, depth, 2)
+    n, C = batch.shape[0], 64
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(n, C, generator=g).to(dtype)
+    sd = {"w": 1 + 0.1 * torch.randn(C, generator=g), "b": 0.1 * torch.randn(C, generator=g),
+          "m": 0.1 * torch.randn(C, generator=g), "v": 0.5 + torch.rand(C, generator=g)}
+    bn = lambda t: F.batch_norm(t, sd["m"].to(dtype), sd["v"].to(dtype), sd["w"].to(dtype), sd["b"].to(dtype),
+                                False, 0.0, 1e-3)
+    ref = F.gelu(bn(O.segment_reduce(x[plan["indices"]], plan["idx_ptr"], "max")))
+    ref_coord = O.segment_reduce(data["coord"][plan["indices"]], plan["idx_ptr"], "mean")
+    scale = (sd["w"] / torch.sqrt(sd["v"] + 1e-3)).cuda()
+    shift = (sd["b"] - sd["m"] * sd["w"] / torch.sqrt(sd["v"] + 1e-3)).cuda()
+    got, got_coord = ops.pool(x.cuda(), data["coord"].cuda(), order[0].cuda(), plan["idx_ptr"].cuda(), scale, shift)
+    assert_close(got, ref, what="pool", **TOL[dtype])
+    assert_close(got_coord, ref_coord, atol=1e-5, rtol=1e-5, what="coord mean")
+    # unpool
+    m = plan["code"].shape[1]
+    child = torch.randn(m, C, generator=g).to(dtype)
+    ref_a = F.gelu(bn(child))
+    ref_b = F.gelu(bn(x))
+    ref_u = ref_b + ref_a[plan["cluster"]]
+    out, act = ops.unpool(x.cuda(), child.cuda(), plan["cluster"].cuda(), scale, shift, scale, shift)
+    assert_close(out, ref_u, what="unpool", **TOL[dtype])
+    assert_close(act, ref_b, what="unpool skip", **TOL[dtype])
