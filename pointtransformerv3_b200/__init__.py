@@ -1,1 +1,11 @@
 """B200-native inference path of Point Transformer V3 behind the reference's API."""
+from . import serialization
+from .point import Point, batch2offset, offset2batch, offset2bincount
+from .sparse import SparseConvTensor, SubMConv3d
+from .model import (Block, Embedding, GridPooling, GridUnpooling, MLP, PointModule, PointSequential,
+                    PointTransformerV3, SerializedAttention, SerializedPooling, SerializedUnpooling)
+
+__all__ = ["serialization", "Point", "batch2offset", "offset2batch", "offset2bincount", "SparseConvTensor",
+           "SubMConv3d", "Block", "Embedding", "GridPooling", "GridUnpooling", "MLP", "PointModule",
+           "PointSequential", "PointTransformerV3", "SerializedAttention", "SerializedPooling",
+           "SerializedUnpooling"]

@@ -1,0 +1,460 @@
+"""Point Transformer V3 backbone with the reference's module names, constructor
+arguments and state_dict layout (model.py:177-982).  Host code is PyTorch; the
+point operators (serialization, patch attention, submanifold convolution,
+pooling) call the CUDA library, dense Linear layers use torch's GEMM."""
+import math
+import sys
+from collections import OrderedDict
+from functools import partial
+
+import torch
+import torch.nn as nn
+
+from . import ops
+from . import sparse as spconv
+from .point import AttrDict, Point, offset2bincount
+
+
+class PointModule(nn.Module):
+    """Modules derived from this class take and return a Point inside a
+    PointSequential (model.py:177-183)."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__(*args, **kwargs)
+
+
+class PointSequential(PointModule):
+    """Sequential container dispatching on module type (model.py:186-252): Point
+    modules get the Point, sparse-convolution modules its sparse tensor, plain
+    torch modules its feature matrix (mirrored into the sparse tensor)."""
+
+    def __init__(self, *args, **kwargs):
+        super().__init__()
+        if len(args) == 1 and isinstance(args[0], OrderedDict):
+            for key, module in args[0].items():
+                self.add_module(key, module)
+        else:
+            for idx, module in enumerate(args):
+                self.add_module(str(idx), module)
+        for name, module in kwargs.items():
+            if name in self._modules:
+                raise ValueError("name exists.")
+            self.add_module(name, module)
+
+    def __getitem__(self, idx):
+        if not (-len(self) <= idx < len(self)):
+            raise IndexError("index {} is out of range".format(idx))
+        if idx < 0:
+            idx += len(self)
+        return list(self._modules.values())[idx]
+
+    def __len__(self):
+        return len(self._modules)
+
+    def add(self, module, name=None):
+        if name is None:
+            name = str(len(self._modules))
+            if name in self._modules:
+                raise KeyError("name exists")
+        self.add_module(name, module)
+
+    def forward(self, input):
+        for module in self._modules.values():
+            if isinstance(module, PointModule):
+                input = module(input)
+            elif spconv.modules.is_spconv_module(module):
+                if isinstance(input, Point):
+                    input.sparse_conv_feat = module(input.sparse_conv_feat)
+                    input.feat = input.sparse_conv_feat.features
+                else:
+                    input = module(input)
+            else:
+                if isinstance(input, Point):
+                    input.feat = module(input.feat)
+                    if "sparse_conv_feat" in input.keys():
+                        input.sparse_conv_feat = input.sparse_conv_feat.replace_feature(input.feat)
+                elif isinstance(input, spconv.SparseConvTensor):
+                    if input.indices.shape[0] != 0:
+                        input = input.replace_feature(module(input.features))
+                else:
+                    input = module(input)
+        return input
+
+
+def _bn_eval_affine(bn):
+    """Per-channel (scale, shift) of a BatchNorm1d in eval mode, fp32."""
+    w = bn.weight.float() if bn.weight is not None else torch.ones_like(bn.running_var)
+    b = bn.bias.float() if bn.bias is not None else torch.zeros_like(bn.running_var)
+    scale = w * torch.rsqrt(bn.running_var.float() + bn.eps)
+    return scale.contiguous(), (b - bn.running_mean.float() * scale).contiguous()
+
+
+def _is_bn_gelu(norm, act):
+    """True when (norm, act) is the BatchNorm1d(eval) + exact GELU pair the fused
+    pooling kernels implement."""
+    if norm is None or act is None or len(norm) != 1 or len(act) != 1:
+        return False
+    n, a = norm[0], act[0]
+    return (type(n) is nn.BatchNorm1d and not n.training and n.track_running_stats
+            and type(a) is nn.GELU and getattr(a, "approximate", "none") == "none")
+
+
+class SerializedAttention(PointModule):
+    """Multi-head self-attention inside patches of a serialized order
+    (model.py:319-490).  Both settings of ``enable_flash`` run the same CUDA
+    kernel; the flag keeps the reference's patch-size rule: off -> patch =
+    min(smallest scene, patch_size) re-evaluated per call (model.py:441-444),
+    on -> patch = patch_size with shorter scenes as one short sequence."""
+
+    def __init__(self, channels, num_heads, patch_size, qkv_bias=True, qk_scale=None, attn_drop=0.0,
+                 proj_drop=0.0, order_index=0, enable_rpe=False, enable_flash=True,
+                 upcast_attention=True, upcast_softmax=True):
+        super().__init__()
+        assert channels % num_heads == 0
+        self.channels = channels
+        self.num_heads = num_heads
+        self.scale = qk_scale or (channels // num_heads) ** -0.5
+        self.order_index = order_index
+        self.upcast_attention = upcast_attention
+        self.upcast_softmax = upcast_softmax
+        self.enable_rpe = enable_rpe
+        self.enable_flash = enable_flash
+        if enable_rpe:
+            raise NotImplementedError("relative position bias (enable_rpe) is not implemented")
+        if enable_flash:
+            assert upcast_attention is False, "Set upcast_attention to False when enable Flash Attention"
+            assert upcast_softmax is False, "Set upcast_softmax to False when enable Flash Attention"
+            self.patch_size = patch_size
+        else:
+            self.patch_size_max = patch_size
+            self.patch_size = 0
+        self.attn_drop = attn_drop
+        self.qkv = nn.Linear(channels, channels * 3, bias=qkv_bias)
+        self.proj = nn.Linear(channels, channels)
+        self.proj_drop = nn.Dropout(proj_drop)
+        self.algo = 0
+
+    @torch.no_grad()
+    def get_padding_and_inverse(self, point):
+        """model.py:382-438; cached in the Point under the reference's keys."""
+        if not {"pad", "unpad", "cu_seqlens_key"}.issubset(point.keys()):
+            pad, unpad, cu = ops.pad_plan(point.offset, point.host_counts(), self.patch_size)
+            point["pad"], point["unpad"], point["cu_seqlens_key"] = pad, unpad, cu
+        return point["pad"], point["unpad"], point["cu_seqlens_key"]
+
+    def forward(self, point):
+        assert not self.training, "inference only"
+        if not self.enable_flash:
+            self.patch_size = min(min(point.host_counts()), self.patch_size_max)
+        pad, unpad, cu_seqlens = self.get_padding_and_inverse(point)
+        qkv = self.qkv(point.feat)
+        feat = ops.attention(qkv, point.serialized_order[self.order_index], pad, unpad, cu_seqlens,
+                             self.num_heads, self.patch_size, self.scale, self.algo)
+        feat = self.proj(feat)
+        feat = self.proj_drop(feat)
+        point.feat = feat
+        return point
+
+
+class MLP(nn.Module):
+    """model.py:493-516."""
+
+    def __init__(self, in_channels, hidden_channels=None, out_channels=None, act_layer=nn.GELU, drop=0.0):
+        super().__init__()
+        out_channels = out_channels or in_channels
+        hidden_channels = hidden_channels or in_channels
+        self.fc1 = nn.Linear(in_channels, hidden_channels)
+        self.act = act_layer()
+        self.fc2 = nn.Linear(hidden_channels, out_channels)
+        self.drop = nn.Dropout(drop)
+
+    def forward(self, x):
+        return self.drop(self.fc2(self.drop(self.act(self.fc1(x)))))
+
+
+class Block(PointModule):
+    """xCPE convolution + attention + MLP with residuals (model.py:519-606)."""
+
+    def __init__(self, channels, num_heads, patch_size=48, mlp_ratio=4.0, qkv_bias=True, qk_scale=None,
+                 attn_drop=0.0, proj_drop=0.0, drop_path=0.0, norm_layer=nn.LayerNorm, act_layer=nn.GELU,
+                 pre_norm=True, order_index=0, cpe_indice_key=None, enable_rpe=False, enable_flash=True,
+                 upcast_attention=True, upcast_softmax=True):
+        super().__init__()
+        self.channels = channels
+        self.pre_norm = pre_norm
+        self.cpe = PointSequential(
+            spconv.SubMConv3d(channels, channels, kernel_size=3, bias=True, indice_key=cpe_indice_key),
+            nn.Linear(channels, channels),
+            norm_layer(channels),
+        )
+        self.norm1 = PointSequential(norm_layer(channels))
+        self.attn = SerializedAttention(
+            channels=channels, patch_size=patch_size, num_heads=num_heads, qkv_bias=qkv_bias,
+            qk_scale=qk_scale, attn_drop=attn_drop, proj_drop=proj_drop, order_index=order_index,
+            enable_rpe=enable_rpe, enable_flash=enable_flash, upcast_attention=upcast_attention,
+            upcast_softmax=upcast_softmax)
+        self.norm2 = PointSequential(norm_layer(channels))
+        self.mlp = PointSequential(MLP(in_channels=channels, hidden_channels=int(channels * mlp_ratio),
+                                       out_channels=channels, act_layer=act_layer, drop=proj_drop))
+        # stochastic depth is the identity at inference; the rate is kept for bookkeeping
+        self.drop_path_rate = drop_path
+        self.drop_path = PointSequential(nn.Identity())
+
+    def forward(self, point):
+        assert not self.training, "inference only"
+        shortcut = point.feat
+        point = self.cpe(point)
+        point.feat = shortcut + point.feat
+        shortcut = point.feat
+        if self.pre_norm:
+            point = self.norm1(point)
+        point = self.drop_path(self.attn(point))
+        point.feat = shortcut + point.feat
+        if not self.pre_norm:
+            point = self.norm1(point)
+        shortcut = point.feat
+        if self.pre_norm:
+            point = self.norm2(point)
+        point = self.drop_path(self.mlp(point))
+        point.feat = shortcut + point.feat
+        if not self.pre_norm:
+            point = self.norm2(point)
+        point.sparse_conv_feat = point.sparse_conv_feat.replace_feature(point.feat)
+        return point
+
+
+class SerializedPooling(PointModule):
+    """Pools the points that share a parent cell of the serialization grid
+    (model.py:609-712)."""
+
+    def __init__(self, in_channels, out_channels, stride=2, norm_layer=None, act_layer=None, reduce="max",
+                 shuffle_orders=True, traceable=True):
+        super().__init__()
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        assert stride == 2 ** (math.ceil(stride) - 1).bit_length()
+        self.stride = stride
+        assert reduce in ["sum", "mean", "min", "max"]
+        if reduce != "max":
+            raise NotImplementedError("only reduce='max' is implemented")
+        self.reduce = reduce
+        self.shuffle_orders = shuffle_orders
+        self.traceable = traceable
+        self.proj = nn.Linear(in_channels, out_channels)
+        self.norm = PointSequential(norm_layer(out_channels)) if norm_layer is not None else None
+        self.act = PointSequential(act_layer()) if act_layer is not None else None
+
+    def forward(self, point):
+        assert not self.training, "inference only"
+        pooling_depth = (math.ceil(self.stride) - 1).bit_length()
+        if pooling_depth > point.serialized_depth:
+            pooling_depth = 0
+        assert {"serialized_code", "serialized_order", "serialized_inverse", "serialized_depth"}.issubset(
+            point.keys()), "Run point.serialization() point cloud before SerializedPooling"
+        k = point.serialized_code.shape[0]
+        perm = torch.randperm(k).tolist() if self.shuffle_orders else None
+        plan = ops.pool_plan(point.serialized_code, point.serialized_order, point.grid_coord, point.batch,
+                             len(point.offset), pooling_depth, perm)
+        fused = _is_bn_gelu(self.norm, self.act)
+        scale = shift = None
+        if fused:
+            scale, shift = _bn_eval_affine(self.norm[0])
+        feat, coord = ops.pool(self.proj(point.feat), point.coord if "coord" in point.keys() else None,
+                               point.serialized_order[0], plan["idx_ptr"], scale, shift)
+        counts = plan["counts"]
+        point_dict = AttrDict(
+            feat=feat,
+            grid_coord=plan["grid_coord"],
+            serialized_code=plan["code"],
+            serialized_order=plan["order"],
+            serialized_inverse=plan["inverse"],
+            serialized_depth=point.serialized_depth - pooling_depth,
+            batch=plan["batch"],
+            offset=plan["offset"],
+        )
+        if coord is not None:
+            point_dict["coord"] = coord
+        if "condition" in point.keys():
+            point_dict["condition"] = point.condition
+        if "context" in point.keys():
+            point_dict["context"] = point.context
+        if self.traceable:
+            point_dict["pooling_inverse"] = plan["cluster"]
+            point_dict["pooling_parent"] = point
+        point = Point(point_dict)
+        point["_counts"] = counts
+        if not fused:
+            if self.norm is not None:
+                point = self.norm(point)
+            if self.act is not None:
+                point = self.act(point)
+        point.sparsify()
+        return point
+
+
+class SerializedUnpooling(PointModule):
+    """Projects the coarse level and its skip connection and adds the
+    up-sampled coarse features to the parent level (model.py:715-750)."""
+
+    def __init__(self, in_channels, skip_channels, out_channels, norm_layer=None, act_layer=None,
+                 traceable=False):
+        super().__init__()
+        self.proj = PointSequential(nn.Linear(in_channels, out_channels))
+        self.proj_skip = PointSequential(nn.Linear(skip_channels, out_channels))
+        if norm_layer is not None:
+            self.proj.add(norm_layer(out_channels))
+            self.proj_skip.add(norm_layer(out_channels))
+        if act_layer is not None:
+            self.proj.add(act_layer())
+            self.proj_skip.add(act_layer())
+        self.traceable = traceable
+
+    def _fusable(self):
+        def ok(seq):
+            return (len(seq) == 3 and type(seq[1]) is nn.BatchNorm1d and not seq[1].training
+                    and type(seq[2]) is nn.GELU and getattr(seq[2], "approximate", "none") == "none")
+        return ok(self.proj) and ok(self.proj_skip)
+
+    def forward(self, point):
+        assert not self.training, "inference only"
+        assert "pooling_parent" in point.keys()
+        assert "pooling_inverse" in point.keys()
+        parent = point.pop("pooling_parent")
+        inverse = point.pop("pooling_inverse")
+        if self._fusable():
+            child_lin = self.proj[0](point.feat)
+            skip_lin = self.proj_skip[0](parent.feat)
+            cs, cb = _bn_eval_affine(self.proj[1])
+            ss, sb = _bn_eval_affine(self.proj_skip[1])
+            out, skip_act = ops.unpool(skip_lin, child_lin, inverse, ss, sb, cs, cb)
+            # the parent's sparse tensor keeps the skip branch alone: the reference
+            # adds the up-sampled features to `feat` only (model.py:746), and the next
+            # block's convolution reads the sparse tensor
+            parent.feat = skip_act
+            if "sparse_conv_feat" in parent.keys():
+                parent.sparse_conv_feat = parent.sparse_conv_feat.replace_feature(skip_act)
+            parent.feat = out
+            if self.traceable:
+                point.feat = torch.nn.functional.gelu(torch.nn.functional.batch_norm(
+                    child_lin, self.proj[1].running_mean, self.proj[1].running_var, self.proj[1].weight,
+                    self.proj[1].bias, False, 0.0, self.proj[1].eps))
+        else:
+            point = self.proj(point)
+            parent = self.proj_skip(parent)
+            parent.feat = parent.feat + point.feat[inverse]
+        if self.traceable:
+            parent["unpooling_parent"] = point
+        return parent
+
+
+class Embedding(PointModule):
+    """Stem: 5x5x5 submanifold convolution + norm + activation (model.py:753-783)."""
+
+    def __init__(self, in_channels, embed_channels, norm_layer=None, act_layer=None):
+        super().__init__()
+        self.in_channels = in_channels
+        self.embed_channels = embed_channels
+        self.stem = PointSequential(conv=spconv.SubMConv3d(in_channels, embed_channels, kernel_size=5,
+                                                           padding=1, bias=False, indice_key="stem"))
+        if norm_layer is not None:
+            self.stem.add(norm_layer(embed_channels), name="norm")
+        if act_layer is not None:
+            self.stem.add(act_layer(), name="act")
+
+    def forward(self, point):
+        return self.stem(point)
+
+
+class PointTransformerV3(PointModule):
+    """The backbone (model.py:786-982); constructor arguments as in the reference."""
+
+    def __init__(self, in_channels=6, order=("z", "z-trans", "hilbert", "hilbert-trans"), stride=(2, 2, 2, 2),
+                 enc_depths=(2, 2, 2, 6, 2), enc_channels=(32, 64, 128, 256, 512),
+                 enc_num_head=(2, 4, 8, 16, 32), enc_patch_size=(1024, 1024, 1024, 1024, 1024),
+                 dec_depths=(2, 2, 2, 2), dec_channels=(64, 64, 128, 256), dec_num_head=(4, 4, 8, 16),
+                 dec_patch_size=(1024, 1024, 1024, 1024), mlp_ratio=4, qkv_bias=True, qk_scale=None,
+                 attn_drop=0.0, proj_drop=0.0, drop_path=0.3, pre_norm=True, shuffle_orders=True,
+                 enable_rpe=False, enable_flash=True, upcast_attention=False, upcast_softmax=False,
+                 cls_mode=False, pdnorm_bn=False, pdnorm_ln=False, pdnorm_decouple=True,
+                 pdnorm_adaptive=False, pdnorm_affine=True,
+                 pdnorm_conditions=("ScanNet", "S3DIS", "Structured3D")):
+        super().__init__()
+        self.num_stages = len(enc_depths)
+        self.order = [order] if isinstance(order, str) else order
+        self.cls_mode = cls_mode
+        self.shuffle_orders = shuffle_orders
+        assert self.num_stages == len(stride) + 1
+        assert self.num_stages == len(enc_depths)
+        assert self.num_stages == len(enc_channels)
+        assert self.num_stages == len(enc_num_head)
+        assert self.num_stages == len(enc_patch_size)
+        assert self.cls_mode or self.num_stages == len(dec_depths) + 1
+        assert self.cls_mode or self.num_stages == len(dec_channels) + 1
+        assert self.cls_mode or self.num_stages == len(dec_num_head) + 1
+        assert self.cls_mode or self.num_stages == len(dec_patch_size) + 1
+        if pdnorm_bn or pdnorm_ln:
+            raise NotImplementedError("per-dataset normalisation (pdnorm_*) is not implemented")
+        bn_layer = partial(nn.BatchNorm1d, eps=1e-3, momentum=0.01)
+        ln_layer = nn.LayerNorm
+        act_layer = nn.GELU
+
+        self.embedding = Embedding(in_channels=in_channels, embed_channels=enc_channels[0],
+                                   norm_layer=bn_layer, act_layer=act_layer)
+        enc_drop_path = [x.item() for x in torch.linspace(0, drop_path, sum(enc_depths))]
+        self.enc = PointSequential()
+        for s in range(self.num_stages):
+            enc_drop_path_ = enc_drop_path[sum(enc_depths[:s]): sum(enc_depths[: s + 1])]
+            enc = PointSequential()
+            if s > 0:
+                enc.add(SerializedPooling(in_channels=enc_channels[s - 1], out_channels=enc_channels[s],
+                                          stride=stride[s - 1], norm_layer=bn_layer, act_layer=act_layer),
+                        name="down")
+            for i in range(enc_depths[s]):
+                enc.add(Block(channels=enc_channels[s], num_heads=enc_num_head[s],
+                              patch_size=enc_patch_size[s], mlp_ratio=mlp_ratio, qkv_bias=qkv_bias,
+                              qk_scale=qk_scale, attn_drop=attn_drop, proj_drop=proj_drop,
+                              drop_path=enc_drop_path_[i], norm_layer=ln_layer, act_layer=act_layer,
+                              pre_norm=pre_norm, order_index=i % len(self.order),
+                              cpe_indice_key=f"stage{s}", enable_rpe=enable_rpe, enable_flash=enable_flash,
+                              upcast_attention=upcast_attention, upcast_softmax=upcast_softmax),
+                        name=f"block{i}")
+            if len(enc) != 0:
+                self.enc.add(module=enc, name=f"enc{s}")
+
+        if not self.cls_mode:
+            dec_drop_path = [x.item() for x in torch.linspace(0, drop_path, sum(dec_depths))]
+            self.dec = PointSequential()
+            dec_channels = list(dec_channels) + [enc_channels[-1]]
+            for s in reversed(range(self.num_stages - 1)):
+                dec_drop_path_ = dec_drop_path[sum(dec_depths[:s]): sum(dec_depths[: s + 1])]
+                dec_drop_path_.reverse()
+                dec = PointSequential()
+                dec.add(SerializedUnpooling(in_channels=dec_channels[s + 1], skip_channels=enc_channels[s],
+                                            out_channels=dec_channels[s], norm_layer=bn_layer,
+                                            act_layer=act_layer), name="up")
+                for i in range(dec_depths[s]):
+                    dec.add(Block(channels=dec_channels[s], num_heads=dec_num_head[s],
+                                  patch_size=dec_patch_size[s], mlp_ratio=mlp_ratio, qkv_bias=qkv_bias,
+                                  qk_scale=qk_scale, attn_drop=attn_drop, proj_drop=proj_drop,
+                                  drop_path=dec_drop_path_[i], norm_layer=ln_layer, act_layer=act_layer,
+                                  pre_norm=pre_norm, order_index=i % len(self.order),
+                                  cpe_indice_key=f"stage{s}", enable_rpe=enable_rpe,
+                                  enable_flash=enable_flash, upcast_attention=upcast_attention,
+                                  upcast_softmax=upcast_softmax), name=f"block{i}")
+                self.dec.add(module=dec, name=f"dec{s}")
+
+    def forward(self, data_dict):
+        """data_dict: ``feat``, ``grid_coord`` (or ``coord`` + ``grid_size``) and
+        ``offset`` or ``batch``; returns the Point of the finest level."""
+        point = Point(data_dict)
+        point.serialization(order=self.order, shuffle_orders=self.shuffle_orders)
+        point.sparsify()
+        point = self.embedding(point)
+        point = self.enc(point)
+        if not self.cls_mode:
+            point = self.dec(point)
+        return point
+
+
+GridPooling = SerializedPooling
+GridUnpooling = SerializedUnpooling

@@ -143,7 +143,8 @@ def subm_conv(feat, nbr, weight, bias=None, algo=0):
 def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=None):
     """Builds the pooled level's index tensors; one host sync to learn its size.
 
-    Returns dict(cluster, idx_ptr, head, code, order, inverse, grid_coord, batch, counts)."""
+    Returns dict(cluster, idx_ptr, head, code, order, inverse, grid_coord, batch, counts,
+    offset, m)."""
     _lib.require_cuda(code, order, grid_coord, batch)
     lib = _lib.load()
     code, order = code.contiguous(), order.contiguous()
@@ -180,7 +181,7 @@ def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=
     return dict(cluster=cluster, idx_ptr=idx_ptr[: m + 1], head=head[:m],
                 code=pcode[:, :m].contiguous(), order=porder[:, :m].contiguous(),
                 inverse=pinv[:, :m].contiguous(), grid_coord=pgrid[:m], batch=pbatch[:m],
-                counts=host[1:-1], m=m)
+                counts=host[1:-1], m=m, offset=torch.cumsum(meta[1:], 0))
 
 
 def pool(x, coord, indices, idx_ptr, bn_scale=None, bn_shift=None):

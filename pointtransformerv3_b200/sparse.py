@@ -1,0 +1,83 @@
+"""The slice of spconv's interface the model uses (SparseConvTensor,
+SubMConv3d, modules.is_spconv_module; call sites model.py:165-172, :233-249,
+:546-552, :767-774), implemented on the CUDA library's kernel map and
+submanifold convolution."""
+import math
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+
+class SparseConvTensor:
+    """features (N,C), indices (N,4) int32 rows (batch, x, y, z).  Kernel maps
+    are cached in ``indice_dict`` under ``(indice_key, kernel_size)`` and shared
+    by every tensor derived with ``replace_feature``."""
+
+    def __init__(self, features, indices, spatial_shape, batch_size, indice_dict=None):
+        self.features = features
+        self.indices = indices
+        self.spatial_shape = spatial_shape
+        self.batch_size = batch_size
+        self.indice_dict = {} if indice_dict is None else indice_dict
+
+    def replace_feature(self, feature):
+        return SparseConvTensor(feature, self.indices, self.spatial_shape, self.batch_size, self.indice_dict)
+
+    def kernel_map(self, kernel_size, indice_key=None):
+        key = (indice_key, kernel_size)
+        if indice_key is not None and key in self.indice_dict:
+            return self.indice_dict[key]
+        nbr = ops.kmap_build(self.indices, kernel_size)
+        if indice_key is not None:
+            self.indice_dict[key] = nbr
+        return nbr
+
+
+class SparseModule(nn.Module):
+    """Marker base class (what ``is_spconv_module`` looks for)."""
+
+
+class SubMConv3d(SparseModule):
+    """Submanifold 3-D convolution: outputs only at the input's active voxels.
+    ``weight`` is (out, k, k, k, in); ``padding``/``stride``/``dilation`` other
+    than the defaults do not change a submanifold convolution's output sites
+    and only unit stride/dilation are supported."""
+
+    def __init__(self, in_channels, out_channels, kernel_size, stride=1, padding=0, dilation=1, groups=1,
+                 bias=True, indice_key=None, algo=None, fp32_accum=None, **unused):
+        super().__init__()
+        if not isinstance(kernel_size, int):
+            assert len(set(kernel_size)) == 1, "only cubic kernels are supported"
+            kernel_size = kernel_size[0]
+        assert kernel_size % 2 == 1 and kernel_size <= 7
+        assert stride in (1, (1, 1, 1), [1, 1, 1]) and dilation in (1, (1, 1, 1), [1, 1, 1]) and groups == 1
+        self.in_channels = in_channels
+        self.out_channels = out_channels
+        self.kernel_size = kernel_size
+        self.indice_key = indice_key
+        k = kernel_size
+        self.weight = nn.Parameter(torch.empty(out_channels, k, k, k, in_channels))
+        self.bias = nn.Parameter(torch.empty(out_channels)) if bias else None
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        fan_in = self.in_channels * self.kernel_size ** 3
+        bound = 1.0 / math.sqrt(fan_in)
+        nn.init.uniform_(self.weight, -bound, bound)
+        if self.bias is not None:
+            nn.init.uniform_(self.bias, -bound, bound)
+
+    def forward(self, x):
+        nbr = x.kernel_map(self.kernel_size, self.indice_key)
+        return x.replace_feature(ops.subm_conv(x.features, nbr, self.weight, self.bias))
+
+
+class _Modules:
+    @staticmethod
+    def is_spconv_module(module):
+        return isinstance(module, SparseModule)
+
+
+modules = _Modules()

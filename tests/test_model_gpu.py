@@ -1,0 +1,215 @@
+"""Module- and backbone-level parity of the CUDA-backed modules with the golden
+vectors of the reference and with the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from helpers import TOL, assert_close, rel_l2, small_batch
+from oracle import ptv3_oracle as O, weights
+import pointtransformerv3_b200 as P
+
+pytestmark = pytest.mark.gpu
+ORDERS = ["z", "z-trans", "hilbert", "hilbert-trans"]
+SMALL_CFG = dict(enc_depths=(1, 1, 1, 2, 1), enc_channels=(32, 32, 64, 64, 128), enc_num_head=(2, 2, 4, 4, 8),
+                 enc_patch_size=(128,) * 5, dec_depths=(1, 1, 1, 1), dec_channels=(32, 32, 64, 64),
+                 dec_num_head=(2, 2, 4, 4), dec_patch_size=(128,) * 4)
+
+
+def load(name):
+    return np.load(os.path.join(GOLDEN, name))
+
+
+def from_bf16_bits(a):
+    return torch.from_numpy(a.copy()).view(torch.bfloat16)
+
+
+def cuda_data(data, dtype=None):
+    d = {k: v.cuda() for k, v in data.items()}
+    if dtype is not None:
+        d["feat"] = d["feat"].to(dtype)
+    return d
+
+
+def test_point_serialization_golden():
+    g = load("serialization.npz")
+    data = small_batch([3000, 1700], seed=11)
+    torch.manual_seed(5)
+    pt = P.Point(cuda_data(data))
+    pt.serialization(order=ORDERS, shuffle_orders=True)
+    assert pt.serialized_depth == int(g["point_depth"])
+    assert (pt.serialized_code.cpu().numpy() == g["point_code"]).all()
+    assert (pt.serialized_order.cpu().numpy() == g["point_order"]).all()
+    assert (pt.serialized_inverse.cpu().numpy() == g["point_inverse"]).all()
+
+
+def test_serialization_api_golden():
+    g = load("serialization.npz")
+    for depth in (1, 3, 9, 11, 16):
+        grid = torch.from_numpy(g[f"grid_d{depth}"]).cuda()
+        batch = torch.from_numpy(g[f"batch_d{depth}"]).cuda()
+        for o in ORDERS:
+            got = P.serialization.encode(grid, batch, depth, o)
+            assert (got.cpu().numpy() == g[f"code_d{depth}_{o}"]).all(), (depth, o)
+
+
+@pytest.mark.parametrize("name,sizes,C,H,K,oi", [("a", [1800], 32, 2, 128, 0), ("b", [700, 90, 400], 64, 4, 256, 1)])
+def test_attention_module_golden(name, sizes, C, H, K, oi):
+    g = load("attention.npz")
+    data = small_batch(sizes, seed=21)
+    pt = P.Point(cuda_data(data))
+    pt.serialization(order=["hilbert", "z"], shuffle_orders=False)
+    n = pt.batch.shape[0]
+    feat = weights.keyed_tensor("attention.feat." + name, (n, C))
+    att = P.SerializedAttention(C, H, K, order_index=oi, enable_flash=False, upcast_attention=False,
+                                upcast_softmax=False).eval()
+    weights.fill_state_dict(att, prefix="attention.%s." % name)
+    att = att.cuda()
+    with torch.inference_mode():
+        pt.feat = feat.cuda()
+        out = att(pt).feat
+        pad, unpad, cu = att.get_padding_and_inverse(pt)
+        assert (pad.cpu().numpy() == g[name + "_pad"]).all()
+        assert (unpad.cpu().numpy() == g[name + "_unpad"]).all()
+        assert (cu.cpu().numpy() == g[name + "_cu"]).all()
+        ref = torch.from_numpy(g[name + "_fp32"])
+        assert_close(out, ref, what="attention fp32", **TOL[torch.float32])
+        att = att.bfloat16()
+        pt.feat = feat.cuda().bfloat16()
+        out16 = att(pt).feat
+        assert_close(out16, from_bf16_bits(g[name + "_bf16"]), what="attention bf16", **TOL[torch.bfloat16])
+        assert rel_l2(out16, ref) < 1e-2
+
+
+def test_pooling_modules_golden():
+    g = load("pooling.npz")
+    data = small_batch([2500, 1200], seed=31)
+    torch.manual_seed(9)
+    pt = P.Point(cuda_data(data))
+    pt.serialization(order=ORDERS, shuffle_orders=True)
+    n = pt.batch.shape[0]
+    pt.feat = weights.keyed_tensor("pooling.feat", (n, 32)).cuda()
+    pt.sparsify()
+    bn = lambda c: torch.nn.BatchNorm1d(c, eps=1e-3, momentum=0.01)
+    pool = P.GridPooling(32, 64, stride=2, norm_layer=bn, act_layer=torch.nn.GELU).eval()
+    up = P.GridUnpooling(64, 32, 48, norm_layer=bn, act_layer=torch.nn.GELU).eval()
+    weights.fill_state_dict(pool, prefix="pooling.down.")
+    weights.fill_state_dict(up, prefix="pooling.up.")
+    pool, up = pool.cuda(), up.cuda()
+    with torch.inference_mode():
+        c = pool(pt)
+        for k in ("grid_coord", "batch", "serialized_code", "serialized_order", "serialized_inverse",
+                  "pooling_inverse", "offset"):
+            assert (c[k].cpu().numpy() == g["down_" + k]).all(), k
+        assert c.serialized_depth == int(g["down_depth"])
+        assert_close(c.feat, torch.from_numpy(g["down_feat"]), what="pooled feat", **TOL[torch.float32])
+        assert_close(c.coord, torch.from_numpy(g["down_coord"]), atol=1e-5, rtol=1e-5, what="pooled coord")
+        p = up(c)
+        assert_close(p.feat, torch.from_numpy(g["up_feat"]), what="unpooled feat", **TOL[torch.float32])
+        assert_close(p.sparse_conv_feat.features, torch.from_numpy(g["up_sparse_feat"]),
+                     what="sparse tensor after unpooling", **TOL[torch.float32])
+
+
+def _small_net(dtype):
+    net = P.PointTransformerV3(in_channels=6, enable_flash=False, **SMALL_CFG).eval()
+    sd = weights.fill_state_dict(net, prefix="ptv3.")
+    return net.cuda().to(dtype), sd
+
+
+def test_backbone_golden_fp32():
+    g = load("backbone.npz")
+    data = small_batch([6000, 4000], seed=41)
+    net, _ = _small_net(torch.float32)
+    stage = {}
+    for name in ("embedding", "enc.enc0", "enc.enc2", "enc.enc4", "dec.dec3", "dec.dec1"):
+        net.get_submodule(name).register_forward_hook(
+            lambda m, i, o, name=name: stage.__setitem__(name, o.feat.detach().clone()))
+    with torch.inference_mode():
+        torch.manual_seed(1)
+        out = net(cuda_data(data))
+    assert (out.serialized_order.cpu().numpy() == g["order"]).all()
+    for k, v in stage.items():
+        ref = torch.from_numpy(g["fp32_" + k])
+        assert_close(v[:: max(1, v.shape[0] // 256)], ref, atol=2e-4, rtol=2e-4, what=k)
+    # 11 blocks deep: errors of the order of 1e-6 per operator accumulate
+    assert_close(out.feat, torch.from_numpy(g["fp32"]), atol=5e-4, rtol=5e-4, what="backbone fp32")
+    assert rel_l2(out.feat, torch.from_numpy(g["fp32"])) < 1e-5
+
+
+def test_backbone_golden_bf16():
+    """End to end in bf16 the reference differs from its own fp32 run by far more
+    than the per-operator tolerance, so the bound here is relative to that noise
+    floor: the CUDA path must be as close to the fp32 reference as the bf16
+    reference is (up to a factor), and close to the bf16 reference itself."""
+    g = load("backbone.npz")
+    data = small_batch([6000, 4000], seed=41)
+    net, _ = _small_net(torch.bfloat16)
+    with torch.inference_mode():
+        torch.manual_seed(1)
+        out = net(cuda_data(data, torch.bfloat16)).feat
+    ref32 = torch.from_numpy(g["fp32"])
+    ref16 = from_bf16_bits(g["bf16"]).float()
+    floor = rel_l2(ref16, ref32)
+    assert rel_l2(out, ref32) <= 1.5 * floor + 1e-3, (rel_l2(out, ref32), floor)
+    assert rel_l2(out, ref16) <= 2.0 * floor + 1e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_block_vs_oracle(dtype):
+    """One Block (xCPE + attention + MLP) on identical inputs against the oracle."""
+    data = small_batch([5000, 2000], seed=51)
+    C, H, K = 64, 4, 1024
+    blk = P.Block(C, H, K, order_index=2, cpe_indice_key="s", enable_flash=False, upcast_attention=False,
+                  upcast_softmax=False).eval()
+    sd = weights.fill_state_dict(blk, prefix="blk.")
+    sd = {("b." + k): v.to(dtype) for k, v in sd.items()}
+    pt = P.Point(cuda_data(data))
+    pt.serialization(order=ORDERS, shuffle_orders=False)
+    n = pt.batch.shape[0]
+    feat = weights.keyed_tensor("blk.feat", (n, C)).to(dtype)
+    pt.feat = feat.cuda()
+    pt.sparsify()
+    with torch.inference_mode():
+        got = blk.cuda().to(dtype)(pt).feat
+    batch = O.offset_to_batch(data["offset"])
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ORDERS)
+    lv = O.Level(coord=data["coord"], grid_coord=data["grid_coord"], batch=batch, offset=data["offset"],
+                 code=code, order=order, inverse=inverse, depth=depth, cluster=None, parent=None)
+    ref = O.block(sd, "b.", lv, feat, H, K, 2)
+    if dtype == torch.float32:
+        assert_close(got, ref, atol=2e-4, rtol=2e-4, what="block fp32")
+    else:
+        ref32 = O.block({k: v.float() for k, v in sd.items()}, "b.", lv, feat.float(), H, K, 2)
+        assert rel_l2(got, ref32) <= 1.5 * rel_l2(ref, ref32) + 1e-3
+        assert_close(got, ref, atol=6e-2, rtol=3e-2, what="block bf16")
+
+
+def test_flash_flag_uses_full_patch_and_short_sequences():
+    """enable_flash=True keeps patch = patch_size; scenes shorter than the patch
+    become one short sequence (model.py:394-404, :476-483)."""
+    data = small_batch([900, 300], seed=61)
+    C, H, K = 32, 2, 256
+    att = P.SerializedAttention(C, H, K, enable_flash=True, upcast_attention=False, upcast_softmax=False).eval()
+    sd = weights.fill_state_dict(att, prefix="fl.")
+    pt = P.Point(cuda_data(data))
+    pt.serialization(order=["z"], shuffle_orders=False)
+    n = pt.batch.shape[0]
+    feat = weights.keyed_tensor("fl.feat", (n, C))
+    pt.feat = feat.cuda()
+    with torch.inference_mode():
+        got = att.cuda()(pt).feat.cpu()
+    # oracle: varlen attention written directly from the padded layout
+    counts = O.offset_to_counts(data["offset"]).tolist()
+    pad, unpad, cu = O.pad_plan(data["offset"], K)
+    order, inverse = pt.serialized_order[0].cpu(), pt.serialized_inverse[0].cpu()
+    qkv = torch.nn.functional.linear(feat, sd["qkv.weight"], sd["qkv.bias"])[order[pad]]
+    outp = torch.empty(qkv.shape[0], C)
+    for s in range(len(cu) - 1):
+        a, b = int(cu[s]), int(cu[s + 1])
+        q, k, v = qkv[a:b].reshape(b - a, 3, H, C // H).permute(1, 2, 0, 3)
+        w = torch.softmax((q * (C // H) ** -0.5) @ k.transpose(-1, -2), -1)
+        outp[a:b] = (w @ v).transpose(0, 1).reshape(b - a, C)
+    ref = torch.nn.functional.linear(outp[unpad[inverse]], sd["proj.weight"], sd["proj.bias"])
+    assert_close(got, ref, what="varlen attention", **TOL[torch.float32])
