@@ -1,0 +1,288 @@
+#!/usr/bin/env python
+"""Throughput of the Point Transformer V3 forward pass (points per second).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload per GPU: the default backbone, random init, eval, bf16, on a batch of
+four synthetic indoor scenes of about 100k voxels each (grid 0.02 m).  With N
+GPUs every rank runs its own four scenes (weak scaling) and the output features
+are all-gathered over NCCL at the end of every step.  One JSON line is printed
+by rank 0.
+
+`--impl reference` times the CPU restatement of the reference path (the oracle)
+on the host cores, on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "ptv3_forward_points_per_sec"
+UNIT = "points/s"
+SCENES_PER_GPU = 4
+TARGET_VOXELS = 100_000
+GRID = 0.02
+CPU_SAMPLE_VOXELS = 100_000
+
+
+def workload_config(n_gpus):
+    return {"workload": "full PTv3 backbone forward, default config, bf16 eval, random init; "
+                        "%d synthetic indoor scenes of ~100k voxels per GPU, grid 0.02" % SCENES_PER_GPU,
+            "scenes_per_gpu": SCENES_PER_GPU, "parallelism": "scene-parallel x%d, outputs all-gathered" % n_gpus,
+            "l2": "256 MiB buffer written between timed steps (outside the per-step events)"}
+
+
+# --------------------------------------------------------------------------- #
+# clocks
+# --------------------------------------------------------------------------- #
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc = [], None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(index), "--query-gpu=" + self.FIELDS,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for t, r in self.rows if t0 <= t <= t1 and len(r) >= 6] or \
+               [r for _, r in self.rows if len(r) >= 6]
+        if not rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(r[2 + i] == "Active" for r in rows)]
+        return {"sm_mhz": statistics.median(float(r[0]) for r in rows), "sm_max_mhz": float(rows[0][1]),
+                "reasons": reasons, "samples": len(rows)}
+
+
+# --------------------------------------------------------------------------- #
+# CPU arm (oracle port of the reference path)
+# --------------------------------------------------------------------------- #
+def cpu_state_dict(dtype):
+    from pointtransformerv3_b200 import PointTransformerV3
+    torch.manual_seed(0)
+    net = PointTransformerV3(in_channels=6, enable_flash=False).eval()
+    return {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in net.state_dict().items()}
+
+
+def cpu_step_fn():
+    """Returns (callable running one bounded CPU step, points per step, description)."""
+    from oracle import ptv3_oracle as O
+    from pointtransformerv3_b200 import synthetic
+    torch.set_num_threads(os.cpu_count() or 1)
+    data = synthetic.make_batch([synthetic.indoor_scene(0, CPU_SAMPLE_VOXELS, GRID)], 3, 0, torch.bfloat16)
+    sd = cpu_state_dict(torch.bfloat16)
+    n = int(data["offset"][-1])
+
+    def step():
+        with torch.inference_mode():
+            torch.manual_seed(1)
+            return O.ptv3_forward(sd, data)
+    sample = ("CPU restatement of the reference forward (bf16, enable_flash=False) on one indoor scene "
+              "of %d voxels from the same generator; points/s = voxels / time" % n)
+    return step, n, sample
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    step, n, sample = cpu_step_fn()
+    for _ in range(max(args.warmup, 1) if args.warmup else 0):
+        step()
+    t = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        step()
+        t.append(time.perf_counter() - t0)
+    per = sum(t) / len(t)
+    v = n / per
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# --------------------------------------------------------------------------- #
+# GPU arm
+# --------------------------------------------------------------------------- #
+def run_ours(args):
+    import torch.distributed as dist
+    from pointtransformerv3_b200 import PointTransformerV3, _lib, distributed, ops, synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (this library has no CPU path)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+
+    data = synthetic.indoor_batch(SCENES_PER_GPU, first_seed=rank * SCENES_PER_GPU,
+                                  target_voxels=TARGET_VOXELS, grid_size=GRID, dtype=torch.bfloat16)
+    n_points = int(data["offset"][-1])
+    torch.manual_seed(0)
+    net = PointTransformerV3(in_channels=6).eval().to(dev).bfloat16()
+    host = {k: v.pin_memory() for k, v in data.items()}
+    resident = {k: v.to(dev) for k, v in data.items()}
+    out_host = torch.empty((n_points, 64), dtype=torch.bfloat16).pin_memory()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    h2d = sum(v.numel() * v.element_size() for v in host.values())
+    d2h = out_host.numel() * out_host.element_size()
+
+    def forward(d):
+        torch.manual_seed(1)          # fixes the order-shuffle draws of every step
+        with torch.inference_mode():
+            feat = net(dict(d)).feat
+            if world > 1:
+                feat, _ = distributed.gather_features(feat)
+        return feat
+
+    def step_resident():
+        return forward(resident)
+
+    def step_e2e():
+        d = {k: v.to(dev, non_blocking=True) for k, v in host.items()}
+        with torch.inference_mode():
+            torch.manual_seed(1)
+            feat = net(d).feat
+            out_host.copy_(feat, non_blocking=True)
+            if world > 1:
+                distributed.gather_features(feat)
+        torch.cuda.current_stream().synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+              for _ in range(steps)]
+        barrier()
+        t0 = time.time()
+        for a, b in ev:
+            flush.fill_(1)
+            a.record()
+            fn()
+            b.record()
+        barrier()
+        t1 = time.time()
+        ms = sum(a.elapsed_time(b) for a, b in ev)
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), t0, t1
+
+    for _ in range(max(args.warmup, 3)):
+        step_resident()
+    sampler = ClockSampler(local) if rank == 0 else None
+    ops.TIMERS = {}
+    launches0 = lib.ptv3_launch_count()
+    ms, t0, t1 = timed(step_resident, args.steps)
+    launches = lib.ptv3_launch_count() - launches0
+    timers = ops.timer_summary()
+    ops.TIMERS = None
+    clocks = sampler.stop(t0, t1) if sampler else None
+
+    for _ in range(2):
+        step_e2e()
+    ms_e2e, _, _ = timed(step_e2e, args.steps)
+
+    total_points = torch.tensor([n_points], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_points)
+    total_points = float(total_points.item())
+
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        att = timers.get("attention", {"calls": 0, "ms": 0.0, "work": 0.0})
+        tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
+        achieved = att["work"] / (att["ms"] * 1e-3) / 1e12 if att["ms"] else 0.0
+        roofline = {"kernel": "attention core (all patch-attention launches of the timed steps)",
+                    "bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
+                    "frac": achieved / tf_peak, "traffic": None,
+                    "peak_source": "measured (sustained)" if peaks else "fallback",
+                    "launches": att["calls"], "avg_launch_ms": att["ms"] / max(att["calls"], 1)}
+        breakdown = {k: {"calls": v["calls"], "ms_per_step": v["ms"] / args.steps} for k, v in timers.items()}
+        line = {
+            "metric": METRIC, "value": total_points * args.steps / (ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": dict(workload_config(world), points_per_gpu=n_points),
+            "clocks": clocks,
+            "e2e": {"value": total_points * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": int(launches),
+            "roofline": roofline,
+            "kernel_ms_per_step": breakdown,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            step, n, sample = cpu_step_fn()
+            step()
+            t = time.perf_counter()
+            step()
+            dt = time.perf_counter() - t
+            line["cpu_baseline"] = {"value": n / dt, "unit": UNIT, "cores": torch.get_num_threads(),
+                                    "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -53,6 +53,8 @@ extern "C" {
 
 const char* ptv3_last_error(void);
 int ptv3_version(void);
+/* kernels launched by this library in this process so far */
+long long ptv3_launch_count(void);
 
 /*
  * Space-filling-curve codes.

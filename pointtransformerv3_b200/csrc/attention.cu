@@ -119,6 +119,7 @@ static int launch_attn_fma(const void* qkv, const int64_t* order, const int64_t*
             return PTV3_ERR_UNSUPPORTED;
     }
 #undef AF_LAUNCH
+    count_launches(1);
     return check_launch("ptv3_attention_fwd");
 }
 

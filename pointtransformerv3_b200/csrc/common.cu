@@ -1,10 +1,15 @@
 #include "common.cuh"
 #include <stdarg.h>
+#include <atomic>
 #include "../../include/ptv3_b200.h"
 
 namespace ptv3 {
 
 static thread_local char g_err[512] = "";
+static std::atomic<long long> g_launches{0};
+
+void count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
 
 void set_error(const char* fmt, ...)
 {
@@ -28,3 +33,4 @@ int check_launch(const char* what)
 
 extern "C" const char* ptv3_last_error(void) { return ptv3::g_err; }
 extern "C" int ptv3_version(void) { return 1; }
+extern "C" long long ptv3_launch_count(void) { return ptv3::launches(); }

@@ -15,6 +15,9 @@ namespace ptv3 {
 
 void set_error(const char* fmt, ...);
 int check_launch(const char* what);
+// Adds to the process-wide count of kernels this library has launched
+// (read through ptv3_launch_count()).
+void count_launches(int n);
 
 #define PTV3_REQUIRE(cond, code, ...)            \
     do {                                         \

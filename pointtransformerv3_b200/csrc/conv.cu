@@ -108,6 +108,7 @@ static int launch_conv_fma(const void* feat, const int32_t* nbr, const void* wei
         conv_fma_kernel<T, 64><<<dim3(gx, (cout + 63) / 64), CF_THREADS, 0, stream>>>(
             (const T*)feat, nbr, (const T*)weight, (const T*)bias, (T*)out, n, cin, cout, kvol);
     }
+    count_launches(1);
     return check_launch("ptv3_subm_conv_fwd");
 }
 

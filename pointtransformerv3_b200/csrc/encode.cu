@@ -71,5 +71,6 @@ extern "C" int ptv3_encode(const int32_t* grid_coord, const int64_t* batch, int6
     if (blocks > 148 * 16) blocks = 148 * 16;
     encode_kernel<<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(grid_coord, batch, n, depth,
                                                                            ol, codes);
+    count_launches(1);
     return check_launch("ptv3_encode");
 }

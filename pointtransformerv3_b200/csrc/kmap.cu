@@ -132,5 +132,6 @@ extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int
     km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
     km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(
         indices, n, ksize, keys, vals, cap - 1, nbr, status);
+    count_launches(2);
     return check_launch("ptv3_kmap_build");
 }

@@ -197,6 +197,7 @@ extern "C" int ptv3_pad_plan(const int64_t* offset, int n_scenes, int patch, int
     const size_t smem = 3 * (size_t)(n_scenes + 1) * sizeof(int64_t);
     pad_plan_kernel<<<(unsigned)blocks, 256, smem, (cudaStream_t)stream>>>(
         offset, n_scenes, patch, n, n_pad, n_seq, pad, unpad, cu_seqlens, status);
+    count_launches(1);
     return check_launch("ptv3_pad_plan");
 }
 
@@ -257,5 +258,6 @@ extern "C" int ptv3_pool_plan(const int64_t* code, const int64_t* order, const i
     scan_sums_kernel<<<k, SC_THREADS, 0, stream>>>(ts2, w.ntiles, totals + 1);
     scan_apply_kernel<<<dim3(w.ntiles, k), SC_THREADS, 0, stream>>>(of, os, n, w.ntiles, ts2);
     pool_meta_kernel<<<1, 32, 0, stream>>>(totals, k, n, n_scenes, scene_count, idx_ptr, meta, status);
+    count_launches(7);
     return check_launch("ptv3_pool_plan");
 }

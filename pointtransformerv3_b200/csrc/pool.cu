@@ -173,6 +173,7 @@ extern "C" int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* i
     if (coord && coord_out)
         pool_coord_mean_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(coord, indices, idx_ptr,
                                                                                m, coord_out);
+    count_launches((coord && coord_out) ? 2 : 1);
     return check_launch("ptv3_pool_fwd");
 }
 
@@ -202,5 +203,6 @@ extern "C" int ptv3_unpool_fwd(const void* skip, const void* child, const int64_
         unpool_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
             (const __nv_bfloat16*)skip, (const __nv_bfloat16*)child, cluster, n, channels, skip_scale,
             skip_shift, child_scale, child_shift, (__nv_bfloat16*)out, (__nv_bfloat16*)skip_act);
+    count_launches(1);
     return check_launch("ptv3_unpool_fwd");
 }

@@ -240,5 +240,6 @@ extern "C" int ptv3_argsort_inverse(const int64_t* codes, int k, int64_t n, int 
         vin = vout;
         cur ^= 1;
     }
+    count_launches(3 * p.passes);
     return check_launch("ptv3_argsort_inverse");
 }

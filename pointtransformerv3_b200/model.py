@@ -445,9 +445,14 @@ class PointTransformerV3(PointModule):
 
     def forward(self, data_dict):
         """data_dict: ``feat``, ``grid_coord`` (or ``coord`` + ``grid_size``) and
-        ``offset`` or ``batch``; returns the Point of the finest level."""
+        ``offset`` or ``batch``; returns the Point of the finest level.
+
+        Extension: an optional ``serialization_depth`` entry fixes the depth of
+        the codes instead of deriving it from this batch's largest coordinate
+        (needed when one logical batch is split over several processes)."""
         point = Point(data_dict)
-        point.serialization(order=self.order, shuffle_orders=self.shuffle_orders)
+        depth = point.pop("serialization_depth", None)
+        point.serialization(order=self.order, depth=depth, shuffle_orders=self.shuffle_orders)
         point.sparsify()
         point = self.embedding(point)
         point = self.enc(point)

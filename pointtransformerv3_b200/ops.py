@@ -10,6 +10,39 @@ from . import _lib
 
 ORDER_IDS = {"z": 0, "z-trans": 1, "hilbert": 2, "hilbert-trans": 3}
 
+# Optional per-operator device timing: when TIMERS is a dict, every wrapped call
+# records a CUDA event pair on the current stream under the operator's name,
+# together with the `work` figure (algorithmic FLOPs or bytes) of the call.
+TIMERS = None
+
+
+class timed:
+    def __init__(self, name, work=0.0):
+        self.name, self.work = name, work
+
+    def __enter__(self):
+        if TIMERS is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+        return self
+
+    def __exit__(self, *exc):
+        if TIMERS is not None:
+            self.end.record()
+            TIMERS.setdefault(self.name, []).append((self.start, self.end, self.work))
+        return False
+
+
+def timer_summary():
+    """name -> dict(calls, ms, work) from the recorded events (synchronises)."""
+    torch.cuda.synchronize()
+    out = {}
+    for name, evs in (TIMERS or {}).items():
+        out[name] = dict(calls=len(evs), ms=sum(a.elapsed_time(b) for a, b, _ in evs),
+                         work=sum(w for _, _, w in evs))
+    return out
+
 
 def encode(grid_coord, batch, depth, orders):
     """grid_coord (N,3) integer CUDA tensor, batch (N,) or None, orders: list of
@@ -27,8 +60,9 @@ def encode(grid_coord, batch, depth, orders):
             raise ValueError("batch must be (N,)")
     ids = (ctypes.c_int * len(orders))(*[ORDER_IDS[o] for o in orders])
     codes = torch.empty((len(orders), n), dtype=torch.int64, device=g.device)
-    _lib.check(lib.ptv3_encode(_lib.ptr(g), _lib.ptr(b), n, int(depth), ids, len(orders),
-                               _lib.ptr(codes), _lib.stream()), "ptv3_encode")
+    with timed("encode", n * (12.0 + (8.0 if b is not None else 0.0) + 8.0 * len(orders))):
+        _lib.check(lib.ptv3_encode(_lib.ptr(g), _lib.ptr(b), n, int(depth), ids, len(orders),
+                                   _lib.ptr(codes), _lib.stream()), "ptv3_encode")
     return codes
 
 
@@ -42,9 +76,10 @@ def argsort_inverse(codes, sig_bits):
     inverse = torch.empty_like(codes)
     nbytes = lib.ptv3_argsort_workspace_bytes(k, n, int(sig_bits))
     ws = _lib.workspace(nbytes, codes.device)
-    _lib.check(lib.ptv3_argsort_inverse(_lib.ptr(codes), k, n, int(sig_bits), _lib.ptr(order),
-                                        _lib.ptr(inverse), _lib.ptr(ws), nbytes, _lib.stream()),
-               "ptv3_argsort_inverse")
+    with timed("argsort_inverse", 24.0 * k * n):
+        _lib.check(lib.ptv3_argsort_inverse(_lib.ptr(codes), k, n, int(sig_bits), _lib.ptr(order),
+                                            _lib.ptr(inverse), _lib.ptr(ws), nbytes, _lib.stream()),
+                   "ptv3_argsort_inverse")
     return order, inverse
 
 
@@ -92,11 +127,13 @@ def attention(qkv, order_row, pad, unpad, cu_seqlens, heads, max_seqlen, scale, 
     n, c3 = qkv.shape
     C = c3 // 3
     out = torch.empty((n, C), dtype=qkv.dtype, device=qkv.device)
-    _lib.check(lib.ptv3_attention_fwd(_lib.ptr(qkv), _lib.ptr(order_row.contiguous()), _lib.ptr(pad),
-                                      _lib.ptr(unpad), _lib.ptr(cu_seqlens), _lib.ptr(out), n,
-                                      cu_seqlens.numel() - 1, int(max_seqlen), C, int(heads),
-                                      float(scale), _lib.dtype_id(qkv), int(algo), _lib.stream()),
-               "ptv3_attention_fwd")
+    # algorithmic work: QK^T and PV over every padded row against its whole patch
+    with timed("attention", 4.0 * pad.numel() * max_seqlen * C):
+        _lib.check(lib.ptv3_attention_fwd(_lib.ptr(qkv), _lib.ptr(order_row.contiguous()), _lib.ptr(pad),
+                                          _lib.ptr(unpad), _lib.ptr(cu_seqlens), _lib.ptr(out), n,
+                                          cu_seqlens.numel() - 1, int(max_seqlen), C, int(heads),
+                                          float(scale), _lib.dtype_id(qkv), int(algo), _lib.stream()),
+                   "ptv3_attention_fwd")
     return out
 
 
@@ -112,8 +149,9 @@ def kmap_build(indices, ksize, status=None):
     own = status is None
     if own:
         status = new_status(indices.device)
-    _lib.check(lib.ptv3_kmap_build(_lib.ptr(indices), n, int(ksize), _lib.ptr(nbr), _lib.ptr(status),
-                                   _lib.ptr(ws), nbytes, _lib.stream()), "ptv3_kmap_build")
+    with timed("kmap_k%d" % ksize, n * (16.0 + 4.0 * ksize ** 3)):
+        _lib.check(lib.ptv3_kmap_build(_lib.ptr(indices), n, int(ksize), _lib.ptr(nbr), _lib.ptr(status),
+                                       _lib.ptr(ws), nbytes, _lib.stream()), "ptv3_kmap_build")
     if own:
         _lib.raise_on_status(status, "ptv3_kmap_build")
     return nbr
@@ -133,10 +171,11 @@ def subm_conv(feat, nbr, weight, bias=None, algo=0):
     if bias is not None and bias.dtype != feat.dtype:
         raise ValueError("bias dtype %s != feature dtype %s" % (bias.dtype, feat.dtype))
     out = torch.empty((n, cout), dtype=feat.dtype, device=feat.device)
-    _lib.check(lib.ptv3_subm_conv_fwd(_lib.ptr(feat), _lib.ptr(nbr), _lib.ptr(weight.contiguous()),
-                                      _lib.ptr(bias), _lib.ptr(out), n, cin, cout, kvol,
-                                      _lib.dtype_id(feat), int(algo), _lib.stream()),
-               "ptv3_subm_conv_fwd")
+    with timed("subm_conv_k%d" % round(kvol ** (1 / 3)), 2.0 * n * kvol * cin * cout):
+        _lib.check(lib.ptv3_subm_conv_fwd(_lib.ptr(feat), _lib.ptr(nbr), _lib.ptr(weight.contiguous()),
+                                          _lib.ptr(bias), _lib.ptr(out), n, cin, cout, kvol,
+                                          _lib.dtype_id(feat), int(algo), _lib.stream()),
+                   "ptv3_subm_conv_fwd")
     return out
 
 
