@@ -130,6 +130,31 @@ int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int32_t* nbr, 
                     void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * ptv3_kmap_build for callers that cannot hand over a workspace because they
+ * cannot allocate device memory at the point of the call: a plugin running
+ * inside a host framework that owns the whole device heap, or a latency-bound
+ * service loop where cudaMalloc (a device-wide synchronisation) is forbidden
+ * after start-up.  This entry point has no counterpart in the reference.
+ * The hash table lives in a static device array of the library (1.5 MiB on
+ * every GPU that loads it, until the process exits), so
+ *   - n is limited to ptv3_kmap_static_max_voxels() (65536); larger inputs are
+ *     rejected with PTV3_ERR_UNSUPPORTED and the caller should fall back to
+ *     ptv3_kmap_build
+ *   - nothing is allocated or freed, here or in any library it calls
+ *   - the first call on each device resolves the array's device address; make
+ *     that first call outside any stream capture
+ *   - all calls on a device share the one table (it is re-initialised at the
+ *     start of each call, in stream order): two calls whose kernels may overlap
+ *     on the GPU (different streams or threads) race and must be serialised by
+ *     the caller
+ * Inputs, outputs and `status` are as for ptv3_kmap_build and are still
+ * provided by the caller.
+ */
+int64_t ptv3_kmap_static_max_voxels(void);
+int ptv3_kmap_build_static(const int32_t* indices, int64_t n, int ksize, int32_t* nbr,
+                           uint32_t* status, void* stream);
+
+/*
  * Submanifold convolution over a kernel map:
  *   out[i] = bias + sum_o weight[:, o, :] . feat[nbr[o][i]]
  * Replaces spconv.SubMConv3d.forward at model.py:546-552 and :767-774.

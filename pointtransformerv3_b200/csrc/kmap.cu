@@ -135,3 +135,85 @@ extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int
     count_launches(2);
     return check_launch("ptv3_kmap_build");
 }
+
+// ----------------------------------------------------------------------------
+// Kernel map without any caller-provided or allocated scratch memory.
+// ----------------------------------------------------------------------------
+namespace ptv3 {
+
+// Largest voxel count the static table serves, and the table itself: 131072
+// slots of an 8-byte key plus a 4-byte row index (1.5 MiB per GPU that loads
+// the library, held until the process exits).
+constexpr int64_t KM_STATIC_MAX_VOXELS = 65536;
+constexpr uint64_t KM_STATIC_SLOTS = 131072;
+constexpr size_t KM_STATIC_KEY_BYTES = KM_STATIC_SLOTS * sizeof(uint64_t);
+constexpr size_t KM_STATIC_BYTES = KM_STATIC_KEY_BYTES + KM_STATIC_SLOTS * sizeof(uint32_t);
+static __device__ __align__(256) unsigned char g_kmap_static_scratch[KM_STATIC_BYTES];
+
+constexpr int KM_MAX_DEVICES = 64;
+// device address of the static table on each device, resolved on first use there
+static void* g_kmap_static_ptr[KM_MAX_DEVICES] = {nullptr};
+
+// In host code `g_kmap_static_scratch` is only a handle for the runtime, not an
+// address a kernel could use, so the device address is looked up once per
+// device (with that device current) and handed to the kernels as a pointer.
+static int km_static_table(void** out)
+{
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= KM_MAX_DEVICES) {
+        set_error("ptv3_kmap_build_static: cannot identify the current device (%s)",
+                  e != cudaSuccess ? cudaGetErrorString(e) : "index out of range");
+        return PTV3_ERR_CUDA;
+    }
+    if (g_kmap_static_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_kmap_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            set_error("ptv3_kmap_build_static: cudaGetSymbolAddress failed on device %d (%s)", dev,
+                      cudaGetErrorString(e));
+            return PTV3_ERR_CUDA;
+        }
+        g_kmap_static_ptr[dev] = p;
+    }
+    *out = g_kmap_static_ptr[dev];
+    return PTV3_OK;
+}
+
+}  // namespace ptv3
+
+extern "C" int64_t ptv3_kmap_static_max_voxels(void) { return ptv3::KM_STATIC_MAX_VOXELS; }
+
+extern "C" int ptv3_kmap_build_static(const int32_t* indices, int64_t n, int ksize, int32_t* nbr,
+                                      uint32_t* status, void* stream_)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0, PTV3_ERR_INVALID_ARGUMENT, "ptv3_kmap_build_static: bad n");
+    PTV3_REQUIRE(n <= KM_STATIC_MAX_VOXELS, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_kmap_build_static: %lld voxels exceed the static table's limit of %lld; use "
+                 "ptv3_kmap_build with a workspace",
+                 (long long)n, (long long)KM_STATIC_MAX_VOXELS);
+    PTV3_REQUIRE(ksize == 1 || ksize == 3 || ksize == 5 || ksize == 7, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_kmap_build_static: kernel size %d (supported: 1, 3, 5, 7)", ksize);
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(indices && nbr && status, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_kmap_build_static: null pointer");
+    PTV3_REQUIRE(((uintptr_t)indices & 15) == 0, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_kmap_build_static: indices must be 16-byte aligned");
+    void* table = nullptr;
+    const int rc = km_static_table(&table);
+    if (rc != PTV3_OK) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    unsigned long long* keys = reinterpret_cast<unsigned long long*>(table);
+    uint32_t* vals = reinterpret_cast<uint32_t*>(static_cast<char*>(table) + KM_STATIC_KEY_BYTES);
+    // the table still holds the previous call's entries: reset exactly the slots this call uses
+    const uint64_t cap = km_capacity(n);   // <= KM_STATIC_SLOTS because n <= KM_STATIC_MAX_VOXELS
+    cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
+    cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream);
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
+    km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(
+        indices, n, ksize, keys, vals, cap - 1, nbr, status);
+    count_launches(2);
+    return check_launch("ptv3_kmap_build_static");
+}
