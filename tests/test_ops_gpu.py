@@ -169,3 +169,48 @@ def test_pool_and_unpool_features(dtype):
     out, act = ops.unpool(x.cuda(), child.cuda(), plan["cluster"].cuda(), scale, shift, scale, shift)
     assert_close(out, ref_u, what="unpool", **TOL[dtype])
     assert_close(act, ref_b, what="unpool skip", **TOL[dtype])
+
+
+@pytest.mark.parametrize("sizes,C,H,K", [([3000], 64, 4, 1024), ([1100, 90, 2049], 32, 2, 1024),
+                                         ([5000], 128, 8, 2048), ([777], 16, 1, 100)])
+def test_attention_tensor_core_path_matches_cuda_core_path(sizes, C, H, K):
+    """Same inputs through both kernels (algo 2 vs algo 1), bf16."""
+    data = small_batch(sizes, 7)
+    offset = data["offset"]
+    counts = O.offset_to_counts(offset).tolist()
+    batch = O.offset_to_batch(offset)
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ["z-trans"])
+    g = torch.Generator().manual_seed(1)
+    qkv = (torch.randn(batch.shape[0], 3 * C, generator=g) * 1.5).bfloat16().cuda()
+    Ke = min(min(counts), K)
+    pad, unpad, cu = ops.pad_plan(offset.cuda(), counts, Ke)
+    a = ops.attention(qkv, order[0].cuda(), pad, unpad, cu, H, Ke, (C // H) ** -0.5, algo=1)
+    b = ops.attention(qkv, order[0].cuda(), pad, unpad, cu, H, Ke, (C // H) ** -0.5, algo=2)
+    assert_close(b, a, atol=1e-2, rtol=1e-2, what="tensor-core vs CUDA-core attention")
+    assert rel_l2(b, a) < 5e-3
+
+
+def test_attention_config2_size_bf16():
+    """N = 120 000, C = 64, 4 heads, patch 1024 (118 patches, the last one padded by
+    borrowing): tensor-core path against the fp32 oracle on a row sample."""
+    n, C, H, K = 120_000, 64, 4, 1024
+    g = torch.Generator().manual_seed(0)
+    grid = torch.randint(0, 512, (n, 3), generator=g, dtype=torch.int32)
+    batch = torch.zeros(n, dtype=torch.int64)
+    offset = torch.tensor([n])
+    code, order, inverse, depth = O.serialization(grid, batch, ["hilbert"])
+    qkv = torch.randn(n, 3 * C, generator=g)
+    pad, unpad, cu = ops.pad_plan(offset.cuda(), [n], K)
+    assert pad.numel() == 120_832 and cu.numel() == 119
+    got = ops.attention(qkv.bfloat16().cuda(), order[0].cuda(), pad, unpad, cu, H, K, 0.25, algo=2).float().cpu()
+    # oracle for the first, a middle and the (borrowing) last patch
+    rp, ru, rc = O.pad_plan(offset, K)
+    x = qkv.bfloat16().float()
+    for patch in (0, 57, 117):
+        rows = order[0][rp[patch * K:(patch + 1) * K]]
+        q, k, v = x[rows].reshape(K, 3, H, 16).permute(1, 2, 0, 3)
+        w = torch.softmax((q * 0.25) @ k.transpose(-1, -2), -1)
+        ref = (w @ v).transpose(0, 1).reshape(K, C)
+        own = ru[inverse[0][rows]] == torch.arange(patch * K, (patch + 1) * K)
+        assert_close(got[rows[own]], ref[own], atol=2e-2, rtol=1e-2, what="patch %d" % patch)
+        assert rel_l2(got[rows[own]], ref[own]) < 1e-2
