@@ -160,11 +160,16 @@ int ptv3_kmap_build_static(const int32_t* indices, int64_t n, int ksize, int32_t
  * Replaces spconv.SubMConv3d.forward at model.py:546-552 and :767-774.
  *   weight      c_out x kernel_volume x c_in (the [C_out, k, k, k, C_in] layout)
  *   bias        c_out or NULL
+ *   row_order   n int64 permutation of the voxels or NULL: the order in which
+ *               voxels are grouped into tiles (a serialized order makes a tile
+ *               spatially compact).  When given, column j of nbr must describe
+ *               voxel row_order[j], i.e. nbr = kernel_map[:, row_order]; the
+ *               result is the same as without it
  *   algo        0 = automatic, 1 = CUDA-core path, 2 = tensor-core path
  */
 int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight, const void* bias,
-                       void* out, int64_t n, int c_in, int c_out, int kernel_volume, int dtype,
-                       int algo, void* stream);
+                       void* out, const int64_t* row_order, int64_t n, int c_in, int c_out,
+                       int kernel_volume, int dtype, int algo, void* stream);
 
 /*
  * Cluster and order bookkeeping of serialized pooling.

@@ -17,6 +17,7 @@
 // at head_dim 16 the exp unit, not the tensor pipe, is the limiter.
 #include "common.cuh"
 #include "attention_mma.cuh"
+#include "mma_util.cuh"
 
 namespace ptv3 {
 
@@ -26,11 +27,6 @@ constexpr int AM_KC = 64;           // keys per online-softmax step
 constexpr int AM_D = 16;
 constexpr float AM_LOG2E = 1.4426950408889634f;
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p)
-{
-    return (uint32_t)__cvta_generic_to_shared(p);
-}
-
 // byte offset of 16-byte chunk c (0/1) of row r in a [rows][16] bf16 tile whose
 // chunks are swapped in rows 4..7 (mod 8) so that 8-row ldmatrix reads hit 32
 // distinct banks
@@ -39,51 +35,10 @@ __device__ __forceinline__ uint32_t kv_offset(int r, int c)
     return (uint32_t)(r * 32 + ((c ^ ((r >> 2) & 1)) << 4));
 }
 
-__device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(saddr), "l"(gptr));
-}
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t saddr)
-{
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(saddr));
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t saddr)
-{
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-                 : "r"(saddr));
-}
-
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1)
-{
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-        "{%0,%1,%2,%3};\n"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi)
-{
-    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
-
 __device__ __forceinline__ uint32_t scale_bf16x2(uint32_t v, float s)
 {
     const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
     return pack_bf16(f.x * s, f.y * s);
-}
-
-__device__ __forceinline__ float fast_exp2(float x)
-{
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
-    return y;
 }
 
 __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
@@ -128,8 +83,8 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
             *reinterpret_cast<uint4*>(Vs + kv_offset(r, 1)) = z;
         }
     }
-    asm volatile("cp.async.commit_group;\n" ::);
-    asm volatile("cp.async.wait_group 0;\n" ::);
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
 
     const int g = lane >> 2, t = lane & 3;

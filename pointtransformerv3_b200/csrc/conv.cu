@@ -9,6 +9,7 @@
 // and gathers the input rows of each remaining offset into shared memory.
 #include "common.cuh"
 #include "convert.cuh"
+#include "conv_mma.cuh"
 #include "../../include/ptv3_b200.h"
 
 namespace ptv3 {
@@ -20,7 +21,8 @@ constexpr int CF_THREADS = 256;
 template <typename T, int TN>
 __global__ void __launch_bounds__(CF_THREADS) conv_fma_kernel(
     const T* __restrict__ feat, const int32_t* __restrict__ nbr, const T* __restrict__ weight,
-    const T* __restrict__ bias, T* __restrict__ out, int64_t n, int cin, int cout, int kvol)
+    const T* __restrict__ bias, T* __restrict__ out, const int64_t* __restrict__ row_order, int64_t n,
+    int cin, int cout, int kvol)
 {
     constexpr int CN = TN / 16;  // output columns per thread
     __shared__ float As[CF_TK][CF_TM + 4];
@@ -83,8 +85,9 @@ __global__ void __launch_bounds__(CF_THREADS) conv_fma_kernel(
     }
 #pragma unroll
     for (int x = 0; x < 4; ++x) {
-        const int64_t i = row0 + ty * 4 + x;
+        int64_t i = row0 + ty * 4 + x;
         if (i >= n) continue;
+        if (row_order) i = row_order[i];
 #pragma unroll
         for (int y = 0; y < CN; ++y) {
             const int c = col0 + tx * CN + y;
@@ -98,15 +101,16 @@ __global__ void __launch_bounds__(CF_THREADS) conv_fma_kernel(
 
 template <typename T>
 static int launch_conv_fma(const void* feat, const int32_t* nbr, const void* weight, const void* bias,
-                           void* out, int64_t n, int cin, int cout, int kvol, cudaStream_t stream)
+                           void* out, const int64_t* row_order, int64_t n, int cin, int cout, int kvol,
+                           cudaStream_t stream)
 {
     const unsigned gx = (unsigned)((n + CF_TM - 1) / CF_TM);
     if (cout <= 32) {
         conv_fma_kernel<T, 32><<<dim3(gx, (cout + 31) / 32), CF_THREADS, 0, stream>>>(
-            (const T*)feat, nbr, (const T*)weight, (const T*)bias, (T*)out, n, cin, cout, kvol);
+            (const T*)feat, nbr, (const T*)weight, (const T*)bias, (T*)out, row_order, n, cin, cout, kvol);
     } else {
         conv_fma_kernel<T, 64><<<dim3(gx, (cout + 63) / 64), CF_THREADS, 0, stream>>>(
-            (const T*)feat, nbr, (const T*)weight, (const T*)bias, (T*)out, n, cin, cout, kvol);
+            (const T*)feat, nbr, (const T*)weight, (const T*)bias, (T*)out, row_order, n, cin, cout, kvol);
     }
     count_launches(1);
     return check_launch("ptv3_subm_conv_fwd");
@@ -115,8 +119,9 @@ static int launch_conv_fma(const void* feat, const int32_t* nbr, const void* wei
 }  // namespace ptv3
 
 extern "C" int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight,
-                                  const void* bias, void* out, int64_t n, int c_in, int c_out,
-                                  int kernel_volume, int dtype, int algo, void* stream)
+                                  const void* bias, void* out, const int64_t* row_order, int64_t n,
+                                  int c_in, int c_out, int kernel_volume, int dtype, int algo,
+                                  void* stream)
 {
     using namespace ptv3;
     PTV3_REQUIRE(n >= 0 && c_in >= 1 && c_out >= 1 && kernel_volume >= 1, PTV3_ERR_INVALID_ARGUMENT,
@@ -126,10 +131,19 @@ extern "C" int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const vo
     if (n == 0) return PTV3_OK;
     PTV3_REQUIRE(feat && nbr && weight && out, PTV3_ERR_INVALID_ARGUMENT,
                  "ptv3_subm_conv_fwd: null pointer");
-    (void)algo;
+    PTV3_REQUIRE(algo >= 0 && algo <= 2, PTV3_ERR_INVALID_ARGUMENT, "ptv3_subm_conv_fwd: algo %d", algo);
+    const bool mma_ok = dtype == PTV3_DTYPE_BF16 && conv_mma_supported(c_in, c_out, kernel_volume) &&
+                        ((uintptr_t)feat & 15) == 0 && ((uintptr_t)weight & 15) == 0 &&
+                        ((uintptr_t)out & 3) == 0;
+    PTV3_REQUIRE(algo != 2 || mma_ok, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_subm_conv_fwd: the tensor-core path needs bf16, <= 27 offsets, channels 32->32 or "
+                 "C_in %% 64 == 0 with C_out 64 or a multiple of 128, and 16-byte aligned tensors");
+    if (mma_ok && algo != 1)
+        return launch_conv_mma(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kernel_volume,
+                               (cudaStream_t)stream);
     if (dtype == PTV3_DTYPE_F32)
-        return launch_conv_fma<float>(feat, nbr, weight, bias, out, n, c_in, c_out, kernel_volume,
-                                      (cudaStream_t)stream);
-    return launch_conv_fma<__nv_bfloat16>(feat, nbr, weight, bias, out, n, c_in, c_out, kernel_volume,
-                                          (cudaStream_t)stream);
+        return launch_conv_fma<float>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out,
+                                      kernel_volume, (cudaStream_t)stream);
+    return launch_conv_fma<__nv_bfloat16>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out,
+                                          kernel_volume, (cudaStream_t)stream);
 }

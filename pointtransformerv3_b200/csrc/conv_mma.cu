@@ -1,0 +1,228 @@
+// Tensor-core path of the submanifold convolution for bf16 features:
+// an implicit GEMM, output-stationary over tiles of 128 voxels.
+//
+// For its tile a CTA first stages the 27 x 128 neighbour rows in shared memory
+// and drops the offsets for which no voxel of the tile has a neighbour.  For
+// each remaining offset o and each 32/64-wide slice of the input channels it
+// gathers the neighbour rows (zero rows where there is none) and the matching
+// slice of W[:, o, :] with cp.async into a double-buffered, bank-swizzled
+// shared-memory stage, and accumulates out_tile += A_o . W_o^T with mma.sync
+// (bf16 operands, fp32 accumulators in registers).  Bias is added in the
+// epilogue.  An optional voxel permutation lets tiles follow a space-filling
+// curve, which makes most offsets of a tile empty on surface-like data.
+//
+// Replaces spconv.SubMConv3d.forward at model.py:546-552 for bf16.
+// Useful work: 2 . pairs . C_in . C_out FLOP.
+#include "common.cuh"
+#include "conv_mma.cuh"
+#include "mma_util.cuh"
+
+namespace ptv3 {
+
+constexpr int CM_THREADS = 256;
+constexpr int CM_TM = 128;
+constexpr int CM_MAX_KVOL = 27;
+
+// physical 16-byte chunk of logical chunk c in row r for rows of NCH chunks
+template <int NCH>
+__device__ __forceinline__ int swz(int r, int c)
+{
+    if (NCH == 8) return c ^ (r & 7);
+    if (NCH == 4) return c ^ ((r >> 1) & 3);
+    return c;
+}
+
+// CN: output channels per CTA; KC: input channels per stage; WM x WN warps
+template <int CN, int KC, int WM, int WN>
+__global__ void __launch_bounds__(CM_THREADS) conv_mma_kernel(
+    const __nv_bfloat16* __restrict__ feat, const int32_t* __restrict__ nbr,
+    const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ bias,
+    __nv_bfloat16* __restrict__ out, const int64_t* __restrict__ row_order, int64_t n, int cin,
+    int cout, int kvol)
+{
+    static_assert(WM * WN == CM_THREADS / 32, "warp layout");
+    constexpr int NCH = KC / 8;              // 16-byte chunks per staged row
+    constexpr int ROWB = KC * 2;             // bytes per staged row
+    constexpr int WTM = CM_TM / WM;          // rows per warp
+    constexpr int WTN = CN / WN;             // cols per warp
+    constexpr int MT = WTM / 16, NT = WTN / 8;
+    static_assert(NT % 2 == 0, "n tiles are loaded in pairs");
+    constexpr int A_BYTES = CM_TM * ROWB, B_BYTES = CN * ROWB;
+
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* As = smem;                          // 2 stages
+    unsigned char* Bs = smem + 2 * A_BYTES;            // 2 stages
+    int32_t* nbr_s = reinterpret_cast<int32_t*>(smem + 2 * A_BYTES + 2 * B_BYTES);   // kvol x 128
+    int* act = reinterpret_cast<int*>(nbr_s + CM_MAX_KVOL * CM_TM);                   // kvol + 1
+    int64_t* rows_s = reinterpret_cast<int64_t*>(act + 32);                          // 128
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int wm = warp % WM, wn = warp / WM;
+    const int64_t row0 = (int64_t)blockIdx.x * CM_TM;
+    const int col0 = blockIdx.y * CN;
+
+    // ---- voxels of this tile and their neighbour rows ----------------------
+    if (tid < CM_TM) {
+        const int64_t i = row0 + tid;
+        rows_s[tid] = i < n ? (row_order ? row_order[i] : i) : -1;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < kvol * CM_TM; idx += CM_THREADS) {
+        const int o = idx / CM_TM, r = idx % CM_TM;
+        nbr_s[idx] = row0 + r < n ? nbr[(int64_t)o * n + row0 + r] : -1;
+    }
+    __syncthreads();
+    // offsets with at least one neighbour in the tile, in ascending order
+    for (int o = warp; o < kvol; o += CM_THREADS / 32) {
+        bool any = false;
+#pragma unroll
+        for (int r = lane; r < CM_TM; r += 32) any |= nbr_s[o * CM_TM + r] >= 0;
+        const unsigned b = __ballot_sync(0xffffffffu, any);
+        if (lane == 0) act[1 + o] = b != 0;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int c = 0;
+        for (int o = 0; o < kvol; ++o)
+            if (act[1 + o]) act[1 + c++] = o;
+        act[0] = c;
+    }
+    __syncthreads();
+    const int n_act = act[0];
+    const int kchunks = cin / KC;
+    const int nit = n_act * kchunks;
+
+    float acc[MT][NT][4];
+#pragma unroll
+    for (int a = 0; a < MT; ++a)
+#pragma unroll
+        for (int b = 0; b < NT; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f;
+
+    auto prefetch = [&](int it, int buf) {
+        const int o = act[1 + it / kchunks];
+        const int kc = (it % kchunks) * KC;
+        const uint32_t a_base = smem_u32(As + buf * A_BYTES);
+        const uint32_t b_base = smem_u32(Bs + buf * B_BYTES);
+        for (int idx = tid; idx < CM_TM * NCH; idx += CM_THREADS) {
+            const int r = idx / NCH, c = idx % NCH;
+            const int32_t src = nbr_s[o * CM_TM + r];
+            const uint32_t dst = a_base + r * ROWB + swz<NCH>(r, c) * 16;
+            if (src >= 0) {
+                cp_async16(dst, feat + (int64_t)src * cin + kc + c * 8);
+            } else {
+                *reinterpret_cast<uint4*>(As + buf * A_BYTES + r * ROWB + swz<NCH>(r, c) * 16) =
+                    make_uint4(0, 0, 0, 0);
+            }
+        }
+        for (int idx = tid; idx < CN * NCH; idx += CM_THREADS) {
+            const int r = idx / NCH, c = idx % NCH;
+            const uint32_t dst = b_base + r * ROWB + swz<NCH>(r, c) * 16;
+            cp_async16(dst, weight + ((int64_t)(col0 + r) * kvol + o) * cin + kc + c * 8);
+        }
+        cp_async_commit();
+    };
+
+    // ldmatrix lane roles
+    const int a_row = (lane & 7) + (((lane >> 3) & 1) << 3), a_ch = lane >> 4;
+    const int b_row = (lane & 7) + ((lane >> 4) << 3), b_ch = (lane >> 3) & 1;
+
+    if (nit > 0) prefetch(0, 0);
+    for (int it = 0; it < nit; ++it) {
+        const int buf = it & 1;
+        if (it + 1 < nit) {
+            prefetch(it + 1, buf ^ 1);
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const uint32_t a_base = smem_u32(As + buf * A_BYTES);
+        const uint32_t b_base = smem_u32(Bs + buf * B_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < KC / 16; ++ks) {
+            uint32_t af[MT][4];
+#pragma unroll
+            for (int a = 0; a < MT; ++a) {
+                const int r = wm * WTM + a * 16 + a_row;
+                ldmatrix_x4(af[a], a_base + r * ROWB + swz<NCH>(r, ks * 2 + a_ch) * 16);
+            }
+#pragma unroll
+            for (int b = 0; b < NT / 2; ++b) {
+                uint32_t bf[4];
+                const int r = wn * WTN + b * 16 + b_row;
+                ldmatrix_x4(bf, b_base + r * ROWB + swz<NCH>(r, ks * 2 + b_ch) * 16);
+#pragma unroll
+                for (int a = 0; a < MT; ++a) {
+                    mma_bf16(acc[a][2 * b], af[a], bf[0], bf[1]);
+                    mma_bf16(acc[a][2 * b + 1], af[a], bf[2], bf[3]);
+                }
+            }
+        }
+        __syncthreads();   // the stage is free for the prefetch of iteration it + 2
+    }
+
+    // ---- epilogue: + bias, round, store -------------------------------------
+    const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+    for (int a = 0; a < MT; ++a) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int r = wm * WTM + a * 16 + g + half * 8;
+            const int64_t v = rows_s[r];
+            if (v < 0) continue;
+            __nv_bfloat16* op = out + v * (int64_t)cout + col0 + wn * WTN;
+#pragma unroll
+            for (int b = 0; b < NT; ++b) {
+                const int c = b * 8 + 2 * t;
+                float x0 = acc[a][b][half * 2], x1 = acc[a][b][half * 2 + 1];
+                if (bias) {
+                    x0 += __bfloat162float(bias[col0 + wn * WTN + c]);
+                    x1 += __bfloat162float(bias[col0 + wn * WTN + c + 1]);
+                }
+                *reinterpret_cast<uint32_t*>(op + c) = pack_bf16(x0, x1);
+            }
+        }
+    }
+}
+
+template <int CN, int KC>
+constexpr size_t conv_mma_smem()
+{
+    return 2 * (size_t)CM_TM * KC * 2 + 2 * (size_t)CN * KC * 2 + (size_t)CM_MAX_KVOL * CM_TM * 4 + 32 * 4 +
+           CM_TM * 8;
+}
+
+bool conv_mma_supported(int c_in, int c_out, int kernel_volume)
+{
+    if (kernel_volume > CM_MAX_KVOL) return false;
+    if (c_in == 32 && c_out == 32) return true;
+    return c_in % 64 == 0 && (c_out == 64 || c_out % 128 == 0);
+}
+
+template <int CN, int KC, int WM, int WN>
+static int launch_one(const void* feat, const int32_t* nbr, const void* weight, const void* bias, void* out,
+                      const int64_t* row_order, int64_t n, int cin, int cout, int kvol, cudaStream_t stream)
+{
+    constexpr size_t smem = conv_mma_smem<CN, KC>();
+    auto kern = conv_mma_kernel<CN, KC, WM, WN>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return check_launch("ptv3_subm_conv_fwd: shared memory attribute");
+    const dim3 grid((unsigned)((n + CM_TM - 1) / CM_TM), cout / CN);
+    kern<<<grid, CM_THREADS, smem, stream>>>((const __nv_bfloat16*)feat, nbr, (const __nv_bfloat16*)weight,
+                                             (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, row_order, n,
+                                             cin, cout, kvol);
+    count_launches(1);
+    return check_launch("ptv3_subm_conv_fwd");
+}
+
+int launch_conv_mma(const void* feat, const int32_t* nbr, const void* weight, const void* bias, void* out,
+                    const int64_t* row_order, int64_t n, int c_in, int c_out, int kvol, cudaStream_t stream)
+{
+    if (c_in == 32 && c_out == 32)
+        return launch_one<32, 32, 8, 1>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kvol, stream);
+    if (c_out == 64)
+        return launch_one<64, 64, 4, 2>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kvol, stream);
+    return launch_one<128, 64, 4, 2>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kvol, stream);
+}
+
+}  // namespace ptv3

@@ -1,0 +1,16 @@
+// Launcher of the tensor-core submanifold convolution path (conv_mma.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace ptv3 {
+
+bool conv_mma_supported(int c_in, int c_out, int kernel_volume);
+// row_order: optional permutation of the voxels (n int64); tile t then owns
+// voxels row_order[128 t .. 128 t + 127] and column j of nbr describes voxel
+// row_order[j].  NULL = natural order.
+int launch_conv_mma(const void* feat, const int32_t* nbr, const void* weight, const void* bias,
+                    void* out, const int64_t* row_order, int64_t n, int c_in, int c_out,
+                    int kernel_volume, cudaStream_t stream);
+
+}  // namespace ptv3

@@ -157,8 +157,9 @@ def kmap_build(indices, ksize, status=None):
     return nbr
 
 
-def subm_conv(feat, nbr, weight, bias=None, algo=0):
-    """feat (N,Cin), nbr (k^3,N) int32, weight (Cout,k,k,k,Cin) -> (N,Cout)."""
+def subm_conv(feat, nbr, weight, bias=None, algo=0, row_order=None):
+    """feat (N,Cin), nbr (k^3,N) int32, weight (Cout,k,k,k,Cin) -> (N,Cout).
+    row_order: optional (N,) int64 permutation used to group voxels into tiles."""
     _lib.require_cuda(feat, nbr, weight, bias)
     lib = _lib.load()
     feat = feat.contiguous()
@@ -173,7 +174,7 @@ def subm_conv(feat, nbr, weight, bias=None, algo=0):
     out = torch.empty((n, cout), dtype=feat.dtype, device=feat.device)
     with timed("subm_conv_k%d" % round(kvol ** (1 / 3)), 2.0 * n * kvol * cin * cout):
         _lib.check(lib.ptv3_subm_conv_fwd(_lib.ptr(feat), _lib.ptr(nbr), _lib.ptr(weight.contiguous()),
-                                          _lib.ptr(bias), _lib.ptr(out), n, cin, cout, kvol,
+                                          _lib.ptr(bias), _lib.ptr(out), _lib.ptr(row_order), n, cin, cout, kvol,
                                           _lib.dtype_id(feat), int(algo), _lib.stream()),
                    "ptv3_subm_conv_fwd")
     return out

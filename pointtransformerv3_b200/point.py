@@ -133,4 +133,5 @@ class Point(AttrDict):
             indices=torch.cat([self.batch.unsqueeze(-1).int(), self.grid_coord.int()], dim=1).contiguous(),
             spatial_shape=sparse_shape,
             batch_size=len(self.offset),
+            row_order=self.serialized_order[0] if "serialized_order" in self.keys() else None,
         )

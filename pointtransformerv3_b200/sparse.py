@@ -15,24 +15,33 @@ class SparseConvTensor:
     are cached in ``indice_dict`` under ``(indice_key, kernel_size)`` and shared
     by every tensor derived with ``replace_feature``."""
 
-    def __init__(self, features, indices, spatial_shape, batch_size, indice_dict=None):
+    def __init__(self, features, indices, spatial_shape, batch_size, indice_dict=None, row_order=None):
         self.features = features
         self.indices = indices
         self.spatial_shape = spatial_shape
         self.batch_size = batch_size
         self.indice_dict = {} if indice_dict is None else indice_dict
+        # optional voxel permutation along a space-filling curve; convolutions
+        # group voxels into tiles in this order (an extension, not in spconv)
+        self.row_order = row_order
 
     def replace_feature(self, feature):
-        return SparseConvTensor(feature, self.indices, self.spatial_shape, self.batch_size, self.indice_dict)
+        return SparseConvTensor(feature, self.indices, self.spatial_shape, self.batch_size, self.indice_dict,
+                                self.row_order)
 
     def kernel_map(self, kernel_size, indice_key=None):
+        """(nbr, row_order): the offset-major neighbour table with its columns in
+        ``row_order`` (natural order when that is None)."""
         key = (indice_key, kernel_size)
         if indice_key is not None and key in self.indice_dict:
             return self.indice_dict[key]
         nbr = ops.kmap_build(self.indices, kernel_size)
+        if self.row_order is not None:
+            nbr = nbr.index_select(1, self.row_order)
+        entry = (nbr, self.row_order)
         if indice_key is not None:
-            self.indice_dict[key] = nbr
-        return nbr
+            self.indice_dict[key] = entry
+        return entry
 
 
 class SparseModule(nn.Module):
@@ -70,8 +79,8 @@ class SubMConv3d(SparseModule):
             nn.init.uniform_(self.bias, -bound, bound)
 
     def forward(self, x):
-        nbr = x.kernel_map(self.kernel_size, self.indice_key)
-        return x.replace_feature(ops.subm_conv(x.features, nbr, self.weight, self.bias))
+        nbr, row_order = x.kernel_map(self.kernel_size, self.indice_key)
+        return x.replace_feature(ops.subm_conv(x.features, nbr, self.weight, self.bias, row_order=row_order))
 
 
 class _Modules:

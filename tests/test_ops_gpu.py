@@ -214,3 +214,30 @@ def test_attention_config2_size_bf16():
         own = ru[inverse[0][rows]] == torch.arange(patch * K, (patch + 1) * K)
         assert_close(got[rows[own]], ref[own], atol=2e-2, rtol=1e-2, what="patch %d" % patch)
         assert rel_l2(got[rows[own]], ref[own]) < 1e-2
+
+
+@pytest.mark.parametrize("c", [32, 64, 128, 256])
+@pytest.mark.parametrize("permuted", [False, True])
+def test_subm_conv_tensor_core_path(c, permuted):
+    """bf16 tensor-core convolution against the fp32 oracle and the CUDA-core path,
+    with and without a space-filling-curve tile order."""
+    data = small_batch([6000, 2500], 8)
+    batch = O.offset_to_batch(data["offset"])
+    ind = O.sparse_indices(batch, data["grid_coord"])
+    n = ind.shape[0]
+    g = torch.Generator().manual_seed(c)
+    feat = torch.randn(n, c, generator=g).bfloat16()
+    w = (torch.randn(c, 3, 3, 3, c, generator=g) / (9 * c) ** 0.5).bfloat16()
+    b = (torch.randn(c, generator=g) * 0.1).bfloat16()
+    ref = O.subm_conv(feat.float(), O.kernel_map(ind, 3), w.float(), b.float())
+    nbr = ops.kmap_build(ind.cuda(), 3)
+    row_order = None
+    if permuted:
+        code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ["z"])
+        row_order = order[0].cuda()
+        nbr = nbr.index_select(1, row_order)
+    got = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=2, row_order=row_order)
+    base = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=1, row_order=row_order)
+    assert_close(got, ref, what="tensor-core conv vs fp32 oracle", **TOL[torch.bfloat16])
+    assert_close(got, base, atol=1e-2, rtol=1e-2, what="tensor-core vs CUDA-core conv")
+    assert rel_l2(got, ref) < 4e-3
