@@ -217,6 +217,21 @@ int ptv3_unpool_fwd(const void* skip, const void* child, const int64_t* cluster,
                     const float* child_scale, const float* child_shift, void* out, void* skip_act,
                     int dtype, void* stream);
 
+/*
+ * Residual + LayerNorm glue between the GEMMs of a block, one pass over the rows:
+ *     t   = ln1 given ? LayerNorm(x; ln1) : x
+ *     sum = residual given ? residual + t : t      -> sum_out  (optional)
+ *     y   = LayerNorm(sum; ln2)                    -> norm_out (with ln2 only)
+ * Replaces the LayerNorm modules and residual additions of Block.forward
+ * (model.py:553-554, 589-592, 594, 598-600, 602).  All tensors n x channels in
+ * `dtype`; LayerNorm weights and biases have `dtype` too.  channels / (16 bytes
+ * worth of elements) must be a power of two or three times one.
+ */
+int ptv3_add_layernorm_fwd(const void* x, const void* residual, const void* ln1_weight,
+                           const void* ln1_bias, float ln1_eps, void* sum_out, const void* ln2_weight,
+                           const void* ln2_bias, float ln2_eps, void* norm_out, int64_t n, int channels,
+                           int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -142,17 +142,20 @@ class SerializedAttention(PointModule):
             point["pad"], point["unpad"], point["cu_seqlens_key"] = pad, unpad, cu
         return point["pad"], point["unpad"], point["cu_seqlens_key"]
 
-    def forward(self, point):
+    def attend(self, point, feat):
+        """qkv projection, patch attention over ``point``'s serialized order and
+        output projection of the feature matrix ``feat``."""
         assert not self.training, "inference only"
         if not self.enable_flash:
             self.patch_size = min(min(point.host_counts()), self.patch_size_max)
         pad, unpad, cu_seqlens = self.get_padding_and_inverse(point)
-        qkv = self.qkv(point.feat)
+        qkv = self.qkv(feat)
         feat = ops.attention(qkv, point.serialized_order[self.order_index], pad, unpad, cu_seqlens,
                              self.num_heads, self.patch_size, self.scale, self.algo)
-        feat = self.proj(feat)
-        feat = self.proj_drop(feat)
-        point.feat = feat
+        return self.proj_drop(self.proj(feat))
+
+    def forward(self, point):
+        point.feat = self.attend(point, point.feat)
         return point
 
 
@@ -200,8 +203,42 @@ class Block(PointModule):
         self.drop_path_rate = drop_path
         self.drop_path = PointSequential(nn.Identity())
 
+    def _fusable(self, point):
+        """The fused path covers the reference configuration: pre-norm, plain
+        affine LayerNorms, exact GELU, fp32 or bf16 features."""
+        def plain_ln(m):
+            return type(m) is nn.LayerNorm and m.elementwise_affine and m.bias is not None
+        mlp = self.mlp[0] if len(self.mlp) == 1 else None
+        return (self.pre_norm and len(self.cpe) == 3 and isinstance(self.cpe[0], spconv.SubMConv3d)
+                and type(self.cpe[1]) is nn.Linear and plain_ln(self.cpe[2])
+                and len(self.norm1) == 1 and plain_ln(self.norm1[0])
+                and len(self.norm2) == 1 and plain_ln(self.norm2[0])
+                and type(mlp) is MLP and type(mlp.act) is nn.GELU
+                and getattr(mlp.act, "approximate", "none") == "none"
+                and point.feat.dtype in (torch.float32, torch.bfloat16)
+                and "sparse_conv_feat" in point.keys())
+
+    def _forward_fused(self, point):
+        """Same arithmetic as the generic path with the LayerNorms and residual
+        additions done by the fused row kernel (three launches instead of eight)."""
+        shortcut = point.feat
+        sparse = point.sparse_conv_feat
+        # the convolution reads the sparse tensor's features, which differ from
+        # `feat` right after an unpooling (model.py:233-236, 744-746)
+        x = self.cpe[1](self.cpe[0](sparse).features)
+        feat, normed = ops.add_layernorm(x, shortcut, self.cpe[2], self.norm1[0])
+        x = self.attn.attend(point, normed)
+        feat, normed = ops.add_layernorm(x, feat, None, self.norm2[0])
+        x = self.mlp[0](normed)
+        feat, _ = ops.add_layernorm(x, feat, None, None)
+        point.feat = feat
+        point.sparse_conv_feat = sparse.replace_feature(feat)
+        return point
+
     def forward(self, point):
         assert not self.training, "inference only"
+        if self._fusable(point):
+            return self._forward_fused(point)
         shortcut = point.feat
         point = self.cpe(point)
         point.feat = shortcut + point.feat

@@ -254,3 +254,36 @@ def unpool(skip, child, cluster, skip_scale, skip_shift, child_scale, child_shif
                                    _lib.ptr(child_shift), _lib.ptr(out), _lib.ptr(act),
                                    _lib.dtype_id(skip), _lib.stream()), "ptv3_unpool_fwd")
     return out, act
+
+
+def add_layernorm(x, residual=None, ln1=None, ln2=None, want_sum=True):
+    """Fused glue of a block: t = LN1(x) (or x), s = residual + t (or t),
+    y = LN2(s).  ln1/ln2 are torch.nn.LayerNorm modules or None.
+    Returns (s or None, y or None)."""
+    _lib.require_cuda(x, residual)
+    lib = _lib.load()
+    x = x.contiguous()
+    n, C = x.shape
+    if residual is not None:
+        residual = residual.contiguous()
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError("residual must match x")
+
+    def params(ln):
+        if ln is None:
+            return None, None, 0.0
+        if ln.weight is None or ln.bias is None or tuple(ln.normalized_shape) != (C,):
+            raise ValueError("LayerNorm must be affine over the channel axis")
+        if ln.weight.dtype != x.dtype:
+            raise ValueError("LayerNorm parameters must have the feature dtype")
+        return ln.weight, ln.bias, float(ln.eps)
+    w1, b1, e1 = params(ln1)
+    w2, b2, e2 = params(ln2)
+    s = torch.empty_like(x) if (want_sum or ln2 is None) else None
+    y = torch.empty_like(x) if ln2 is not None else None
+    with timed("add_layernorm", float(x.numel() * x.element_size()) * (1 + (residual is not None) +
+                                                                       (s is not None) + (y is not None))):
+        _lib.check(lib.ptv3_add_layernorm_fwd(_lib.ptr(x), _lib.ptr(residual), _lib.ptr(w1), _lib.ptr(b1), e1,
+                                              _lib.ptr(s), _lib.ptr(w2), _lib.ptr(b2), e2, _lib.ptr(y), n, C,
+                                              _lib.dtype_id(x), _lib.stream()), "ptv3_add_layernorm_fwd")
+    return s, y

@@ -241,3 +241,34 @@ def test_subm_conv_tensor_core_path(c, permuted):
     assert_close(got, ref, what="tensor-core conv vs fp32 oracle", **TOL[torch.bfloat16])
     assert_close(got, base, atol=1e-2, rtol=1e-2, what="tensor-core vs CUDA-core conv")
     assert rel_l2(got, ref) < 4e-3
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("C", [32, 48, 64, 128, 256, 512])
+def test_add_layernorm(C, dtype):
+    n = 3001
+    g = torch.Generator().manual_seed(C)
+    x = torch.randn(n, C, generator=g).to(dtype)
+    r = torch.randn(n, C, generator=g).to(dtype)
+    ln1 = torch.nn.LayerNorm(C)
+    ln2 = torch.nn.LayerNorm(C)
+    for ln in (ln1, ln2):
+        ln.weight.data = 1 + 0.1 * torch.randn(C, generator=g)
+        ln.bias.data = 0.1 * torch.randn(C, generator=g)
+    ln1, ln2 = ln1.to(dtype), ln2.to(dtype)
+    ref_s = r + ln1(x)
+    ref_y = ln2(ref_s)
+    import copy
+    c1, c2 = copy.deepcopy(ln1).cuda(), copy.deepcopy(ln2).cuda()
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=1e-2)
+    s, y = ops.add_layernorm(x.cuda(), r.cuda(), c1, c2)
+    assert_close(s, ref_s, what="sum", **tol)
+    assert_close(y, ref_y, what="norm", **tol)
+    s, y = ops.add_layernorm(x.cuda(), r.cuda(), None, c2)
+    assert_close(s, r + x, what="plain sum", **tol)
+    assert_close(y, ln2(r + x), what="norm of plain sum", **tol)
+    s, y = ops.add_layernorm(x.cuda(), None, c1, None)
+    assert y is None
+    assert_close(s, ln1(x), what="plain layer norm", **tol)
+    s, y = ops.add_layernorm(x.cuda(), r.cuda(), None, None)
+    assert_close(s, r + x, what="add only", **tol)
