@@ -172,6 +172,25 @@ int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight,
                        int kernel_volume, int dtype, int algo, void* stream);
 
 /*
+ * Submanifold convolution with few input channels and a large kernel, without a
+ * kernel map: the voxel hash table is built in `workspace` and probed inside
+ * the convolution.  Replaces the stem of model.py:766-779 (SubMConv3d 5x5x5,
+ * bias=False) and, optionally, the BatchNorm1d(eval) + GELU that follow it
+ * (model.py:776-779).
+ *   indices     n x 4 int32 (batch, x, y, z) as for ptv3_kmap_build
+ *   weight      c_out x ksize^3 x c_in; c_in <= 8; c_out in {16, 32, 48, 64}
+ *   bias        c_out or NULL; bn_scale/bn_shift fp32 per channel or both NULL
+ *   apply_gelu  non-zero: exact GELU after the (optional) normalisation
+ *   row_order   optional voxel permutation used to group voxels into tiles
+ */
+size_t ptv3_subm_conv_direct_workspace_bytes(int64_t n, int ksize);
+int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indices, const void* weight,
+                              const void* bias, const float* bn_scale, const float* bn_shift,
+                              int apply_gelu, void* out, const int64_t* row_order, int64_t n, int c_in,
+                              int c_out, int ksize, int dtype, uint32_t* status, void* workspace,
+                              size_t workspace_bytes, void* stream);
+
+/*
  * Cluster and order bookkeeping of serialized pooling.
  * Replaces the index part of model.py:639-695 (unique, sort, cumsum, head
  * gather, argsort + scatter_ of the pooled codes, row shuffle).

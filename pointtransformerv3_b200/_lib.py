@@ -33,6 +33,9 @@ SIGNATURES = {
     "ptv3_kmap_build_static": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr]),
     "ptv3_subm_conv_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int,
                                    c_int, c_int, c_ptr]),
+    "ptv3_subm_conv_direct_workspace_bytes": (c_sz, [c_i64, c_int]),
+    "ptv3_subm_conv_direct_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64,
+                                          c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_pool_plan_workspace_bytes": (c_sz, [c_int, c_i64, c_int]),
     "ptv3_pool_plan": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_i64, c_int, c_int,
                                ctypes.POINTER(c_int), c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,

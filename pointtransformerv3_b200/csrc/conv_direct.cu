@@ -1,0 +1,250 @@
+// Submanifold convolution with few input channels and a large kernel (the 5x5x5
+// stem, model.py:766-779) without a kernel map: the neighbour table of such a
+// convolution (125 x N int32) is several times larger than its input and its
+// output, so the voxel hash table is probed inside the convolution instead.
+//
+// A CTA owns 128 voxels and walks the kernel offsets 25 at a time.  In each
+// round its 256 threads probe the hash table for 25 x 128 neighbour coordinates
+// and gather the features of the neighbours found into shared memory (all
+// probes and gathers of a round are independent, so their latencies overlap);
+// then thread (voxel, half) accumulates half of the output channels in fp32
+// registers, reading the weights (staged once per CTA) as warp-wide broadcasts
+// and skipping absent neighbours.
+// Epilogue: optional bias, optional BatchNorm(eval) scale/shift + exact GELU
+// (model.py:848,860 for the stem), rounding, one contiguous store per thread.
+#include "common.cuh"
+#include "convert.cuh"
+#include "kmap.cuh"
+#include "vec.cuh"
+
+namespace ptv3 {
+
+constexpr int CD_TM = 128;
+constexpr int CD_THREADS = 256;
+constexpr int CD_MAX_CIN = 8;
+
+__device__ __forceinline__ float cd_gelu(float x)
+{
+    return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
+}
+
+constexpr int CD_CHUNK = 25;   // kernel offsets staged per round
+
+// [cout][kvol][cin] -> [kvol][cin][cout], once per call (a few thousand elements)
+template <typename T>
+__global__ void conv_direct_transpose_kernel(const T* __restrict__ w, T* __restrict__ wt, int cout,
+                                             int kvol, int cin)
+{
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= cout * kvol * cin) return;
+    const int ci = idx % cin, rest = idx / cin;
+    const int o = rest % kvol, co = rest / kvol;
+    wt[((size_t)o * cin + ci) * cout + co] = w[idx];
+}
+
+// CO: output channels per thread (c_out = 2 * CO)
+template <typename T, int CO>
+__global__ void __launch_bounds__(CD_THREADS) conv_direct_kernel(
+    const T* __restrict__ feat, const int32_t* __restrict__ indices, const T* __restrict__ weight,
+    const T* __restrict__ bias, const float* __restrict__ bn_scale, const float* __restrict__ bn_shift,
+    int apply_gelu, T* __restrict__ out, const int64_t* __restrict__ row_order, int64_t n, int cin,
+    int ksize, const unsigned long long* __restrict__ keys, const uint32_t* __restrict__ vals,
+    uint64_t cap_mask, uint32_t* __restrict__ status)
+{
+    extern __shared__ __align__(16) unsigned char smem[];
+    const int kvol = ksize * ksize * ksize;
+    const int cout = 2 * CO;
+    // staged neighbour features of one round: [CD_CHUNK][128][CD_MAX_CIN], zero where absent
+    T* x_s = reinterpret_cast<T*>(smem);
+    unsigned char* has_s = smem + (size_t)CD_CHUNK * CD_TM * CD_MAX_CIN * sizeof(T);   // [CD_CHUNK][128]
+    T* w_s = reinterpret_cast<T*>(has_s + CD_CHUNK * CD_TM);                            // kvol x cin x cout
+    __shared__ int4 coord_s[CD_TM];
+    __shared__ char4 delta_s[343];   // (dx, dy, dz) of every kernel offset (runtime division once per CTA)
+
+    const int tid = threadIdx.x;
+    const int v = tid % CD_TM, half = tid / CD_TM;
+    const int64_t i = (int64_t)blockIdx.x * CD_TM + v;
+    const int64_t row = i < n ? (row_order ? row_order[i] : i) : -1;
+    if (half == 0) coord_s[v] = row >= 0 ? reinterpret_cast<const int4*>(indices)[row] : make_int4(-1, 0, 0, 0);
+
+    for (int o = tid; o < kvol; o += CD_THREADS) {
+        const int rr = ksize / 2;
+        delta_s[o] = make_char4((char)(o / (ksize * ksize) - rr), (char)((o / ksize) % ksize - rr),
+                                (char)(o % ksize - rr), 0);
+    }
+    // weights, already transposed to [kvol][cin][cout]: straight 16-byte copy
+    {
+        const int nvec = kvol * cin * cout / Vec<T>::N;
+        const typename Vec<T>::Raw* src = reinterpret_cast<const typename Vec<T>::Raw*>(weight);
+        typename Vec<T>::Raw* dst = reinterpret_cast<typename Vec<T>::Raw*>(w_s);
+        for (int idx = tid; idx < nvec; idx += CD_THREADS) dst[idx] = src[idx];
+    }
+    __syncthreads();
+
+    bool overflow = false;
+    float acc[CO];
+#pragma unroll
+    for (int k = 0; k < CO; ++k) acc[k] = 0.f;
+
+    for (int o0 = 0; o0 < kvol; o0 += CD_CHUNK) {
+        const int no = min(CD_CHUNK, kvol - o0);
+        // probe + gather: one (offset, voxel) pair per thread and step, all independent
+        for (int idx = tid; idx < no * CD_TM; idx += CD_THREADS) {
+            const int ol = idx / CD_TM, vv = idx % CD_TM;
+            const int o = o0 + ol;
+            const int4 c = coord_s[vv];
+            int32_t j = -1;
+            if (c.x >= 0) {
+                const char4 d = delta_s[o];
+                uint64_t key;
+                if (km_key(c.x, c.y + d.x, c.z + d.y, c.w + d.z, key))
+                    j = km_lookup(keys, vals, cap_mask, key, &overflow);
+            }
+            T* dst = x_s + ((size_t)ol * CD_TM + vv) * CD_MAX_CIN;
+            has_s[ol * CD_TM + vv] = j >= 0;
+            if (j >= 0) {
+                const T* src = feat + (int64_t)j * cin;
+#pragma unroll
+                for (int ci = 0; ci < CD_MAX_CIN; ++ci) dst[ci] = ci < cin ? src[ci] : from_f<T>(0.f);
+            }
+        }
+        __syncthreads();
+        for (int ol = 0; ol < no; ++ol) {
+            if (!has_s[ol * CD_TM + v]) continue;
+            const T* xp = x_s + ((size_t)ol * CD_TM + v) * CD_MAX_CIN;
+            float x[CD_MAX_CIN];
+#pragma unroll
+            for (int ci = 0; ci < CD_MAX_CIN; ci += Vec<T>::N)
+                Vec<T>::unpack(*reinterpret_cast<const typename Vec<T>::Raw*>(xp + ci), x + ci);
+            const T* w = w_s + (size_t)(o0 + ol) * cin * cout + half * CO;
+#pragma unroll
+            for (int ci = 0; ci < CD_MAX_CIN; ++ci) {
+                if (ci < cin) {
+                    // CO consecutive weights with 16-byte shared-memory loads (same address warp-wide)
+#pragma unroll
+                    for (int k = 0; k < CO; k += Vec<T>::N) {
+                        float wv[Vec<T>::N];
+                        Vec<T>::unpack(*reinterpret_cast<const typename Vec<T>::Raw*>(w + ci * cout + k), wv);
+#pragma unroll
+                        for (int q = 0; q < Vec<T>::N; ++q) acc[k + q] = fmaf(x[ci], wv[q], acc[k + q]);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (overflow) atomicOr(status, PTV3_STATUS_PROBE_LIMIT);
+    if (row < 0) return;
+    T* op = out + row * (int64_t)cout + half * CO;
+#pragma unroll
+    for (int k = 0; k < CO; ++k) {
+        const int ch = half * CO + k;
+        float y = acc[k];
+        if (bias) y += to_f<T>(bias[ch]);
+        if (bn_scale) {
+            // the convolution output is rounded to the element type first, as a
+            // separate normalisation module would see it
+            y = to_f<T>(from_f<T>(y));
+            y = fmaf(y, bn_scale[ch], bn_shift[ch]);
+        }
+        if (apply_gelu) {
+            if (bn_scale) y = to_f<T>(from_f<T>(y));
+            y = cd_gelu(y);
+        }
+        op[k] = from_f<T>(y);
+    }
+}
+
+template <typename T>
+static int launch_conv_direct(const void* feat, const int32_t* indices, const void* weight, const void* bias,
+                              const float* bn_scale, const float* bn_shift, int apply_gelu, void* out,
+                              const int64_t* row_order, int64_t n, int cin, int cout, int ksize,
+                              const unsigned long long* keys, const uint32_t* vals, uint64_t cap_mask,
+                              uint32_t* status, void* wt, cudaStream_t stream)
+{
+    const int kvol = ksize * ksize * ksize;
+    conv_direct_transpose_kernel<T><<<(cout * kvol * cin + 255) / 256, 256, 0, stream>>>(
+        (const T*)weight, (T*)wt, cout, kvol, cin);
+    weight = wt;
+    const size_t smem = (size_t)CD_CHUNK * CD_TM * (CD_MAX_CIN * sizeof(T) + 1) +
+                        (size_t)kvol * cin * cout * sizeof(T);
+    const unsigned blocks = (unsigned)((n + CD_TM - 1) / CD_TM);
+#define CD_LAUNCH(CO)                                                                                    \
+    do {                                                                                                 \
+        auto kern = conv_direct_kernel<T, CO>;                                                           \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=        \
+            cudaSuccess)                                                                                 \
+            return check_launch("ptv3_subm_conv_direct_fwd: shared memory attribute");                   \
+        kern<<<blocks, CD_THREADS, smem, stream>>>((const T*)feat, indices, (const T*)weight,             \
+                                                   (const T*)bias, bn_scale, bn_shift, apply_gelu,        \
+                                                   (T*)out, row_order, n, cin, ksize, keys, vals,         \
+                                                   cap_mask, status);                                     \
+    } while (0)
+    if (smem > 220 * 1024) {
+        set_error("ptv3_subm_conv_direct_fwd: %zu bytes of shared memory needed", smem);
+        return PTV3_ERR_UNSUPPORTED;
+    }
+    switch (cout) {
+        case 16: CD_LAUNCH(8); break;
+        case 32: CD_LAUNCH(16); break;
+        case 48: CD_LAUNCH(24); break;
+        case 64: CD_LAUNCH(32); break;
+        default:
+            set_error("ptv3_subm_conv_direct_fwd: c_out %d (supported: 16, 32, 48, 64)", cout);
+            return PTV3_ERR_UNSUPPORTED;
+    }
+#undef CD_LAUNCH
+    count_launches(2);
+    return check_launch("ptv3_subm_conv_direct_fwd");
+}
+
+static size_t conv_direct_weight_bytes(int ksize) { return align_up((size_t)ksize * ksize * ksize * 8 * 64 * 4, 256); }
+
+}  // namespace ptv3
+
+extern "C" size_t ptv3_subm_conv_direct_workspace_bytes(int64_t n, int ksize)
+{
+    return n > 0 ? ptv3::km_table_bytes(n) + ptv3::conv_direct_weight_bytes(ksize) : 0;
+}
+
+extern "C" int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indices, const void* weight,
+                                         const void* bias, const float* bn_scale, const float* bn_shift,
+                                         int apply_gelu, void* out, const int64_t* row_order, int64_t n,
+                                         int c_in, int c_out, int ksize, int dtype, uint32_t* status,
+                                         void* workspace, size_t workspace_bytes, void* stream_)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0 && n < (1ll << 31), PTV3_ERR_INVALID_ARGUMENT, "ptv3_subm_conv_direct_fwd: bad n");
+    PTV3_REQUIRE(c_in >= 1 && c_in <= CD_MAX_CIN, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_subm_conv_direct_fwd: c_in %d outside [1, %d]", c_in, CD_MAX_CIN);
+    PTV3_REQUIRE(ksize == 1 || ksize == 3 || ksize == 5 || ksize == 7, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_subm_conv_direct_fwd: kernel size %d (supported: 1, 3, 5, 7)", ksize);
+    PTV3_REQUIRE(dtype == PTV3_DTYPE_F32 || dtype == PTV3_DTYPE_BF16, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_subm_conv_direct_fwd: dtype %d", dtype);
+    PTV3_REQUIRE((bn_scale == nullptr) == (bn_shift == nullptr), PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_subm_conv_direct_fwd: bn_scale and bn_shift go together");
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(feat && indices && weight && out && status && workspace, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_subm_conv_direct_fwd: null pointer");
+    PTV3_REQUIRE(((uintptr_t)indices & 15) == 0, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_subm_conv_direct_fwd: indices must be 16-byte aligned");
+    const size_t need = km_table_bytes(n) + conv_direct_weight_bytes(ksize);
+    PTV3_REQUIRE(workspace_bytes >= need, PTV3_ERR_WORKSPACE,
+                 "ptv3_subm_conv_direct_fwd: workspace %zu < %zu bytes", workspace_bytes, need);
+    PTV3_REQUIRE(((size_t)ksize * ksize * ksize * c_in * c_out) % 8 == 0, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_subm_conv_direct_fwd: weight size must be a multiple of 8 elements");
+    void* wt = static_cast<char*>(workspace) + km_table_bytes(n);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    unsigned long long* keys;
+    uint32_t* vals;
+    uint64_t cap_mask;
+    const int rc = km_build_table(indices, n, workspace, status, stream, &keys, &vals, &cap_mask);
+    if (rc != PTV3_OK) return rc;
+    if (dtype == PTV3_DTYPE_F32)
+        return launch_conv_direct<float>(feat, indices, weight, bias, bn_scale, bn_shift, apply_gelu, out,
+                                         row_order, n, c_in, c_out, ksize, keys, vals, cap_mask, status, wt,
+                                         stream);
+    return launch_conv_direct<__nv_bfloat16>(feat, indices, weight, bias, bn_scale, bn_shift, apply_gelu,
+                                             out, row_order, n, c_in, c_out, ksize, keys, vals, cap_mask,
+                                             status, wt, stream);
+}

@@ -19,9 +19,8 @@
 
 namespace ptv3 {
 
-constexpr int CM_THREADS = 256;
-constexpr int CM_TM = 128;
 constexpr int CM_MAX_KVOL = 27;
+constexpr int CM_STAGES = 3;
 
 // physical 16-byte chunk of logical chunk c in row r for rows of NCH chunks
 template <int NCH>
@@ -32,15 +31,16 @@ __device__ __forceinline__ int swz(int r, int c)
     return c;
 }
 
-// CN: output channels per CTA; KC: input channels per stage; WM x WN warps
-template <int CN, int KC, int WM, int WN>
-__global__ void __launch_bounds__(CM_THREADS) conv_mma_kernel(
+// CM_TM: voxels per CTA; CN: output channels per CTA; KC: input channels per
+// stage; WM x WN warps
+template <int CM_TM, int CN, int KC, int WM, int WN>
+__global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
     const __nv_bfloat16* __restrict__ feat, const int32_t* __restrict__ nbr,
     const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ bias,
     __nv_bfloat16* __restrict__ out, const int64_t* __restrict__ row_order, int64_t n, int cin,
     int cout, int kvol)
 {
-    static_assert(WM * WN == CM_THREADS / 32, "warp layout");
+    constexpr int CM_THREADS = WM * WN * 32;
     constexpr int NCH = KC / 8;              // 16-byte chunks per staged row
     constexpr int ROWB = KC * 2;             // bytes per staged row
     constexpr int WTM = CM_TM / WM;          // rows per warp
@@ -50,9 +50,9 @@ __global__ void __launch_bounds__(CM_THREADS) conv_mma_kernel(
     constexpr int A_BYTES = CM_TM * ROWB, B_BYTES = CN * ROWB;
 
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* As = smem;                          // 2 stages
-    unsigned char* Bs = smem + 2 * A_BYTES;            // 2 stages
-    int32_t* nbr_s = reinterpret_cast<int32_t*>(smem + 2 * A_BYTES + 2 * B_BYTES);   // kvol x 128
+    unsigned char* As = smem;                                  // CM_STAGES stages
+    unsigned char* Bs = smem + CM_STAGES * A_BYTES;            // CM_STAGES stages
+    int32_t* nbr_s = reinterpret_cast<int32_t*>(smem + CM_STAGES * (A_BYTES + B_BYTES));   // kvol x CM_TM
     int* act = reinterpret_cast<int*>(nbr_s + CM_MAX_KVOL * CM_TM);                   // kvol + 1
     int64_t* rows_s = reinterpret_cast<int64_t*>(act + 32);                          // 128
 
@@ -119,23 +119,24 @@ __global__ void __launch_bounds__(CM_THREADS) conv_mma_kernel(
             const uint32_t dst = b_base + r * ROWB + swz<NCH>(r, c) * 16;
             cp_async16(dst, weight + ((int64_t)(col0 + r) * kvol + o) * cin + kc + c * 8);
         }
-        cp_async_commit();
     };
 
     // ldmatrix lane roles
     const int a_row = (lane & 7) + (((lane >> 3) & 1) << 3), a_ch = lane >> 4;
     const int b_row = (lane & 7) + ((lane >> 4) << 3), b_ch = (lane >> 3) & 1;
 
-    if (nit > 0) prefetch(0, 0);
+    // one cp.async group per iteration (empty past the end) keeps the wait uniform
+#pragma unroll
+    for (int st = 0; st < CM_STAGES - 1; ++st) {
+        if (st < nit) prefetch(st, st);
+        cp_async_commit();
+    }
     for (int it = 0; it < nit; ++it) {
-        const int buf = it & 1;
-        if (it + 1 < nit) {
-            prefetch(it + 1, buf ^ 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int buf = it % CM_STAGES;
+        cp_async_wait<CM_STAGES - 2>();
+        __syncthreads();   // stage `buf` has landed; stage (it - 1) % CM_STAGES is free again
+        if (it + CM_STAGES - 1 < nit) prefetch(it + CM_STAGES - 1, (it + CM_STAGES - 1) % CM_STAGES);
+        cp_async_commit();
         const uint32_t a_base = smem_u32(As + buf * A_BYTES);
         const uint32_t b_base = smem_u32(Bs + buf * B_BYTES);
 #pragma unroll
@@ -158,8 +159,8 @@ __global__ void __launch_bounds__(CM_THREADS) conv_mma_kernel(
                 }
             }
         }
-        __syncthreads();   // the stage is free for the prefetch of iteration it + 2
     }
+    cp_async_wait<0>();
 
     // ---- epilogue: + bias, round, store -------------------------------------
     const int g = lane >> 2, t = lane & 3;
@@ -185,11 +186,11 @@ __global__ void __launch_bounds__(CM_THREADS) conv_mma_kernel(
     }
 }
 
-template <int CN, int KC>
+template <int CM_TM, int CN, int KC>
 constexpr size_t conv_mma_smem()
 {
-    return 2 * (size_t)CM_TM * KC * 2 + 2 * (size_t)CN * KC * 2 + (size_t)CM_MAX_KVOL * CM_TM * 4 + 32 * 4 +
-           CM_TM * 8;
+    return CM_STAGES * ((size_t)CM_TM * KC * 2 + (size_t)CN * KC * 2) + (size_t)CM_MAX_KVOL * CM_TM * 4 +
+           32 * 4 + CM_TM * 8;
 }
 
 bool conv_mma_supported(int c_in, int c_out, int kernel_volume)
@@ -199,16 +200,16 @@ bool conv_mma_supported(int c_in, int c_out, int kernel_volume)
     return c_in % 64 == 0 && (c_out == 64 || c_out % 128 == 0);
 }
 
-template <int CN, int KC, int WM, int WN>
+template <int CM_TM, int CN, int KC, int WM, int WN>
 static int launch_one(const void* feat, const int32_t* nbr, const void* weight, const void* bias, void* out,
                       const int64_t* row_order, int64_t n, int cin, int cout, int kvol, cudaStream_t stream)
 {
-    constexpr size_t smem = conv_mma_smem<CN, KC>();
-    auto kern = conv_mma_kernel<CN, KC, WM, WN>;
+    constexpr size_t smem = conv_mma_smem<CM_TM, CN, KC>();
+    auto kern = conv_mma_kernel<CM_TM, CN, KC, WM, WN>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_subm_conv_fwd: shared memory attribute");
     const dim3 grid((unsigned)((n + CM_TM - 1) / CM_TM), cout / CN);
-    kern<<<grid, CM_THREADS, smem, stream>>>((const __nv_bfloat16*)feat, nbr, (const __nv_bfloat16*)weight,
+    kern<<<grid, WM * WN * 32, smem, stream>>>((const __nv_bfloat16*)feat, nbr, (const __nv_bfloat16*)weight,
                                              (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, row_order, n,
                                              cin, cout, kvol);
     count_launches(1);
@@ -218,11 +219,17 @@ static int launch_one(const void* feat, const int32_t* nbr, const void* weight, 
 int launch_conv_mma(const void* feat, const int32_t* nbr, const void* weight, const void* bias, void* out,
                     const int64_t* row_order, int64_t n, int c_in, int c_out, int kvol, cudaStream_t stream)
 {
-    if (c_in == 32 && c_out == 32)
-        return launch_one<32, 32, 8, 1>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kvol, stream);
-    if (c_out == 64)
-        return launch_one<64, 64, 4, 2>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kvol, stream);
-    return launch_one<128, 64, 4, 2>(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kvol, stream);
+#define CM_ARGS feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kvol, stream
+    if (c_in == 32 && c_out == 32) return launch_one<128, 32, 32, 8, 1>(CM_ARGS);
+    // few voxels: 64 x 64 tiles on 4 warps so that enough CTAs exist to fill the GPU
+    const int64_t big_ctas = ((n + 127) / 128) * ((c_out + 127) / 128);
+    if (c_out == 64) {
+        if (big_ctas * 2 < 2 * 148) return launch_one<64, 64, 64, 2, 2>(CM_ARGS);
+        return launch_one<128, 64, 64, 4, 2>(CM_ARGS);
+    }
+    if (big_ctas < 2 * 148) return launch_one<64, 64, 64, 2, 2>(CM_ARGS);
+    return launch_one<128, 128, 64, 4, 2>(CM_ARGS);
+#undef CM_ARGS
 }
 
 }  // namespace ptv3

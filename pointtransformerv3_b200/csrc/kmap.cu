@@ -8,29 +8,9 @@
 // consecutive voxels reads each offset's neighbour rows coalesced.
 // Offset index o = ((dx+r)*k + (dy+r))*k + (dz+r), r = k/2.
 #include "common.cuh"
-#include "../../include/ptv3_b200.h"
+#include "kmap.cuh"
 
 namespace ptv3 {
-
-constexpr uint64_t KM_EMPTY = ~0ull;
-
-__device__ __forceinline__ uint64_t km_mix(uint64_t h)
-{
-    h ^= h >> 33;
-    h *= 0xff51afd7ed558ccdull;
-    h ^= h >> 33;
-    h *= 0xc4ceb9fe1a85ec53ull;
-    h ^= h >> 33;
-    return h;
-}
-
-__device__ __forceinline__ bool km_key(int b, int x, int y, int z, uint64_t& key)
-{
-    if ((unsigned)b > 0xfffeu || (unsigned)x > 0xffffu || (unsigned)y > 0xffffu || (unsigned)z > 0xffffu)
-        return false;
-    key = ((uint64_t)b << 48) | ((uint64_t)x << 32) | ((uint64_t)y << 16) | (uint64_t)z;
-    return true;
-}
 
 __global__ void __launch_bounds__(256) km_insert_kernel(const int32_t* __restrict__ indices, int64_t n,
                                                         unsigned long long* __restrict__ keys,
@@ -64,11 +44,19 @@ __global__ void __launch_bounds__(256) km_probe_kernel(const int32_t* __restrict
                                                        uint64_t cap_mask, int32_t* __restrict__ nbr,
                                                        uint32_t* __restrict__ status)
 {
+    // the offset is the same for the whole CTA: one thread does the runtime divisions
+    __shared__ int delta[3];
+    if (threadIdx.x == 0) {
+        const int o = blockIdx.y, r = ksize / 2;
+        delta[0] = o / (ksize * ksize) - r;
+        delta[1] = (o / ksize) % ksize - r;
+        delta[2] = o % ksize - r;
+    }
+    __syncthreads();
+    const int o = blockIdx.y;
+    const int dx = delta[0], dy = delta[1], dz = delta[2];
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const int o = blockIdx.y;
-    const int r = ksize / 2;
-    const int dz = o % ksize - r, dy = (o / ksize) % ksize - r, dx = o / (ksize * ksize) - r;
     const int4 v = reinterpret_cast<const int4*>(indices)[i];
     int32_t found = -1;
     uint64_t key;
@@ -89,11 +77,36 @@ __global__ void __launch_bounds__(256) km_probe_kernel(const int32_t* __restrict
     nbr[(int64_t)o * n + i] = found;
 }
 
-static uint64_t km_capacity(int64_t n)
+uint64_t km_capacity(int64_t n)
 {
     uint64_t c = 1024;
     while (c < (uint64_t)n * 2) c <<= 1;
     return c;
+}
+
+size_t km_table_bytes(int64_t n)
+{
+    const uint64_t cap = km_capacity(n);
+    return align_up(cap * sizeof(uint64_t), 256) + align_up(cap * sizeof(uint32_t), 256);
+}
+
+int km_build_table(const int32_t* indices, int64_t n, void* workspace, uint32_t* status,
+                   cudaStream_t stream, unsigned long long** keys_out, uint32_t** vals_out,
+                   uint64_t* cap_mask_out)
+{
+    const uint64_t cap = km_capacity(n);
+    Carver cv(workspace);
+    unsigned long long* keys = cv.take<unsigned long long>(cap);
+    uint32_t* vals = cv.take<uint32_t>(cap);
+    cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
+    cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream);
+    km_insert_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(indices, n, keys, vals, cap - 1,
+                                                                      status);
+    count_launches(1);
+    *keys_out = keys;
+    *vals_out = vals;
+    *cap_mask_out = cap - 1;
+    return check_launch("voxel hash table");
 }
 
 }  // namespace ptv3

@@ -10,7 +10,7 @@ from functools import partial
 import torch
 import torch.nn as nn
 
-from . import ops
+from . import _lib, ops
 from . import sparse as spconv
 from .point import AttrDict, Point, offset2bincount
 
@@ -138,7 +138,9 @@ class SerializedAttention(PointModule):
     def get_padding_and_inverse(self, point):
         """model.py:382-438; cached in the Point under the reference's keys."""
         if not {"pad", "unpad", "cu_seqlens_key"}.issubset(point.keys()):
-            pad, unpad, cu = ops.pad_plan(point.offset, point.host_counts(), self.patch_size)
+            pad, unpad, cu = ops.pad_plan(point.offset, point.host_counts(), self.patch_size,
+                                          point.device_status())
+            point.check_status("ptv3_pad_plan")
             point["pad"], point["unpad"], point["cu_seqlens_key"] = pad, unpad, cu
         return point["pad"], point["unpad"], point["cu_seqlens_key"]
 
@@ -281,8 +283,11 @@ class SerializedPooling(PointModule):
         self.norm = PointSequential(norm_layer(out_channels)) if norm_layer is not None else None
         self.act = PointSequential(act_layer()) if act_layer is not None else None
 
-    def forward(self, point):
-        assert not self.training, "inference only"
+    def plan(self, point):
+        """Index side of the pooling (model.py:640-680, 690-695): clusters, pooled
+        codes/orders/inverses, grid coordinates and scene ids of the coarse level,
+        returned as a Point without features.  Draws the order shuffle.  One host
+        read (the size of the coarse level)."""
         pooling_depth = (math.ceil(self.stride) - 1).bit_length()
         if pooling_depth > point.serialized_depth:
             pooling_depth = 0
@@ -291,16 +296,8 @@ class SerializedPooling(PointModule):
         k = point.serialized_code.shape[0]
         perm = torch.randperm(k).tolist() if self.shuffle_orders else None
         plan = ops.pool_plan(point.serialized_code, point.serialized_order, point.grid_coord, point.batch,
-                             len(point.offset), pooling_depth, perm)
-        fused = _is_bn_gelu(self.norm, self.act)
-        scale = shift = None
-        if fused:
-            scale, shift = _bn_eval_affine(self.norm[0])
-        feat, coord = ops.pool(self.proj(point.feat), point.coord if "coord" in point.keys() else None,
-                               point.serialized_order[0], plan["idx_ptr"], scale, shift)
-        counts = plan["counts"]
-        point_dict = AttrDict(
-            feat=feat,
+                             len(point.offset), pooling_depth, perm, point.device_status())
+        child = Point(AttrDict(
             grid_coord=plan["grid_coord"],
             serialized_code=plan["code"],
             serialized_order=plan["order"],
@@ -308,18 +305,43 @@ class SerializedPooling(PointModule):
             serialized_depth=point.serialized_depth - pooling_depth,
             batch=plan["batch"],
             offset=plan["offset"],
-        )
+        ))
+        child["_counts"] = plan["counts"]
+        child["_status"] = point.device_status()
+        child["_defer_status"] = point.get("_defer_status", False)
+        child["_idx_ptr"] = plan["idx_ptr"]
+        child["_cluster"] = plan["cluster"]
+        if "_shape_pad" in point.keys():
+            # max(coord >> d) == max(coord) >> d, so the coarse sparse shape follows
+            # from the fine one without reading the device (model.py:162-164)
+            pad = point["_shape_pad"]
+            child["sparse_shape"] = [((v - pad) >> pooling_depth) + pad for v in point.sparse_shape]
+            child["_shape_pad"] = pad
+        return child
+
+    def forward(self, point):
+        assert not self.training, "inference only"
+        child = point.pop("_pooled_child", None)
+        if child is None:
+            child = self.plan(point)
+        fused = _is_bn_gelu(self.norm, self.act)
+        scale = shift = None
+        if fused:
+            scale, shift = _bn_eval_affine(self.norm[0])
+        feat, coord = ops.pool(self.proj(point.feat), point.coord if "coord" in point.keys() else None,
+                               point.serialized_order[0], child.pop("_idx_ptr"), scale, shift)
+        cluster = child.pop("_cluster")
+        child["feat"] = feat
         if coord is not None:
-            point_dict["coord"] = coord
+            child["coord"] = coord
         if "condition" in point.keys():
-            point_dict["condition"] = point.condition
+            child["condition"] = point.condition
         if "context" in point.keys():
-            point_dict["context"] = point.context
+            child["context"] = point.context
         if self.traceable:
-            point_dict["pooling_inverse"] = plan["cluster"]
-            point_dict["pooling_parent"] = point
-        point = Point(point_dict)
-        point["_counts"] = counts
+            child["pooling_inverse"] = cluster
+            child["pooling_parent"] = point
+        point = child
         if not fused:
             if self.norm is not None:
                 point = self.norm(point)
@@ -399,6 +421,17 @@ class Embedding(PointModule):
             self.stem.add(act_layer(), name="act")
 
     def forward(self, point):
+        mods = list(self.stem._modules.values())
+        conv = mods[0]
+        # convolution + BatchNorm(eval) + GELU in one kernel when that is what the stem is
+        if (len(mods) == 3 and isinstance(conv, spconv.SubMConv3d) and conv.uses_direct_path()
+                and type(mods[1]) is nn.BatchNorm1d and not mods[1].training and mods[1].track_running_stats
+                and type(mods[2]) is nn.GELU and getattr(mods[2], "approximate", "none") == "none"
+                and "sparse_conv_feat" in point.keys()):
+            scale, shift = _bn_eval_affine(mods[1])
+            point.sparse_conv_feat = conv(point.sparse_conv_feat, scale, shift, True)
+            point.feat = point.sparse_conv_feat.features
+            return point
         return self.stem(point)
 
 
@@ -489,12 +522,38 @@ class PointTransformerV3(PointModule):
         (needed when one logical batch is split over several processes)."""
         point = Point(data_dict)
         depth = point.pop("serialization_depth", None)
+        status = point.device_status()
+        point["_defer_status"] = True
+        # -- planning phase: everything whose size depends on the data, so that all
+        #    host reads happen here and the feature phase is queued without waiting
+        point._ensure_grid_coord()
+        if "sparse_shape" not in point.keys() or depth is None or "_counts" not in point.keys():
+            stats = torch.cat([point.grid_coord.max(0).values.to(torch.int64), point.offset.to(torch.int64)])
+            stats = stats.tolist()                                     # one host read
+            if depth is None:
+                depth = max(stats[:3]).bit_length()
+            if "sparse_shape" not in point.keys():
+                point["sparse_shape"] = [v + 96 for v in stats[:3]]
+                point["_shape_pad"] = 96
+            off = [0] + stats[3:]
+            point["_counts"] = [off[i + 1] - off[i] for i in range(len(off) - 1)]
         point.serialization(order=self.order, depth=depth, shuffle_orders=self.shuffle_orders)
+        level = point
+        for s in range(1, self.num_stages):
+            down = self.enc[s][0] if isinstance(self.enc[s][0], SerializedPooling) else None
+            if down is None:
+                break
+            child = down.plan(level)
+            level["_pooled_child"] = child
+            level = child
+        # -- feature phase
         point.sparsify()
         point = self.embedding(point)
         point = self.enc(point)
         if not self.cls_mode:
             point = self.dec(point)
+        point["_defer_status"] = False
+        _lib.raise_on_status(status, "PointTransformerV3.forward")
         return point
 
 

@@ -180,7 +180,7 @@ def subm_conv(feat, nbr, weight, bias=None, algo=0, row_order=None):
     return out
 
 
-def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=None):
+def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=None, status=None):
     """Builds the pooled level's index tensors; one host sync to learn its size.
 
     Returns dict(cluster, idx_ptr, head, code, order, inverse, grid_coord, batch, counts,
@@ -202,7 +202,8 @@ def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=
     pgrid = torch.empty((n, 3), dtype=torch.int32, device=dev)
     pbatch = torch.empty(n, **i64)
     meta = torch.empty(1 + n_scenes, **i64)
-    status = new_status(dev)
+    if status is None:
+        status = new_status(dev)
     nbytes = lib.ptv3_pool_plan_workspace_bytes(k, n, n_scenes)
     ws = _lib.workspace(nbytes, dev)
     perm = None
@@ -287,3 +288,32 @@ def add_layernorm(x, residual=None, ln1=None, ln2=None, want_sum=True):
                                               _lib.ptr(s), _lib.ptr(w2), _lib.ptr(b2), e2, _lib.ptr(y), n, C,
                                               _lib.dtype_id(x), _lib.stream()), "ptv3_add_layernorm_fwd")
     return s, y
+
+
+def subm_conv_direct(feat, indices, weight, bias=None, bn_scale=None, bn_shift=None, gelu=False,
+                     row_order=None, status=None):
+    """Submanifold convolution for few input channels / large kernels that probes
+    the voxel hash table itself (no kernel map); optional fused BN(eval) + GELU."""
+    _lib.require_cuda(feat, indices, weight, bias)
+    lib = _lib.load()
+    feat = feat.contiguous()
+    indices = indices.to(torch.int32).contiguous()
+    n, cin = feat.shape
+    cout, ksize = weight.shape[0], weight.shape[1]
+    if weight.dtype != feat.dtype or weight.shape[-1] != cin:
+        raise ValueError("weight does not match the features")
+    out = torch.empty((n, cout), dtype=feat.dtype, device=feat.device)
+    nbytes = lib.ptv3_subm_conv_direct_workspace_bytes(n, ksize)
+    ws = _lib.workspace(nbytes, feat.device)
+    own = status is None
+    if own:
+        status = new_status(feat.device)
+    with timed("subm_conv_direct_k%d" % ksize, 2.0 * n * ksize ** 3 * cin * cout):
+        _lib.check(lib.ptv3_subm_conv_direct_fwd(
+            _lib.ptr(feat), _lib.ptr(indices), _lib.ptr(weight.contiguous()), _lib.ptr(bias),
+            _lib.ptr(bn_scale), _lib.ptr(bn_shift), int(bool(gelu)), _lib.ptr(out), _lib.ptr(row_order), n, cin,
+            cout, ksize, _lib.dtype_id(feat), _lib.ptr(status), _lib.ptr(ws), nbytes, _lib.stream()),
+            "ptv3_subm_conv_direct_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_subm_conv_direct_fwd")
+    return out

@@ -3,7 +3,7 @@ and methods (model.py:28-174); serialization and kernel maps run on the CUDA
 library."""
 import torch
 
-from . import ops
+from . import _lib, ops
 from .sparse import SparseConvTensor
 
 
@@ -80,6 +80,20 @@ class Point(AttrDict):
         elif "offset" not in self.keys() and "batch" in self.keys():
             self["offset"] = batch2offset(self.batch)
 
+    def device_status(self):
+        """The device status word kernels OR error bits into (created on first use
+        and shared with the levels pooled from this one)."""
+        if "_status" not in self.keys():
+            ref = self.feat if "feat" in self.keys() else self.batch
+            self["_status"] = torch.zeros(1, dtype=torch.int32, device=ref.device)
+        return self["_status"]
+
+    def check_status(self, what="point operators", force=False):
+        """Raises if a kernel reported a problem.  Reads the status word (a host
+        sync) unless the owner of the forward pass deferred the check to its end."""
+        if "_status" in self.keys() and (force or not self.get("_defer_status", False)):
+            _lib.raise_on_status(self["_status"], what)
+
     def host_counts(self):
         """Per-scene point counts as Python ints (one device read, then cached)."""
         if "_counts" not in self.keys():
@@ -127,6 +141,7 @@ class Point(AttrDict):
             sparse_shape = self.sparse_shape
         else:
             sparse_shape = torch.add(torch.max(self.grid_coord, dim=0).values, pad).tolist()
+            self["_shape_pad"] = pad
         self["sparse_shape"] = sparse_shape
         self["sparse_conv_feat"] = SparseConvTensor(
             features=self.feat,
@@ -134,4 +149,6 @@ class Point(AttrDict):
             spatial_shape=sparse_shape,
             batch_size=len(self.offset),
             row_order=self.serialized_order[0] if "serialized_order" in self.keys() else None,
+            status=self.device_status(),
+            defer_status=self.get("_defer_status", False),
         )

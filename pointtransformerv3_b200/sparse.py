@@ -15,7 +15,8 @@ class SparseConvTensor:
     are cached in ``indice_dict`` under ``(indice_key, kernel_size)`` and shared
     by every tensor derived with ``replace_feature``."""
 
-    def __init__(self, features, indices, spatial_shape, batch_size, indice_dict=None, row_order=None):
+    def __init__(self, features, indices, spatial_shape, batch_size, indice_dict=None, row_order=None,
+                 status=None, defer_status=False):
         self.features = features
         self.indices = indices
         self.spatial_shape = spatial_shape
@@ -24,10 +25,14 @@ class SparseConvTensor:
         # optional voxel permutation along a space-filling curve; convolutions
         # group voxels into tiles in this order (an extension, not in spconv)
         self.row_order = row_order
+        # device status word of the owning Point; when the check is deferred the
+        # owner reads it once at the end of its forward pass
+        self.status = status
+        self.defer_status = defer_status
 
     def replace_feature(self, feature):
         return SparseConvTensor(feature, self.indices, self.spatial_shape, self.batch_size, self.indice_dict,
-                                self.row_order)
+                                self.row_order, self.status, self.defer_status)
 
     def kernel_map(self, kernel_size, indice_key=None):
         """(nbr, row_order): the offset-major neighbour table with its columns in
@@ -35,7 +40,10 @@ class SparseConvTensor:
         key = (indice_key, kernel_size)
         if indice_key is not None and key in self.indice_dict:
             return self.indice_dict[key]
-        nbr = ops.kmap_build(self.indices, kernel_size)
+        nbr = ops.kmap_build(self.indices, kernel_size, self.status)
+        if self.status is not None and not self.defer_status:
+            from . import _lib
+            _lib.raise_on_status(self.status, "ptv3_kmap_build")
         if self.row_order is not None:
             nbr = nbr.index_select(1, self.row_order)
         entry = (nbr, self.row_order)
@@ -78,7 +86,20 @@ class SubMConv3d(SparseModule):
         if self.bias is not None:
             nn.init.uniform_(self.bias, -bound, bound)
 
-    def forward(self, x):
+    def uses_direct_path(self):
+        """Few input channels with a large kernel: probing the hash table inside
+        the convolution beats building a (kernel volume x N) neighbour table."""
+        return self.in_channels <= 8 and self.kernel_size >= 5 and self.out_channels in (16, 32, 48, 64)
+
+    def forward(self, x, bn_scale=None, bn_shift=None, gelu=False):
+        if self.uses_direct_path():
+            out = ops.subm_conv_direct(x.features, x.indices, self.weight, self.bias, bn_scale, bn_shift, gelu,
+                                       x.row_order, x.status)
+            if x.status is not None and not x.defer_status:
+                from . import _lib
+                _lib.raise_on_status(x.status, "ptv3_subm_conv_direct_fwd")
+            return x.replace_feature(out)
+        assert bn_scale is None and not gelu
         nbr, row_order = x.kernel_map(self.kernel_size, self.indice_key)
         return x.replace_feature(ops.subm_conv(x.features, nbr, self.weight, self.bias, row_order=row_order))
 

@@ -272,3 +272,26 @@ def test_add_layernorm(C, dtype):
     assert_close(s, ln1(x), what="plain layer norm", **tol)
     s, y = ops.add_layernorm(x.cuda(), r.cuda(), None, None)
     assert_close(s, r + x, what="add only", **tol)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("cin,cout,k,fuse", [(6, 32, 5, True), (4, 32, 5, False), (3, 16, 3, True), (8, 64, 3, False)])
+def test_subm_conv_direct(cin, cout, k, fuse, dtype):
+    data = small_batch([3000, 1200], 12)
+    batch = O.offset_to_batch(data["offset"])
+    ind = O.sparse_indices(batch, data["grid_coord"])
+    n = ind.shape[0]
+    g = torch.Generator().manual_seed(cin * 100 + cout)
+    feat = torch.randn(n, cin, generator=g).to(dtype)
+    w = (torch.randn(cout, k, k, k, cin, generator=g) / (k ** 3 * cin) ** 0.5 * 3).to(dtype)
+    ref = O.subm_conv(feat, O.kernel_map(ind, k), w, None)
+    scale = shift = None
+    if fuse:
+        scale = (1 + 0.1 * torch.randn(cout, generator=g))
+        shift = 0.1 * torch.randn(cout, generator=g)
+        ref = F.gelu((ref.float() * scale + shift).to(dtype))
+        scale, shift = scale.cuda(), shift.cuda()
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ["hilbert"])
+    for row_order in (None, order[0].cuda()):
+        got = ops.subm_conv_direct(feat.cuda(), ind.cuda(), w.cuda(), None, scale, shift, fuse, row_order)
+        assert_close(got, ref, what="direct conv", **TOL[dtype])
