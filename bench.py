@@ -274,6 +274,108 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+# --------------------------------------------------------------------------- #
+# single-operator cases (the smaller configurations): device timing + roofline
+# --------------------------------------------------------------------------- #
+def _time_device(fn, steps, warmup, flush):
+    for _ in range(max(warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    torch.cuda.profiler.start()
+    for a, b in ev:
+        if flush is not None:
+            flush.fill_(1)
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    return sum(a.elapsed_time(b) for a, b in ev) / steps
+
+
+def run_operator_case(args):
+    """--case serialization | attention | conv: one operator of the path on the
+    configuration BASELINE.json gives for it, timed on the device."""
+    from pointtransformerv3_b200 import ops, synthetic
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except OSError:
+        pass
+    hbm = peaks.get("hbm_gbs", 6650.0)
+    tf = peaks.get("bf16_tflops", 1590.0)
+    src = "measured" if peaks else "fallback"
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    orders = ["z", "z-trans", "hilbert", "hilbert-trans"]
+    out = {"case": args.case, "n_gpus": 1, "steps": args.steps, "data": "synthetic", "peak_source": src}
+    if args.case == "serialization":
+        n = args.points or 100_000
+        _, gc = synthetic.uniform_cloud(n, seed=0)
+        gc = gc.to(dev)
+        batch = torch.zeros(n, dtype=torch.int64, device=dev)
+        codes = ops.encode(gc, batch, 16, orders)
+        t_enc = _time_device(lambda: ops.encode(gc, batch, 16, orders), args.steps, args.warmup, flush)
+        t_sort = _time_device(lambda: ops.argsort_inverse(codes, 49), args.steps, args.warmup, flush)
+        enc_b, sort_b = 52.0 * n, 128.0 * n          # algorithmic bytes (see DESIGN.md)
+        out.update(config={"workload": "encode x4 orders + stable argsort + inverse, depth 16", "points": n},
+                   metric="serialization_points_per_sec", unit="points/s", value=n / ((t_enc + t_sort) * 1e-3),
+                   encode_ms=t_enc, argsort_inverse_ms=t_sort,
+                   roofline={"kernel": "encode_kernel", "bound": "hbm", "achieved": enc_b / t_enc / 1e6,
+                             "peak": hbm, "unit": "GB/s", "frac": enc_b / t_enc / 1e6 / hbm, "traffic": None},
+                   roofline_argsort={"kernel": "rs_* (all passes)", "bound": "hbm",
+                                     "achieved": sort_b / t_sort / 1e6, "peak": hbm, "unit": "GB/s",
+                                     "frac": sort_b / t_sort / 1e6 / hbm, "traffic": None})
+    elif args.case == "attention":
+        n, C, H, K = args.points or 120_000, 64, 4, 1024
+        g = torch.Generator().manual_seed(0)
+        gc = torch.randint(0, 512, (n, 3), generator=g, dtype=torch.int32).to(dev)
+        batch = torch.zeros(n, dtype=torch.int64, device=dev)
+        codes = ops.encode(gc, batch, 9, ["hilbert"])
+        order, _ = ops.argsort_inverse(codes, 28)
+        qkv = torch.randn(n, 3 * C, generator=g).bfloat16().to(dev)
+        pad, unpad, cu = ops.pad_plan(torch.tensor([n], device=dev), [n], K)
+        t = _time_device(lambda: ops.attention(qkv, order[0], pad, unpad, cu, H, K, 0.25), args.steps,
+                         args.warmup, flush)
+        flops = 4.0 * pad.numel() * K * C
+        out.update(config={"workload": "patch attention core, bf16, C=64, 4 heads, patch 1024", "points": n,
+                           "patches": cu.numel() - 1},
+                   metric="attention_points_per_sec", unit="points/s", value=n / (t * 1e-3), ms=t,
+                   exps_per_sec=pad.numel() * K * H / (t * 1e-3),
+                   roofline={"kernel": "attn_mma_d16_kernel", "bound": "tensor", "achieved": flops / t / 1e9,
+                             "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e9 / tf, "traffic": None})
+    elif args.case == "conv":
+        c = 128
+        coord, gc = synthetic.indoor_scene(0, args.points or 80_000, GRID)
+        n = gc.shape[0]
+        ind = torch.cat([torch.zeros(n, 1, dtype=torch.int32), gc], 1).contiguous().to(dev)
+        g = torch.Generator().manual_seed(0)
+        feat = torch.randn(n, c, generator=g).bfloat16().to(dev)
+        w = (torch.randn(c, 3, 3, 3, c, generator=g) / (9 * c) ** 0.5).bfloat16().to(dev)
+        b = torch.zeros(c).bfloat16().to(dev)
+        codes = ops.encode(gc.to(dev), torch.zeros(n, dtype=torch.int64, device=dev), 9, ["z"])
+        order, _ = ops.argsort_inverse(codes, 28)
+        t_map = _time_device(lambda: ops.kmap_build(ind, 3), args.steps, args.warmup, flush)
+        nbr = ops.kmap_build(ind, 3)
+        pairs = int((nbr >= 0).sum())
+        nbr = nbr.index_select(1, order[0])
+        t = _time_device(lambda: ops.subm_conv(feat, nbr, w, b, row_order=order[0]), args.steps, args.warmup,
+                         flush)
+        flops = 2.0 * pairs * c * c
+        out.update(config={"workload": "SubMConv3d 3x3x3, C=128, bf16, one indoor scene", "voxels": n,
+                           "pairs": pairs},
+                   metric="conv_voxels_per_sec", unit="voxels/s", value=n / (t * 1e-3), ms=t, kmap_ms=t_map,
+                   roofline={"kernel": "conv_mma_kernel", "bound": "tensor", "achieved": flops / t / 1e9,
+                             "peak": tf, "unit": "TFLOP/s (useful FLOPs: 2 x pairs x C^2)",
+                             "frac": flops / t / 1e9 / tf, "traffic": None},
+                   roofline_kmap={"kernel": "km_insert + km_probe", "bound": "hbm",
+                                  "achieved": 124.0 * n / t_map / 1e6, "peak": hbm, "unit": "GB/s",
+                                  "frac": 124.0 * n / t_map / 1e6 / hbm, "traffic": None})
+    print(json.dumps(out))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -282,8 +384,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv"],
+                    help="forward = the headline workload; the others time one operator of the path")
+    ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.case != "forward":
+        run_operator_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
