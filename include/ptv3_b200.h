@@ -109,7 +109,10 @@ int ptv3_pad_plan(const int64_t* offset, int n_scenes, int patch, int64_t n, int
  *   out         n x channels, every row written exactly once
  *   max_seqlen  longest patch (rows); head_dim = channels / heads in {8,16,32,64}
  *   dtype       PTV3_DTYPE_*; algo 0 = automatic, 1 = CUDA-core path,
- *               2 = tensor-core path (bf16 only)
+ *               2 = tensor-core path (bf16 only), 3 = tensor-core path with the
+ *               exponent arguments rounded to bf16 and two exps per instruction
+ *               (measured no faster on B200: the exp unit's rate per element
+ *               is the same; kept for comparison)
  */
 int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
                        const int64_t* unpad, const int32_t* cu_seqlens, void* out, int64_t n,
@@ -250,6 +253,21 @@ int ptv3_add_layernorm_fwd(const void* x, const void* residual, const void* ln1_
                            const void* ln1_bias, float ln1_eps, void* sum_out, const void* ln2_weight,
                            const void* ln2_bias, float ln2_eps, void* norm_out, int64_t n, int channels,
                            int dtype, void* stream);
+
+/*
+ * Fused MLP of a block: out = residual + fc2(GELU(fc1(x) + b1)) + b2, the hidden
+ * activation kept on chip (tcgen05 tensor cores, TMEM accumulators, TMA loads).
+ * Replaces MLP.forward and the residual addition, model.py:510-516, 601-602.
+ *   x, residual, out   n x channels bf16 (out may alias residual)
+ *   fc1_weight  hidden x channels, fc2_weight  channels x hidden (nn.Linear layout)
+ * ptv3_mlp_supported() tells whether a shape is covered (bf16, channels 32 or 64,
+ * hidden = 4 x channels); other shapes use separate GEMMs.
+ * A wait that exceeds its bound sets PTV3_STATUS_WAIT_LIMIT in *status.
+ */
+int ptv3_mlp_supported(int channels, int hidden, int dtype);
+int ptv3_mlp_fwd(const void* x, const void* fc1_weight, const void* fc1_bias, const void* fc2_weight,
+                 const void* fc2_bias, const void* residual, void* out, int64_t n, int channels,
+                 int hidden, int dtype, uint32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

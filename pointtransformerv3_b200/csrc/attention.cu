@@ -142,15 +142,15 @@ extern "C" int ptv3_attention_fwd(const void* qkv, const int64_t* order, const i
     if (n == 0 || n_seq == 0) return PTV3_OK;
     PTV3_REQUIRE(qkv && order && pad && unpad && cu_seqlens && out, PTV3_ERR_INVALID_ARGUMENT,
                  "ptv3_attention_fwd: null pointer");
-    PTV3_REQUIRE(algo >= 0 && algo <= 2, PTV3_ERR_INVALID_ARGUMENT, "ptv3_attention_fwd: algo %d", algo);
+    PTV3_REQUIRE(algo >= 0 && algo <= 3, PTV3_ERR_INVALID_ARGUMENT, "ptv3_attention_fwd: algo %d", algo);
     const bool mma_ok = dtype == PTV3_DTYPE_BF16 && attn_mma_supported(channels, heads, max_seqlen) &&
                         n_seq <= 2147483647 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)out & 3) == 0;
-    PTV3_REQUIRE(algo != 2 || mma_ok, PTV3_ERR_UNSUPPORTED,
+    PTV3_REQUIRE(algo < 2 || mma_ok, PTV3_ERR_UNSUPPORTED,
                  "ptv3_attention_fwd: the tensor-core path needs bf16, head dim 16, max_seqlen <= %d and "
                  "16-byte aligned qkv", ATTN_MMA_MAX_SEQLEN);
     if (mma_ok && algo != 1)
         return launch_attn_mma(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen, channels,
-                               heads, scale, (cudaStream_t)stream);
+                               heads, scale, algo == 3, (cudaStream_t)stream);
     if (dtype == PTV3_DTYPE_F32)
         return launch_attn_fma<float>(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen,
                                       channels, heads, scale, (cudaStream_t)stream);

@@ -41,6 +41,7 @@ __device__ __forceinline__ uint32_t scale_bf16x2(uint32_t v, float s)
     return pack_bf16(f.x * s, f.y * s);
 }
 
+template <bool PACKED>
 __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
     const __nv_bfloat16* __restrict__ qkv, const int64_t* __restrict__ order,
     const int64_t* __restrict__ pad, const int64_t* __restrict__ unpad,
@@ -122,6 +123,7 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
         }
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
         float o[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float osum[4] = {0.f, 0.f, 0.f, 0.f};   // PACKED: row sums from a ones column of V
 
         for (int kc = 0; kc < Lp; kc += AM_KC) {
             float s[8][4];
@@ -159,6 +161,8 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
             m1 = mn1;
             l0 *= c0;
             l1 *= c1;
+            osum[0] *= c0;
+            osum[2] *= c1;
 #pragma unroll
             for (int n = 0; n < 2; ++n) {
                 o[n][0] *= c0;
@@ -170,14 +174,21 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
             uint32_t pa[8][2];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                const float p0 = fast_exp2(fmaf(s[j][0], sl2, -b0));
-                const float p1 = fast_exp2(fmaf(s[j][1], sl2, -b0));
-                const float p2 = fast_exp2(fmaf(s[j][2], sl2, -b1));
-                const float p3 = fast_exp2(fmaf(s[j][3], sl2, -b1));
-                l0 += p0 + p1;
-                l1 += p2 + p3;
-                pa[j][0] = pack_bf16(p0, p1);
-                pa[j][1] = pack_bf16(p2, p3);
+                if (PACKED) {
+                    // exponent argument rounded to bf16, two exps per instruction, the result
+                    // already is the bf16 pair the next MMA consumes
+                    pa[j][0] = exp2_bf16x2(pack_bf16(fmaf(s[j][0], sl2, -b0), fmaf(s[j][1], sl2, -b0)));
+                    pa[j][1] = exp2_bf16x2(pack_bf16(fmaf(s[j][2], sl2, -b1), fmaf(s[j][3], sl2, -b1)));
+                } else {
+                    const float p0 = fast_exp2(fmaf(s[j][0], sl2, -b0));
+                    const float p1 = fast_exp2(fmaf(s[j][1], sl2, -b0));
+                    const float p2 = fast_exp2(fmaf(s[j][2], sl2, -b1));
+                    const float p3 = fast_exp2(fmaf(s[j][3], sl2, -b1));
+                    l0 += p0 + p1;
+                    l1 += p2 + p3;
+                    pa[j][0] = pack_bf16(p0, p1);
+                    pa[j][1] = pack_bf16(p2, p3);
+                }
             }
 #pragma unroll
             for (int kk = 0; kk < 4; ++kk) {
@@ -186,12 +197,19 @@ __global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
                 ldmatrix_x4_trans(vb, vs_base + kv_offset(kc + 16 * kk + v_row, v_chunk));
                 mma_bf16(o[0], a, vb[0], vb[1]);
                 mma_bf16(o[1], a, vb[2], vb[3]);
+                // a column of ones appended to V: the tensor core sums the rounded probabilities
+                if (PACKED) mma_bf16(osum, a, 0x3f803f80u, 0x3f803f80u);
             }
         }
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        if (PACKED) {
+            l0 = osum[0];
+            l1 = osum[2];
+        } else {
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+            l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+            l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        }
         if (ok0 && own0) {
             const float inv = 1.f / l0;
             uint32_t* op = reinterpret_cast<uint32_t*>(out + src0 * (int64_t)C + h * AM_D);
@@ -215,13 +233,14 @@ bool attn_mma_supported(int channels, int heads, int max_seqlen)
 
 int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, const int64_t* unpad,
                     const int32_t* cu, void* out, int n_seq, int max_seqlen, int C, int H, float scale,
-                    cudaStream_t stream)
+                    bool packed_exp, cudaStream_t stream)
 {
     const int lpad = (max_seqlen + AM_KC - 1) / AM_KC * AM_KC;
     const size_t smem = (size_t)lpad * 64;
     // per device and cheap, so it is simply repeated on every call
-    if (cudaFuncSetAttribute(attn_mma_d16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             ATTN_MMA_MAX_SEQLEN * 64) != cudaSuccess)
+    auto kern = packed_exp ? attn_mma_d16_kernel<true> : attn_mma_d16_kernel<false>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_MMA_MAX_SEQLEN * 64) !=
+        cudaSuccess)
         return check_launch("ptv3_attention_fwd: shared memory attribute");
     // slice the queries of a sequence over several CTAs when there are few (sequence, head) pairs
     int qsplit = 1;
@@ -229,7 +248,7 @@ int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, c
     const int tiles = (max_seqlen + 15) / 16;
     while (pairs * qsplit < 2 * 148 && qsplit * 2 * AM_WARPS <= tiles) qsplit *= 2;
     const dim3 grid(n_seq, H, qsplit);
-    attn_mma_d16_kernel<<<grid, AM_THREADS, smem, stream>>>(
+    kern<<<grid, AM_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad);
     count_launches(1);
     return check_launch("ptv3_attention_fwd");

@@ -10,6 +10,6 @@ constexpr int ATTN_MMA_MAX_SEQLEN = 2048;   // keys+values of one head: 128 KiB 
 bool attn_mma_supported(int channels, int heads, int max_seqlen);
 int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, const int64_t* unpad,
                     const int32_t* cu_seqlens, void* out, int n_seq, int max_seqlen, int channels,
-                    int heads, float scale, cudaStream_t stream);
+                    int heads, float scale, bool packed_exp, cudaStream_t stream);
 
 }  // namespace ptv3

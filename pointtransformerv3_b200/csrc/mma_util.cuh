@@ -58,4 +58,12 @@ __device__ __forceinline__ float fast_exp2(float x)
     return y;
 }
 
+// two base-2 exponentials of a packed bf16 pair in one instruction
+__device__ __forceinline__ uint32_t exp2_bf16x2(uint32_t x)
+{
+    uint32_t y;
+    asm("ex2.approx.ftz.bf16x2 %0, %1;\n" : "=r"(y) : "r"(x));
+    return y;
+}
+
 }  // namespace ptv3

@@ -231,8 +231,17 @@ class Block(PointModule):
         feat, normed = ops.add_layernorm(x, shortcut, self.cpe[2], self.norm1[0])
         x = self.attn.attend(point, normed)
         feat, normed = ops.add_layernorm(x, feat, None, self.norm2[0])
-        x = self.mlp[0](normed)
-        feat, _ = ops.add_layernorm(x, feat, None, None)
+        mlp = self.mlp[0]
+        if (mlp.fc1.bias is not None and mlp.fc2.bias is not None
+                and ops.mlp_supported(mlp.fc1.in_features, mlp.fc1.out_features, normed.dtype)
+                and mlp.fc2.out_features == mlp.fc1.in_features):
+            # both GEMMs, GELU and the residual in one tcgen05 kernel
+            feat = ops.mlp(normed, mlp.fc1.weight, mlp.fc1.bias, mlp.fc2.weight, mlp.fc2.bias, feat,
+                           point.device_status())
+            point.check_status("ptv3_mlp_fwd")
+        else:
+            x = mlp(normed)
+            feat, _ = ops.add_layernorm(x, feat, None, None)
         point.feat = feat
         point.sparse_conv_feat = sparse.replace_feature(feat)
         return point

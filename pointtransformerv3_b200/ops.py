@@ -317,3 +317,28 @@ def subm_conv_direct(feat, indices, weight, bias=None, bn_scale=None, bn_shift=N
     if own:
         _lib.raise_on_status(status, "ptv3_subm_conv_direct_fwd")
     return out
+
+
+def mlp_supported(channels, hidden, dtype):
+    return dtype in _lib.DTYPE_IDS and bool(_lib.load().ptv3_mlp_supported(channels, hidden, _lib.DTYPE_IDS[dtype]))
+
+
+def mlp(x, fc1_weight, fc1_bias, fc2_weight, fc2_bias, residual, status=None):
+    """out = residual + fc2(GELU(fc1(x))) in one kernel (see ptv3_mlp_fwd)."""
+    _lib.require_cuda(x, fc1_weight, fc2_weight, residual)
+    lib = _lib.load()
+    x, residual = x.contiguous(), residual.contiguous()
+    n, C = x.shape
+    hidden = fc1_weight.shape[0]
+    out = torch.empty_like(x)
+    own = status is None
+    if own:
+        status = new_status(x.device)
+    with timed("mlp", 4.0 * n * C * hidden):
+        _lib.check(lib.ptv3_mlp_fwd(_lib.ptr(x), _lib.ptr(fc1_weight.contiguous()), _lib.ptr(fc1_bias),
+                                    _lib.ptr(fc2_weight.contiguous()), _lib.ptr(fc2_bias), _lib.ptr(residual),
+                                    _lib.ptr(out), n, C, hidden, _lib.dtype_id(x), _lib.ptr(status),
+                                    _lib.stream()), "ptv3_mlp_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_mlp_fwd")
+    return out

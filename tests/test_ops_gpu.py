@@ -295,3 +295,22 @@ def test_subm_conv_direct(cin, cout, k, fuse, dtype):
     for row_order in (None, order[0].cuda()):
         got = ops.subm_conv_direct(feat.cuda(), ind.cuda(), w.cuda(), None, scale, shift, fuse, row_order)
         assert_close(got, ref, what="direct conv", **TOL[dtype])
+
+
+@pytest.mark.parametrize("C", [32, 64])
+@pytest.mark.parametrize("n", [128, 1000, 40_000])
+def test_fused_mlp_tcgen05(C, n):
+    """out = residual + fc2(GELU(fc1(x))) on the tcgen05 path against torch on CPU."""
+    g = torch.Generator().manual_seed(C + n)
+    x = torch.randn(n, C, generator=g).bfloat16()
+    res = torch.randn(n, C, generator=g).bfloat16()
+    w1 = (torch.randn(4 * C, C, generator=g) / C ** 0.5).bfloat16()
+    b1 = (0.1 * torch.randn(4 * C, generator=g)).bfloat16()
+    w2 = (torch.randn(C, 4 * C, generator=g) / (4 * C) ** 0.5).bfloat16()
+    b2 = (0.1 * torch.randn(C, generator=g)).bfloat16()
+    ref = res + F.linear(F.gelu(F.linear(x, w1, b1)), w2, b2)
+    ref32 = res.float() + F.linear(F.gelu(F.linear(x.float(), w1.float(), b1.float())), w2.float(), b2.float())
+    assert ops.mlp_supported(C, 4 * C, torch.bfloat16)
+    got = ops.mlp(x.cuda(), w1.cuda(), b1.cuda(), w2.cuda(), b2.cuda(), res.cuda())
+    assert_close(got, ref, what="fused mlp", **TOL[torch.bfloat16])
+    assert rel_l2(got, ref32) <= 1.5 * rel_l2(ref, ref32) + 1e-3
