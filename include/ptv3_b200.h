@@ -175,6 +175,29 @@ int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight,
                        int kernel_volume, int dtype, int algo, void* stream);
 
 /*
+ * Pair-list form of the submanifold convolution, for levels with few voxels and
+ * wide channels (the tensor-core path of ptv3_subm_conv_fwd multiplies a tile of
+ * output voxels by every offset that any of them has; on coarse levels most of
+ * those rows are zero).  ptv3_conv_pairs_build lists, offset by offset, the pairs
+ * (nbr[o][j], j) with nbr[o][j] >= 0; ptv3_subm_conv_pairs_fwd multiplies 128
+ * pairs of one offset at a time and accumulates in fp32 with atomics, so the
+ * summation order (and the last bit of the result) can differ between runs.
+ * Replaces spconv's gather-GEMM-scatter behind model.py:546-552.
+ *   nbr, row_order   as for ptv3_subm_conv_fwd (pair_out = row_order[j] when given)
+ *   pair_in/out      kernel_volume * n int32 each (upper bound)
+ *   off_start, tile_start   kernel_volume + 1 int32 each (device)
+ *   workspace (conv) n x c_out floats
+ */
+size_t ptv3_conv_pairs_workspace_bytes(int64_t n, int kernel_volume);
+int ptv3_conv_pairs_build(const int32_t* nbr, const int64_t* row_order, int64_t n, int kernel_volume,
+                          int32_t* pair_in, int32_t* pair_out, int32_t* off_start, int32_t* tile_start,
+                          void* workspace, size_t workspace_bytes, void* stream);
+int ptv3_subm_conv_pairs_fwd(const void* feat, const int32_t* pair_in, const int32_t* pair_out,
+                             const int32_t* off_start, const int32_t* tile_start, const void* weight,
+                             const void* bias, void* out, void* workspace, size_t workspace_bytes,
+                             int64_t n, int c_in, int c_out, int kernel_volume, int dtype, void* stream);
+
+/*
  * Submanifold convolution with few input channels and a large kernel, without a
  * kernel map: the voxel hash table is built in `workspace` and probed inside
  * the convolution.  Replaces the stem of model.py:766-779 (SubMConv3d 5x5x5,

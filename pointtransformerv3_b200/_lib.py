@@ -33,6 +33,10 @@ SIGNATURES = {
     "ptv3_kmap_build_static": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr]),
     "ptv3_subm_conv_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int,
                                    c_int, c_int, c_ptr]),
+    "ptv3_conv_pairs_workspace_bytes": (c_sz, [c_i64, c_int]),
+    "ptv3_conv_pairs_build": (c_int, [c_ptr, c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+    "ptv3_subm_conv_pairs_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_sz,
+                                         c_i64, c_int, c_int, c_int, c_int, c_ptr]),
     "ptv3_subm_conv_direct_workspace_bytes": (c_sz, [c_i64, c_int]),
     "ptv3_subm_conv_direct_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_i64,
                                           c_int, c_int, c_int, c_int, c_ptr, c_ptr, c_sz, c_ptr]),

@@ -33,12 +33,25 @@ __device__ __forceinline__ int swz(int r, int c)
 
 // CM_TM: voxels per CTA; CN: output channels per CTA; KC: input channels per
 // stage; WM x WN warps
-template <int CM_TM, int CN, int KC, int WM, int WN>
+// PAIRS: instead of 128 output voxels and all their offsets, a CTA owns 128
+// (input row, output row) pairs of ONE offset from an offset-sorted pair list and
+// adds its products into an fp32 buffer with atomics (no zero rows are multiplied;
+// used for the coarse levels, where tiles are not planar and most of the 27
+// offsets of an output-stationary tile would be half empty).
+struct PairList {
+    const int32_t* pair_in;     // input row of every pair, sorted by offset
+    const int32_t* pair_out;    // output row of every pair
+    const int32_t* off_start;   // kvol + 1: first pair of every offset
+    const int32_t* tile_start;  // kvol + 1: first 128-pair tile of every offset
+    float* out32;               // n x cout accumulation buffer (zeroed by the launcher)
+};
+
+template <int CM_TM, int CN, int KC, int WM, int WN, bool PAIRS>
 __global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
     const __nv_bfloat16* __restrict__ feat, const int32_t* __restrict__ nbr,
     const __nv_bfloat16* __restrict__ weight, const __nv_bfloat16* __restrict__ bias,
     __nv_bfloat16* __restrict__ out, const int64_t* __restrict__ row_order, int64_t n, int cin,
-    int cout, int kvol)
+    int cout, int kvol, PairList pl)
 {
     constexpr int CM_THREADS = WM * WN * 32;
     constexpr int NCH = KC / 8;              // 16-byte chunks per staged row
@@ -61,33 +74,52 @@ __global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
     const int64_t row0 = (int64_t)blockIdx.x * CM_TM;
     const int col0 = blockIdx.y * CN;
 
-    // ---- voxels of this tile and their neighbour rows ----------------------
-    if (tid < CM_TM) {
-        const int64_t i = row0 + tid;
-        rows_s[tid] = i < n ? (row_order ? row_order[i] : i) : -1;
-    }
-    __syncthreads();
-    for (int idx = tid; idx < kvol * CM_TM; idx += CM_THREADS) {
-        const int o = idx / CM_TM, r = idx % CM_TM;
-        nbr_s[idx] = row0 + r < n ? nbr[(int64_t)o * n + row0 + r] : -1;
-    }
-    __syncthreads();
-    // offsets with at least one neighbour in the tile, in ascending order
-    for (int o = warp; o < kvol; o += CM_THREADS / 32) {
-        bool any = false;
+    if (PAIRS) {
+        // which offset this tile of pairs belongs to
+        const int tile = blockIdx.x;
+        if (tile >= pl.tile_start[kvol]) return;
+        int o = 0;
+        while (o + 1 < kvol && pl.tile_start[o + 1] <= tile) ++o;
+        const int p0 = pl.off_start[o] + (tile - pl.tile_start[o]) * CM_TM;
+        const int cnt = min(CM_TM, pl.off_start[o + 1] - p0);
+        if (tid < CM_TM) {
+            rows_s[tid] = tid < cnt ? pl.pair_out[p0 + tid] : -1;
+            nbr_s[tid] = tid < cnt ? pl.pair_in[p0 + tid] : -1;
+        }
+        if (tid == 0) {
+            act[0] = 1;
+            act[1] = o;
+        }
+        __syncthreads();
+    } else {
+        // ---- voxels of this tile and their neighbour rows ----------------------
+        if (tid < CM_TM) {
+            const int64_t i = row0 + tid;
+            rows_s[tid] = i < n ? (row_order ? row_order[i] : i) : -1;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < kvol * CM_TM; idx += CM_THREADS) {
+            const int o = idx / CM_TM, r = idx % CM_TM;
+            nbr_s[idx] = row0 + r < n ? nbr[(int64_t)o * n + row0 + r] : -1;
+        }
+        __syncthreads();
+        // offsets with at least one neighbour in the tile, in ascending order
+        for (int o = warp; o < kvol; o += CM_THREADS / 32) {
+            bool any = false;
 #pragma unroll
-        for (int r = lane; r < CM_TM; r += 32) any |= nbr_s[o * CM_TM + r] >= 0;
-        const unsigned b = __ballot_sync(0xffffffffu, any);
-        if (lane == 0) act[1 + o] = b != 0;
+            for (int r = lane; r < CM_TM; r += 32) any |= nbr_s[o * CM_TM + r] >= 0;
+            const unsigned b = __ballot_sync(0xffffffffu, any);
+            if (lane == 0) act[1 + o] = b != 0;
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int c = 0;
+            for (int o = 0; o < kvol; ++o)
+                if (act[1 + o]) act[1 + c++] = o;
+            act[0] = c;
+        }
+        __syncthreads();
     }
-    __syncthreads();
-    if (tid == 0) {
-        int c = 0;
-        for (int o = 0; o < kvol; ++o)
-            if (act[1 + o]) act[1 + c++] = o;
-        act[0] = c;
-    }
-    __syncthreads();
     const int n_act = act[0];
     const int kchunks = cin / KC;
     const int nit = n_act * kchunks;
@@ -105,7 +137,7 @@ __global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
         const uint32_t b_base = smem_u32(Bs + buf * B_BYTES);
         for (int idx = tid; idx < CM_TM * NCH; idx += CM_THREADS) {
             const int r = idx / NCH, c = idx % NCH;
-            const int32_t src = nbr_s[o * CM_TM + r];
+            const int32_t src = nbr_s[(PAIRS ? 0 : o) * CM_TM + r];
             const uint32_t dst = a_base + r * ROWB + swz<NCH>(r, c) * 16;
             if (src >= 0) {
                 cp_async16(dst, feat + (int64_t)src * cin + kc + c * 8);
@@ -171,6 +203,15 @@ __global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
             const int r = wm * WTM + a * 16 + g + half * 8;
             const int64_t v = rows_s[r];
             if (v < 0) continue;
+            if (PAIRS) {
+                float* op32 = pl.out32 + v * (int64_t)cout + col0 + wn * WTN;
+#pragma unroll
+                for (int b = 0; b < NT; ++b)
+                    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(op32 + b * 8 + 2 * t),
+                                 "f"(acc[a][b][half * 2]), "f"(acc[a][b][half * 2 + 1])
+                                 : "memory");
+                continue;
+            }
             __nv_bfloat16* op = out + v * (int64_t)cout + col0 + wn * WTN;
 #pragma unroll
             for (int b = 0; b < NT; ++b) {
@@ -205,15 +246,64 @@ static int launch_one(const void* feat, const int32_t* nbr, const void* weight, 
                       const int64_t* row_order, int64_t n, int cin, int cout, int kvol, cudaStream_t stream)
 {
     constexpr size_t smem = conv_mma_smem<CM_TM, CN, KC>();
-    auto kern = conv_mma_kernel<CM_TM, CN, KC, WM, WN>;
+    auto kern = conv_mma_kernel<CM_TM, CN, KC, WM, WN, false>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_subm_conv_fwd: shared memory attribute");
     const dim3 grid((unsigned)((n + CM_TM - 1) / CM_TM), cout / CN);
     kern<<<grid, WM * WN * 32, smem, stream>>>((const __nv_bfloat16*)feat, nbr, (const __nv_bfloat16*)weight,
                                              (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, row_order, n,
-                                             cin, cout, kvol);
+                                             cin, cout, kvol, PairList{});
     count_launches(1);
     return check_launch("ptv3_subm_conv_fwd");
+}
+
+// out = bf16(out32 + bias)
+__global__ void __launch_bounds__(256) conv_pairs_finalize_kernel(const float* __restrict__ acc,
+                                                                  const __nv_bfloat16* __restrict__ bias,
+                                                                  __nv_bfloat16* __restrict__ out, int64_t total,
+                                                                  int cout)
+{
+    const int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4;
+    if (i >= total) return;
+    const float4 v = *reinterpret_cast<const float4*>(acc + i);
+    const int c = (int)(i % cout);
+    float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
+    if (bias) {
+        b0 = __bfloat162float(bias[c]);
+        b1 = __bfloat162float(bias[c + 1]);
+        b2 = __bfloat162float(bias[c + 2]);
+        b3 = __bfloat162float(bias[c + 3]);
+    }
+    uint2 o;
+    o.x = pack_bf16(v.x + b0, v.y + b1);
+    o.y = pack_bf16(v.z + b2, v.w + b3);
+    *reinterpret_cast<uint2*>(out + i) = o;
+}
+
+bool conv_pairs_supported(int c_in, int c_out, int kernel_volume)
+{
+    return kernel_volume <= CM_MAX_KVOL && c_in % 64 == 0 && c_out % 128 == 0;
+}
+
+int launch_conv_pairs(const void* feat, const int32_t* pair_in, const int32_t* pair_out,
+                      const int32_t* off_start, const int32_t* tile_start, int64_t max_tiles,
+                      const void* weight, const void* bias, void* out, float* out32, int64_t n, int c_in,
+                      int c_out, int kvol, cudaStream_t stream)
+{
+    constexpr size_t smem = conv_mma_smem<128, 128, 64>();
+    auto kern = conv_mma_kernel<128, 128, 64, 4, 2, true>;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        return check_launch("ptv3_subm_conv_pairs_fwd: shared memory attribute");
+    cudaMemsetAsync(out32, 0, (size_t)n * c_out * sizeof(float), stream);
+    const PairList pl{pair_in, pair_out, off_start, tile_start, out32};
+    kern<<<dim3((unsigned)max_tiles, c_out / 128), 256, smem, stream>>>(
+        (const __nv_bfloat16*)feat, nullptr, (const __nv_bfloat16*)weight, nullptr, nullptr, nullptr, n, c_in,
+        c_out, kvol, pl);
+    const int64_t total = n * (int64_t)c_out;
+    conv_pairs_finalize_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(
+        out32, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, total, c_out);
+    count_launches(2);
+    return check_launch("ptv3_subm_conv_pairs_fwd");
 }
 
 int launch_conv_mma(const void* feat, const int32_t* nbr, const void* weight, const void* bias, void* out,

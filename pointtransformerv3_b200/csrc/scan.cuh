@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(SC_THREADS) scan_tile_sums_kernel(Flag flag, i
 }
 
 // in-place exclusive scan of tile_sums[row][0..ntiles); totals[row] = sum
-__global__ void __launch_bounds__(SC_THREADS) scan_sums_kernel(uint32_t* __restrict__ tile_sums,
+static __global__ void __launch_bounds__(SC_THREADS) scan_sums_kernel(uint32_t* __restrict__ tile_sums,
                                                               int ntiles,
                                                               uint32_t* __restrict__ totals)
 {

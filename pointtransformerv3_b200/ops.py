@@ -342,3 +342,42 @@ def mlp(x, fc1_weight, fc1_bias, fc2_weight, fc2_bias, residual, status=None):
     if own:
         _lib.raise_on_status(status, "ptv3_mlp_fwd")
     return out
+
+
+def conv_pairs_build(nbr, row_order=None):
+    """Offset-sorted (input row, output row) pair list of a neighbour table.
+    Returns dict(pair_in, pair_out, off_start, tile_start) of device tensors."""
+    _lib.require_cuda(nbr, row_order)
+    lib = _lib.load()
+    kvol, n = nbr.shape
+    dev = nbr.device
+    i32 = dict(dtype=torch.int32, device=dev)
+    pair_in = torch.empty(kvol * n, **i32)
+    pair_out = torch.empty(kvol * n, **i32)
+    off_start = torch.empty(kvol + 1, **i32)
+    tile_start = torch.empty(kvol + 1, **i32)
+    nbytes = lib.ptv3_conv_pairs_workspace_bytes(n, kvol)
+    ws = _lib.workspace(nbytes, dev)
+    _lib.check(lib.ptv3_conv_pairs_build(_lib.ptr(nbr), _lib.ptr(row_order), n, kvol, _lib.ptr(pair_in),
+                                         _lib.ptr(pair_out), _lib.ptr(off_start), _lib.ptr(tile_start),
+                                         _lib.ptr(ws), nbytes, _lib.stream()), "ptv3_conv_pairs_build")
+    return dict(pair_in=pair_in, pair_out=pair_out, off_start=off_start, tile_start=tile_start, n=n, kvol=kvol)
+
+
+def subm_conv_pairs(feat, pairs, weight, bias=None):
+    """Submanifold convolution over a pair list (bf16, coarse levels)."""
+    _lib.require_cuda(feat, weight, bias)
+    lib = _lib.load()
+    feat = feat.contiguous()
+    n, cin = feat.shape
+    cout = weight.shape[0]
+    out = torch.empty((n, cout), dtype=feat.dtype, device=feat.device)
+    nbytes = n * cout * 4
+    ws = _lib.workspace(nbytes, feat.device)
+    with timed("subm_conv_pairs", 2.0 * n * pairs["kvol"] * cin * cout):
+        _lib.check(lib.ptv3_subm_conv_pairs_fwd(
+            _lib.ptr(feat), _lib.ptr(pairs["pair_in"]), _lib.ptr(pairs["pair_out"]), _lib.ptr(pairs["off_start"]),
+            _lib.ptr(pairs["tile_start"]), _lib.ptr(weight.contiguous()), _lib.ptr(bias), _lib.ptr(out),
+            _lib.ptr(ws), nbytes, n, cin, cout, pairs["kvol"], _lib.dtype_id(feat), _lib.stream()),
+            "ptv3_subm_conv_pairs_fwd")
+    return out

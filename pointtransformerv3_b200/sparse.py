@@ -10,6 +10,11 @@ import torch.nn as nn
 from . import ops
 
 
+# largest level handled by the pair-list convolution (its fp32 accumulation buffer
+# and pair arrays stay small, and above this size output-stationary tiles win)
+PAIR_PATH_MAX_VOXELS = 65536
+
+
 class SparseConvTensor:
     """features (N,C), indices (N,4) int32 rows (batch, x, y, z).  Kernel maps
     are cached in ``indice_dict`` under ``(indice_key, kernel_size)`` and shared
@@ -50,6 +55,17 @@ class SparseConvTensor:
         if indice_key is not None:
             self.indice_dict[key] = entry
         return entry
+
+    def pair_list(self, kernel_size, indice_key=None):
+        """Offset-sorted pair list of the kernel map (built once per key)."""
+        key = (indice_key, kernel_size, "pairs")
+        if indice_key is not None and key in self.indice_dict:
+            return self.indice_dict[key]
+        nbr, row_order = self.kernel_map(kernel_size, indice_key)
+        pairs = ops.conv_pairs_build(nbr, row_order)
+        if indice_key is not None:
+            self.indice_dict[key] = pairs
+        return pairs
 
 
 class SparseModule(nn.Module):
@@ -100,6 +116,12 @@ class SubMConv3d(SparseModule):
                 _lib.raise_on_status(x.status, "ptv3_subm_conv_direct_fwd")
             return x.replace_feature(out)
         assert bn_scale is None and not gelu
+        n = x.features.shape[0]
+        # coarse levels (few voxels, wide channels): multiply only the pairs that exist
+        if (x.features.dtype == torch.bfloat16 and self.kernel_size == 3 and n <= PAIR_PATH_MAX_VOXELS
+                and self.in_channels % 64 == 0 and self.out_channels % 128 == 0 and self.in_channels >= 128):
+            pairs = x.pair_list(self.kernel_size, self.indice_key)
+            return x.replace_feature(ops.subm_conv_pairs(x.features, pairs, self.weight, self.bias))
         nbr, row_order = x.kernel_map(self.kernel_size, self.indice_key)
         return x.replace_feature(ops.subm_conv(x.features, nbr, self.weight, self.bias, row_order=row_order))
 

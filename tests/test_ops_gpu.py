@@ -314,3 +314,40 @@ def test_fused_mlp_tcgen05(C, n):
     got = ops.mlp(x.cuda(), w1.cuda(), b1.cuda(), w2.cuda(), b2.cuda(), res.cuda())
     assert_close(got, ref, what="fused mlp", **TOL[torch.bfloat16])
     assert rel_l2(got, ref32) <= 1.5 * rel_l2(ref, ref32) + 1e-3
+
+
+@pytest.mark.parametrize("c", [128, 256])
+@pytest.mark.parametrize("permuted", [False, True])
+def test_subm_conv_pair_list_path(c, permuted):
+    """Pair-list convolution (atomic fp32 accumulation) against the fp32 oracle, and
+    the structure of the pair list itself."""
+    data = small_batch([2000, 900], 14)
+    batch = O.offset_to_batch(data["offset"])
+    ind = O.sparse_indices(batch, data["grid_coord"] >> 2)
+    ind = torch.unique(ind, dim=0)
+    n = ind.shape[0]
+    g = torch.Generator().manual_seed(c)
+    feat = torch.randn(n, c, generator=g).bfloat16()
+    w = (torch.randn(c, 3, 3, 3, c, generator=g) / (9 * c) ** 0.5).bfloat16()
+    b = (torch.randn(c, generator=g) * 0.1).bfloat16()
+    ref_nbr = O.kernel_map(ind, 3)
+    ref = O.subm_conv(feat.float(), ref_nbr, w.float(), b.float())
+    nbr = ops.kmap_build(ind.cuda(), 3)
+    row_order = None
+    if permuted:
+        code, order, inverse, depth = O.serialization(ind[:, 1:], ind[:, 0].long(), ["z"])
+        row_order = order[0].cuda()
+        nbr = nbr.index_select(1, row_order)
+    pairs = ops.conv_pairs_build(nbr, row_order)
+    off = pairs["off_start"].cpu().tolist()
+    tiles = pairs["tile_start"].cpu().tolist()
+    counts = (ref_nbr >= 0).sum(0).tolist()
+    assert [off[i + 1] - off[i] for i in range(27)] == counts
+    assert [tiles[i + 1] - tiles[i] for i in range(27)] == [(c_ + 127) // 128 for c_ in counts]
+    pin, pout = pairs["pair_in"].cpu()[: off[27]].long(), pairs["pair_out"].cpu()[: off[27]].long()
+    for o in (0, 13, 26):
+        sl = slice(off[o], off[o + 1])
+        assert torch.equal(ref_nbr[pout[sl], o], pin[sl])
+    got = ops.subm_conv_pairs(feat.cuda(), pairs, w.cuda(), b.cuda())
+    assert_close(got, ref, what="pair-list conv", **TOL[torch.bfloat16])
+    assert rel_l2(got, ref) < 4e-3
