@@ -204,7 +204,7 @@ int ptv3_subm_conv_pairs_fwd(const void* feat, const int32_t* pair_in, const int
  * bias=False) and, optionally, the BatchNorm1d(eval) + GELU that follow it
  * (model.py:776-779).
  *   indices     n x 4 int32 (batch, x, y, z) as for ptv3_kmap_build
- *   weight      c_out x ksize^3 x c_in; c_in <= 8; c_out in {16, 32, 48, 64}
+ *   weight      c_out x ksize^3 x c_in; ksize in {1, 3, 5}; c_in <= 8; c_out in {16, 32, 48, 64}
  *   bias        c_out or NULL; bn_scale/bn_shift fp32 per channel or both NULL
  *   apply_gelu  non-zero: exact GELU after the (optional) normalisation
  *   row_order   optional voxel permutation used to group voxels into tiles

@@ -3,10 +3,12 @@
 // convolution (125 x N int32) is several times larger than its input and its
 // output, so the voxel hash table is probed inside the convolution instead.
 //
-// A CTA owns 128 voxels and walks the kernel offsets 25 at a time.  In each
-// round its 256 threads probe the hash table for 25 x 128 neighbour coordinates
-// and gather the features of the neighbours found into shared memory (all
-// probes and gathers of a round are independent, so their latencies overlap);
+// The voxels are indexed in two levels: a hash table of 4 x 4 x 4 blocks whose
+// values point at 64-entry cell tables (cell -> row).  A CTA owns 128 voxels:
+// each voxel first looks up the (at most 8) blocks its neighbourhood touches,
+// then the kernel offsets are walked 25 at a time; in each round the 256 threads
+// read 25 x 128 neighbour rows from the cell tables and gather the features of
+// the neighbours found into shared memory (all independent, latencies overlap);
 // then thread (voxel, half) accumulates half of the output channels in fp32
 // registers, reading the weights (staged once per CTA) as warp-wide broadcasts
 // and skipping absent neighbours.
@@ -30,6 +32,94 @@ __device__ __forceinline__ float cd_gelu(float x)
 
 constexpr int CD_CHUNK = 25;   // kernel offsets staged per round
 
+// ---- two-level voxel index: hash of 4x4x4 blocks -> 64-entry cell tables ----------
+// A (2r+1)^3 neighbourhood with r <= 3 touches at most 2 blocks per axis, so a voxel
+// needs 8 hash probes instead of one per kernel offset; each offset then costs a
+// few integer operations and one load from a 256-byte cell table.
+constexpr uint32_t CD_NO_ROW = 0xffffffffu;
+
+__device__ __forceinline__ bool cd_block_key(int b, int bx, int by, int bz, uint64_t& key)
+{
+    if ((unsigned)b > 0xfffeu || (unsigned)bx > 0x3fffu || (unsigned)by > 0x3fffu || (unsigned)bz > 0x3fffu)
+        return false;
+    key = ((uint64_t)b << 48) | ((uint64_t)bx << 32) | ((uint64_t)by << 16) | (uint64_t)bz;
+    return true;
+}
+
+// every voxel claims its block: the first claimant takes the next table and clears it
+__global__ void __launch_bounds__(256) cd_block_insert_kernel(const int32_t* __restrict__ indices, int64_t n,
+                                                              unsigned long long* __restrict__ keys,
+                                                              uint32_t* __restrict__ vals, uint64_t cap_mask,
+                                                              uint32_t* __restrict__ counter,
+                                                              uint32_t* __restrict__ cells,
+                                                              uint32_t* __restrict__ status)
+{
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int4 v = reinterpret_cast<const int4*>(indices)[i];
+    uint64_t key;
+    if ((unsigned)v.y > 0xffffu || (unsigned)v.z > 0xffffu || (unsigned)v.w > 0xffffu ||
+        !cd_block_key(v.x, v.y >> 2, v.z >> 2, v.w >> 2, key)) {
+        atomicOr(status, PTV3_STATUS_BAD_INDEX);
+        return;
+    }
+    uint64_t slot = km_mix(key) & cap_mask;
+    for (uint64_t probe = 0; probe <= cap_mask; ++probe) {
+        const unsigned long long prev = atomicCAS(&keys[slot], KM_EMPTY, key);
+        if (prev == KM_EMPTY) {
+            const uint32_t id = atomicAdd(counter, 1u);
+            uint4* tab = reinterpret_cast<uint4*>(cells + (size_t)id * 64);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) tab[q] = make_uint4(CD_NO_ROW, CD_NO_ROW, CD_NO_ROW, CD_NO_ROW);
+            __threadfence();
+            vals[slot] = id;
+            return;
+        }
+        if (prev == key) return;
+        slot = (slot + 1) & cap_mask;
+    }
+    atomicOr(status, PTV3_STATUS_PROBE_LIMIT);
+}
+
+__device__ __forceinline__ uint32_t cd_block_lookup(const unsigned long long* __restrict__ keys,
+                                                    const uint32_t* __restrict__ vals, uint64_t cap_mask,
+                                                    uint64_t key, bool* overflow)
+{
+    uint64_t slot = km_mix(key) & cap_mask;
+    for (uint64_t probe = 0; probe <= cap_mask; ++probe) {
+        const unsigned long long kk = keys[slot];
+        if (kk == key) return vals[slot];
+        if (kk == KM_EMPTY) return CD_NO_ROW;
+        slot = (slot + 1) & cap_mask;
+    }
+    *overflow = true;
+    return CD_NO_ROW;
+}
+
+// second pass (all tables exist now): every voxel writes its row into its cell;
+// duplicates resolve to the lowest row
+__global__ void __launch_bounds__(256) cd_cell_fill_kernel(const int32_t* __restrict__ indices, int64_t n,
+                                                           const unsigned long long* __restrict__ keys,
+                                                           const uint32_t* __restrict__ vals, uint64_t cap_mask,
+                                                           uint32_t* __restrict__ cells,
+                                                           uint32_t* __restrict__ status)
+{
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int4 v = reinterpret_cast<const int4*>(indices)[i];
+    uint64_t key;
+    if ((unsigned)v.y > 0xffffu || (unsigned)v.z > 0xffffu || (unsigned)v.w > 0xffffu ||
+        !cd_block_key(v.x, v.y >> 2, v.z >> 2, v.w >> 2, key))
+        return;
+    bool overflow = false;
+    const uint32_t id = cd_block_lookup(keys, vals, cap_mask, key, &overflow);
+    if (id == CD_NO_ROW) {
+        atomicOr(status, overflow ? PTV3_STATUS_PROBE_LIMIT : PTV3_STATUS_BAD_INDEX);
+        return;
+    }
+    atomicMin(&cells[(size_t)id * 64 + ((v.y & 3) << 4 | (v.z & 3) << 2 | (v.w & 3))], (uint32_t)i);
+}
+
 // [cout][kvol][cin] -> [kvol][cin][cout], once per call (a few thousand elements)
 template <typename T>
 __global__ void conv_direct_transpose_kernel(const T* __restrict__ w, T* __restrict__ wt, int cout,
@@ -49,7 +139,7 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_kernel(
     const T* __restrict__ bias, const float* __restrict__ bn_scale, const float* __restrict__ bn_shift,
     int apply_gelu, T* __restrict__ out, const int64_t* __restrict__ row_order, int64_t n, int cin,
     int ksize, const unsigned long long* __restrict__ keys, const uint32_t* __restrict__ vals,
-    uint64_t cap_mask, uint32_t* __restrict__ status)
+    uint64_t cap_mask, const uint32_t* __restrict__ cells, uint32_t* __restrict__ status)
 {
     extern __shared__ __align__(16) unsigned char smem[];
     const int kvol = ksize * ksize * ksize;
@@ -59,19 +149,19 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_kernel(
     unsigned char* has_s = smem + (size_t)CD_CHUNK * CD_TM * CD_MAX_CIN * sizeof(T);   // [CD_CHUNK][128]
     T* w_s = reinterpret_cast<T*>(has_s + CD_CHUNK * CD_TM);                            // kvol x cin x cout
     __shared__ int4 coord_s[CD_TM];
-    __shared__ char4 delta_s[343];   // (dx, dy, dz) of every kernel offset (runtime division once per CTA)
+    __shared__ uint32_t block_s[8][CD_TM];   // table id of the 2 x 2 x 2 blocks around each voxel
+    __shared__ char4 delta_s[343];           // (dx, dy, dz) of every kernel offset
 
     const int tid = threadIdx.x;
     const int v = tid % CD_TM, half = tid / CD_TM;
     const int64_t i = (int64_t)blockIdx.x * CD_TM + v;
     const int64_t row = i < n ? (row_order ? row_order[i] : i) : -1;
-    if (half == 0) coord_s[v] = row >= 0 ? reinterpret_cast<const int4*>(indices)[row] : make_int4(-1, 0, 0, 0);
-
-    for (int o = tid; o < kvol; o += CD_THREADS) {
-        const int rr = ksize / 2;
-        delta_s[o] = make_char4((char)(o / (ksize * ksize) - rr), (char)((o / ksize) % ksize - rr),
-                                (char)(o % ksize - rr), 0);
-    }
+    const int r = ksize / 2;
+    const int4 c = row >= 0 ? reinterpret_cast<const int4*>(indices)[row] : make_int4(-1, 0, 0, 0);
+    if (half == 0) coord_s[v] = c;
+    for (int o = tid; o < kvol; o += CD_THREADS)
+        delta_s[o] = make_char4((char)(o / (ksize * ksize) - r), (char)((o / ksize) % ksize - r),
+                                (char)(o % ksize - r), 0);
     // weights, already transposed to [kvol][cin][cout]: straight 16-byte copy
     {
         const int nvec = kvol * cin * cout / Vec<T>::N;
@@ -79,30 +169,45 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_kernel(
         typename Vec<T>::Raw* dst = reinterpret_cast<typename Vec<T>::Raw*>(w_s);
         for (int idx = tid; idx < nvec; idx += CD_THREADS) dst[idx] = src[idx];
     }
+    // the 8 candidate blocks of this voxel: 4 probes per thread
+    bool overflow = false;
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        const int bi = half * 4 + q;   // bit 2: x, bit 1: y, bit 0: z  (0 = block of coord - r)
+        uint32_t id = CD_NO_ROW;
+        if (c.x >= 0) {
+            const int bx = ((c.y - r) >> 2) + ((bi >> 2) & 1);
+            const int by = ((c.z - r) >> 2) + ((bi >> 1) & 1);
+            const int bz = ((c.w - r) >> 2) + (bi & 1);
+            uint64_t key;
+            if (cd_block_key(c.x, bx, by, bz, key)) id = cd_block_lookup(keys, vals, cap_mask, key, &overflow);
+        }
+        block_s[bi][v] = id;
+    }
     __syncthreads();
 
-    bool overflow = false;
     float acc[CO];
 #pragma unroll
     for (int k = 0; k < CO; ++k) acc[k] = 0.f;
 
     for (int o0 = 0; o0 < kvol; o0 += CD_CHUNK) {
         const int no = min(CD_CHUNK, kvol - o0);
-        // probe + gather: one (offset, voxel) pair per thread and step, all independent
+        // neighbour row from the cell tables + feature gather; all independent
         for (int idx = tid; idx < no * CD_TM; idx += CD_THREADS) {
             const int ol = idx / CD_TM, vv = idx % CD_TM;
-            const int o = o0 + ol;
-            const int4 c = coord_s[vv];
-            int32_t j = -1;
-            if (c.x >= 0) {
-                const char4 d = delta_s[o];
-                uint64_t key;
-                if (km_key(c.x, c.y + d.x, c.z + d.y, c.w + d.z, key))
-                    j = km_lookup(keys, vals, cap_mask, key, &overflow);
+            const int4 cc = coord_s[vv];
+            const char4 d = delta_s[o0 + ol];
+            uint32_t j = CD_NO_ROW;
+            if (cc.x >= 0) {
+                const int x = cc.y + d.x, y = cc.z + d.y, z = cc.w + d.z;
+                const int bi = (((x >> 2) - ((cc.y - r) >> 2)) << 2) | (((y >> 2) - ((cc.z - r) >> 2)) << 1) |
+                               ((z >> 2) - ((cc.w - r) >> 2));
+                const uint32_t id = block_s[bi][vv];
+                if (id != CD_NO_ROW) j = cells[(size_t)id * 64 + ((x & 3) << 4 | (y & 3) << 2 | (z & 3))];
             }
             T* dst = x_s + ((size_t)ol * CD_TM + vv) * CD_MAX_CIN;
-            has_s[ol * CD_TM + vv] = j >= 0;
-            if (j >= 0) {
+            has_s[ol * CD_TM + vv] = j != CD_NO_ROW;
+            if (j != CD_NO_ROW) {
                 const T* src = feat + (int64_t)j * cin;
 #pragma unroll
                 for (int ci = 0; ci < CD_MAX_CIN; ++ci) dst[ci] = ci < cin ? src[ci] : from_f<T>(0.f);
@@ -160,7 +265,7 @@ static int launch_conv_direct(const void* feat, const int32_t* indices, const vo
                               const float* bn_scale, const float* bn_shift, int apply_gelu, void* out,
                               const int64_t* row_order, int64_t n, int cin, int cout, int ksize,
                               const unsigned long long* keys, const uint32_t* vals, uint64_t cap_mask,
-                              uint32_t* status, void* wt, cudaStream_t stream)
+                              const uint32_t* cells, uint32_t* status, void* wt, cudaStream_t stream)
 {
     const int kvol = ksize * ksize * ksize;
     conv_direct_transpose_kernel<T><<<(cout * kvol * cin + 255) / 256, 256, 0, stream>>>(
@@ -178,7 +283,7 @@ static int launch_conv_direct(const void* feat, const int32_t* indices, const vo
         kern<<<blocks, CD_THREADS, smem, stream>>>((const T*)feat, indices, (const T*)weight,             \
                                                    (const T*)bias, bn_scale, bn_shift, apply_gelu,        \
                                                    (T*)out, row_order, n, cin, ksize, keys, vals,         \
-                                                   cap_mask, status);                                     \
+                                                   cap_mask, cells, status);                              \
     } while (0)
     if (smem > 220 * 1024) {
         set_error("ptv3_subm_conv_direct_fwd: %zu bytes of shared memory needed", smem);
@@ -199,12 +304,14 @@ static int launch_conv_direct(const void* feat, const int32_t* indices, const vo
 }
 
 static size_t conv_direct_weight_bytes(int ksize) { return align_up((size_t)ksize * ksize * ksize * 8 * 64 * 4, 256); }
+// hash table of blocks (sized for one block per voxel), block counter, one 64-entry table per block
+static size_t conv_direct_index_bytes(int64_t n) { return km_table_bytes(n) + 256 + align_up((size_t)n * 256, 256); }
 
 }  // namespace ptv3
 
 extern "C" size_t ptv3_subm_conv_direct_workspace_bytes(int64_t n, int ksize)
 {
-    return n > 0 ? ptv3::km_table_bytes(n) + ptv3::conv_direct_weight_bytes(ksize) : 0;
+    return n > 0 ? ptv3::conv_direct_index_bytes(n) + ptv3::conv_direct_weight_bytes(ksize) : 0;
 }
 
 extern "C" int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indices, const void* weight,
@@ -217,8 +324,8 @@ extern "C" int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indice
     PTV3_REQUIRE(n >= 0 && n < (1ll << 31), PTV3_ERR_INVALID_ARGUMENT, "ptv3_subm_conv_direct_fwd: bad n");
     PTV3_REQUIRE(c_in >= 1 && c_in <= CD_MAX_CIN, PTV3_ERR_UNSUPPORTED,
                  "ptv3_subm_conv_direct_fwd: c_in %d outside [1, %d]", c_in, CD_MAX_CIN);
-    PTV3_REQUIRE(ksize == 1 || ksize == 3 || ksize == 5 || ksize == 7, PTV3_ERR_UNSUPPORTED,
-                 "ptv3_subm_conv_direct_fwd: kernel size %d (supported: 1, 3, 5, 7)", ksize);
+    PTV3_REQUIRE(ksize == 1 || ksize == 3 || ksize == 5, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_subm_conv_direct_fwd: kernel size %d (supported: 1, 3, 5)", ksize);
     PTV3_REQUIRE(dtype == PTV3_DTYPE_F32 || dtype == PTV3_DTYPE_BF16, PTV3_ERR_UNSUPPORTED,
                  "ptv3_subm_conv_direct_fwd: dtype %d", dtype);
     PTV3_REQUIRE((bn_scale == nullptr) == (bn_shift == nullptr), PTV3_ERR_INVALID_ARGUMENT,
@@ -228,23 +335,31 @@ extern "C" int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indice
                  "ptv3_subm_conv_direct_fwd: null pointer");
     PTV3_REQUIRE(((uintptr_t)indices & 15) == 0, PTV3_ERR_INVALID_ARGUMENT,
                  "ptv3_subm_conv_direct_fwd: indices must be 16-byte aligned");
-    const size_t need = km_table_bytes(n) + conv_direct_weight_bytes(ksize);
+    const size_t need = conv_direct_index_bytes(n) + conv_direct_weight_bytes(ksize);
     PTV3_REQUIRE(workspace_bytes >= need, PTV3_ERR_WORKSPACE,
                  "ptv3_subm_conv_direct_fwd: workspace %zu < %zu bytes", workspace_bytes, need);
     PTV3_REQUIRE(((size_t)ksize * ksize * ksize * c_in * c_out) % 8 == 0, PTV3_ERR_UNSUPPORTED,
                  "ptv3_subm_conv_direct_fwd: weight size must be a multiple of 8 elements");
-    void* wt = static_cast<char*>(workspace) + km_table_bytes(n);
+    void* wt = static_cast<char*>(workspace) + conv_direct_index_bytes(n);
     cudaStream_t stream = (cudaStream_t)stream_;
-    unsigned long long* keys;
-    uint32_t* vals;
-    uint64_t cap_mask;
-    const int rc = km_build_table(indices, n, workspace, status, stream, &keys, &vals, &cap_mask);
-    if (rc != PTV3_OK) return rc;
+    const uint64_t cap = km_capacity(n);
+    const uint64_t cap_mask = cap - 1;
+    Carver cv(workspace);
+    unsigned long long* keys = cv.take<unsigned long long>(cap);
+    uint32_t* vals = cv.take<uint32_t>(cap);
+    uint32_t* counter = cv.take<uint32_t>(64);
+    uint32_t* cells = cv.take<uint32_t>((size_t)n * 64);
+    cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
+    cudaMemsetAsync(counter, 0, sizeof(uint32_t), stream);
+    const unsigned vb = (unsigned)((n + 255) / 256);
+    cd_block_insert_kernel<<<vb, 256, 0, stream>>>(indices, n, keys, vals, cap_mask, counter, cells, status);
+    cd_cell_fill_kernel<<<vb, 256, 0, stream>>>(indices, n, keys, vals, cap_mask, cells, status);
+    count_launches(2);
     if (dtype == PTV3_DTYPE_F32)
         return launch_conv_direct<float>(feat, indices, weight, bias, bn_scale, bn_shift, apply_gelu, out,
-                                         row_order, n, c_in, c_out, ksize, keys, vals, cap_mask, status, wt,
-                                         stream);
+                                         row_order, n, c_in, c_out, ksize, keys, vals, cap_mask, cells, status,
+                                         wt, stream);
     return launch_conv_direct<__nv_bfloat16>(feat, indices, weight, bias, bn_scale, bn_shift, apply_gelu,
                                              out, row_order, n, c_in, c_out, ksize, keys, vals, cap_mask,
-                                             status, wt, stream);
+                                             cells, status, wt, stream);
 }

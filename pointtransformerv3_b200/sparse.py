@@ -105,7 +105,7 @@ class SubMConv3d(SparseModule):
     def uses_direct_path(self):
         """Few input channels with a large kernel: probing the hash table inside
         the convolution beats building a (kernel volume x N) neighbour table."""
-        return self.in_channels <= 8 and self.kernel_size >= 5 and self.out_channels in (16, 32, 48, 64)
+        return self.in_channels <= 8 and self.kernel_size == 5 and self.out_channels in (16, 32, 48, 64)
 
     def forward(self, x, bn_scale=None, bn_shift=None, gelu=False):
         if self.uses_direct_path():
