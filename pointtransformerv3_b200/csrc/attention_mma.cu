@@ -42,7 +42,7 @@ __device__ __forceinline__ uint32_t scale_bf16x2(uint32_t v, float s)
 }
 
 template <bool PACKED>
-__global__ void __launch_bounds__(AM_THREADS, 2) attn_mma_d16_kernel(
+__global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     const __nv_bfloat16* __restrict__ qkv, const int64_t* __restrict__ order,
     const int64_t* __restrict__ pad, const int64_t* __restrict__ unpad,
     const int32_t* __restrict__ cu_seqlens, __nv_bfloat16* __restrict__ out, int C, float scale,
@@ -246,7 +246,8 @@ int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, c
     int qsplit = 1;
     const int pairs = n_seq * H;
     const int tiles = (max_seqlen + 15) / 16;
-    while (pairs * qsplit < 2 * 148 && qsplit * 2 * AM_WARPS <= tiles) qsplit *= 2;
+    // three CTAs fit on an SM; aim at several waves so that the last one costs little
+    while (pairs * qsplit < 4 * 3 * 148 && qsplit * 2 * AM_WARPS <= tiles) qsplit *= 2;
     const dim3 grid(n_seq, H, qsplit);
     kern<<<grid, AM_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad);
