@@ -241,9 +241,14 @@ def run_ours(args):
         att = timers.get("attention", {"calls": 0, "ms": 0.0, "work": 0.0})
         tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
         achieved = att["work"] / (att["ms"] * 1e-3) / 1e12 if att["ms"] else 0.0
+        # DRAM bytes per launch: the ncu capture of one launch on the C = 64, 120 832-row case reads and
+        # writes 56.1 MB, i.e. 7.25 B per padded row and channel; traffic grows in proportion to
+        # rows x channels, which is the work figure / (4 x patch)
+        traffic = 7.25 * att["work"] / (4.0 * 1024.0) / max(att["calls"], 1)
         roofline = {"kernel": "attention core (all patch-attention launches of the timed steps)",
                     "bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
-                    "frac": achieved / tf_peak, "traffic": None,
+                    "frac": achieved / tf_peak, "traffic": traffic,
+                    "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch",
                     "peak_source": "measured (sustained)" if peaks else "fallback",
                     "launches": att["calls"], "avg_launch_ms": att["ms"] / max(att["calls"], 1)}
         breakdown = {k: {"calls": v["calls"], "ms_per_step": v["ms"] / args.steps} for k, v in timers.items()}
@@ -373,6 +378,19 @@ def run_operator_case(args):
                    roofline_kmap={"kernel": "km_insert + km_probe", "bound": "hbm",
                                   "achieved": 124.0 * n / t_map / 1e6, "peak": hbm, "unit": "GB/s",
                                   "frac": 124.0 * n / t_map / 1e6 / hbm, "traffic": None})
+    elif args.case == "mlp":
+        n, c = args.points or 407_000, 64
+        g = torch.Generator().manual_seed(0)
+        mk = lambda *shape: torch.randn(*shape, generator=g).bfloat16().to(dev)
+        x, res = mk(n, c), mk(n, c)
+        w1, b1, w2, b2 = mk(4 * c, c), mk(4 * c), mk(c, 4 * c), mk(c)
+        st = ops.new_status(dev)
+        t = _time_device(lambda: ops.mlp(x, w1, b1, w2, b2, res, st), args.steps, args.warmup, flush)
+        byts = 3.0 * n * c * 2
+        out.update(config={"workload": "fused MLP (fc1, GELU, fc2, residual), C=64, hidden 256, bf16", "rows": n},
+                   metric="mlp_rows_per_sec", unit="rows/s", value=n / (t * 1e-3), ms=t,
+                   roofline={"kernel": "mlp_tc05_kernel", "bound": "hbm", "achieved": byts / t / 1e6,
+                             "peak": hbm, "unit": "GB/s", "frac": byts / t / 1e6 / hbm, "traffic": None})
     print(json.dumps(out))
 
 
@@ -384,7 +402,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
-    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv"],
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv", "mlp"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
     args = ap.parse_args()

@@ -23,32 +23,41 @@ struct OrderList {
 __device__ const hlut::Table1 g_hilbert_t1 = hlut::make_table1();
 __device__ const hlut::Table2 g_hilbert_t2 = hlut::make_table2();
 
-// Hilbert code from the Morton code of the same point: two levels per table step
-__device__ __forceinline__ uint64_t hilbert_from_morton(uint64_t m, int depth, const uint16_t* __restrict__ t1,
-                                                        const uint16_t* __restrict__ t2)
+// The code is handled as two 24-bit words (levels 8..15 and 0..7) so that all
+// arithmetic is 32-bit.  Hilbert code from the Morton words of the same point,
+// two levels per table step.
+struct Code48 {
+    uint32_t hi, lo;
+};
+
+__device__ __forceinline__ Code48 hilbert_from_morton(Code48 m, int depth, const uint16_t* __restrict__ t1,
+                                                      const uint16_t* __restrict__ t2)
 {
-    uint32_t s = 0;
-    uint64_t g = 0;
+    uint32_t s = 0, gh = 0, gl = 0;
     int l = depth;
-    if (l & 1) {
+    if (l & 1) {   // odd number of levels: the top one alone
         --l;
-        const uint32_t e = t1[s * 8 + (uint32_t)((m >> (3 * l)) & 7)];
-        g = e & 7;
+        const uint32_t r = l >= 8 ? (m.hi >> (3 * (l - 8))) & 7u : (m.lo >> (3 * l)) & 7u;
+        const uint32_t e = t1[s * 8 + r];
+        if (l >= 8) gh = e & 7u; else gl = e & 7u;
         s = e >> 3;
     }
-    while (l > 0) {
-        l -= 2;
-        const uint32_t e = t2[s * 64 + (uint32_t)((m >> (3 * l)) & 63)];
-        g = (g << 6) | (e & 63);
+    for (; l > 8; l -= 2) {
+        const uint32_t e = t2[s * 64 + ((m.hi >> (3 * (l - 10))) & 63u)];
+        gh = gh * 64u + (e & 63u);
         s = e >> 6;
     }
-    g ^= g >> 1;
-    g ^= g >> 2;
-    g ^= g >> 4;
-    g ^= g >> 8;
-    g ^= g >> 16;
-    g ^= g >> 32;
-    return g;
+    for (; l > 0; l -= 2) {
+        const uint32_t e = t2[s * 64 + ((m.lo >> (3 * (l - 2))) & 63u)];
+        gl = gl * 64u + (e & 63u);
+        s = e >> 6;
+    }
+    // Gray -> binary: prefix XOR from the top bit, done per word, then the parity of
+    // the upper word carried into the lower one
+    gh ^= gh >> 1; gh ^= gh >> 2; gh ^= gh >> 4; gh ^= gh >> 8; gh ^= gh >> 16;
+    gl ^= gl >> 1; gl ^= gl >> 2; gl ^= gl >> 4; gl ^= gl >> 8; gl ^= gl >> 16;
+    gl ^= (0u - (gh & 1u)) & 0xffffffu;
+    return Code48{gh, gl};
 }
 
 __global__ void __launch_bounds__(256) encode_kernel(const int32_t* __restrict__ grid,
@@ -58,30 +67,39 @@ __global__ void __launch_bounds__(256) encode_kernel(const int32_t* __restrict__
 {
     __shared__ uint16_t t1[48 * 8];
     __shared__ uint16_t t2[48 * 64];
+    __shared__ uint32_t sp[256];   // bit i of a byte -> bit 3 i (as z_order.py:12-50 tabulates)
     for (int i = threadIdx.x; i < 48 * 8; i += blockDim.x) t1[i] = g_hilbert_t1.v[i];
     for (int i = threadIdx.x; i < 48 * 64; i += blockDim.x) t2[i] = g_hilbert_t2.v[i];
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) sp[i] = (uint32_t)spread3((uint32_t)i);
     __syncthreads();
-    const uint32_t mask = (depth >= 32) ? 0xffffffffu : ((1u << depth) - 1u);
+    const uint32_t mask = (1u << depth) - 1u;   // depth <= 16
+    const bool low_only = depth <= 8;
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
          i += (int64_t)gridDim.x * blockDim.x) {
         const uint32_t x = (uint32_t)grid[3 * i + 0] & mask;
         const uint32_t y = (uint32_t)grid[3 * i + 1] & mask;
         const uint32_t z = (uint32_t)grid[3 * i + 2] & mask;
         const uint64_t hi = batch ? ((uint64_t)batch[i] << (3 * depth)) : 0ull;
-        const uint64_t sx = spread3(x), sy = spread3(y), sz = spread3(z);
-        const uint64_t m = (sx << 2) | (sy << 1) | sz;    // z order
-        const uint64_t mt = (sy << 2) | (sx << 1) | sz;   // z order with x and y exchanged
+        const uint32_t xl = sp[x & 255u], yl = sp[y & 255u], zl = sp[z & 255u];
+        uint32_t xh = 0, yh = 0, zh = 0;
+        if (!low_only) {
+            xh = sp[x >> 8];
+            yh = sp[y >> 8];
+            zh = sp[z >> 8];
+        }
+        const Code48 m{(xh << 2) | (yh << 1) | zh, (xl << 2) | (yl << 1) | zl};    // z order
+        const Code48 mt{(yh << 2) | (xh << 1) | zh, (yl << 2) | (xl << 1) | zl};   // x and y exchanged
 #pragma unroll
         for (int r = 0; r < PTV3_MAX_ORDERS; ++r) {
             if (r < orders.n) {
-                uint64_t c;
+                Code48 c;
                 switch (orders.id[r]) {
                     case PTV3_ORDER_Z: c = m; break;
                     case PTV3_ORDER_Z_TRANS: c = mt; break;
                     case PTV3_ORDER_HILBERT: c = hilbert_from_morton(m, depth, t1, t2); break;
                     default: c = hilbert_from_morton(mt, depth, t1, t2); break;
                 }
-                codes[(int64_t)r * n + i] = (int64_t)(c | hi);
+                codes[(int64_t)r * n + i] = (int64_t)((((uint64_t)c.hi << 24) | c.lo) | hi);
             }
         }
     }

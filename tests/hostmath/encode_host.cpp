@@ -9,25 +9,35 @@ using namespace ptv3;
 static constexpr hlut::Table1 T1 = hlut::make_table1();
 static constexpr hlut::Table2 T2 = hlut::make_table2();
 
-static uint64_t from_morton(uint64_t m, int depth)
+// same split-word arithmetic as hilbert_from_morton() in encode.cu
+static uint64_t from_morton(uint64_t m64, int depth)
 {
-    uint32_t s = 0;
-    uint64_t g = 0;
+    const uint32_t mhi = (uint32_t)(m64 >> 24), mlo = (uint32_t)(m64 & 0xffffffu);
+    const uint16_t* t1 = T1.v;
+    const uint16_t* t2 = T2.v;
+    uint32_t s = 0, gh = 0, gl = 0;
     int l = depth;
     if (l & 1) {
         --l;
-        const uint32_t e = T1.v[s * 8 + (uint32_t)((m >> (3 * l)) & 7)];
-        g = e & 7;
+        const uint32_t r = l >= 8 ? (mhi >> (3 * (l - 8))) & 7u : (mlo >> (3 * l)) & 7u;
+        const uint32_t e = t1[s * 8 + r];
+        if (l >= 8) gh = e & 7u; else gl = e & 7u;
         s = e >> 3;
     }
-    while (l > 0) {
-        l -= 2;
-        const uint32_t e = T2.v[s * 64 + (uint32_t)((m >> (3 * l)) & 63)];
-        g = (g << 6) | (e & 63);
+    for (; l > 8; l -= 2) {
+        const uint32_t e = t2[s * 64 + ((mhi >> (3 * (l - 10))) & 63u)];
+        gh = gh * 64u + (e & 63u);
         s = e >> 6;
     }
-    for (int sh = 1; sh < 64; sh <<= 1) g ^= g >> sh;
-    return g;
+    for (; l > 0; l -= 2) {
+        const uint32_t e = t2[s * 64 + ((mlo >> (3 * (l - 2))) & 63u)];
+        gl = gl * 64u + (e & 63u);
+        s = e >> 6;
+    }
+    gh ^= gh >> 1; gh ^= gh >> 2; gh ^= gh >> 4; gh ^= gh >> 8; gh ^= gh >> 16;
+    gl ^= gl >> 1; gl ^= gl >> 2; gl ^= gl >> 4; gl ^= gl >> 8; gl ^= gl >> 16;
+    gl ^= (0u - (gh & 1u)) & 0xffffffu;
+    return ((uint64_t)gh << 24) | gl;
 }
 
 extern "C" void host_encode(const int32_t* grid, int64_t n, int depth, int order, int use_lut, int64_t* out)
