@@ -5,10 +5,11 @@
 // backbone) never leaves the SM.
 //
 // A CTA is persistent and holds both weight matrices in shared memory (TMA, loaded
-// once).  Its 256 threads form two independent groups of 128; each group walks
-// its own 128-row tiles:
+// once).  Its 512 threads form four independent groups of 128 (so that the
+// tensor-memory loads, GELU arithmetic and stores of different tiles overlap);
+// each group walks its own 128-row tiles, 64 hidden columns at a time:
 //   TMA    x tile (128 x C, 64/128-byte swizzle)                 -> shared memory
-//   UMMA   D1[128 x 128] = x . W1_chunk^T    (tcgen05.mma, accumulator in TMEM)
+//   UMMA   D1[128 x 64] = x . W1_chunk^T     (tcgen05.mma, accumulator in TMEM)
 //   warps  tcgen05.ld D1 -> + b1 -> GELU -> bf16 -> shared memory in the UMMA
 //          K-major 128-byte-swizzled layout (the A operand of the second GEMM)
 //   UMMA   D2[128 x C] += h_chunk . W2_chunk^T
@@ -26,7 +27,8 @@ using namespace tc05;
 template <int C>
 struct MlpCfg {
     static constexpr int HD = 4 * C;                  // hidden width
-    static constexpr int HC = 128;                    // hidden columns per round
+    static constexpr int HC = 64;                     // hidden columns per round
+    static constexpr int NG = 4;                      // independent 128-thread groups per CTA
     static constexpr int NCH = HD / HC;
     static constexpr int SWX = C * 2;                 // bytes per row of x / W1 (= swizzle span)
     static constexpr int W1_BYTES = HD * SWX;
@@ -39,24 +41,37 @@ struct MlpCfg {
     static constexpr int OFF_W2 = OFF_W1 + W1_BYTES;
     static constexpr int OFF_G = OFF_W2 + W2_BYTES;   // per group: x tile, activation
     static constexpr int G_BYTES = X_BYTES + H_BYTES;
-    static constexpr int OFF_B1 = OFF_G + 2 * G_BYTES;
+    static constexpr int OFF_B1 = OFF_G + NG * G_BYTES;
     static constexpr int OFF_B2 = OFF_B1 + HD * 4;
-    static constexpr int OFF_BAR = OFF_B2 + C * 4;    // 7 mbarriers, tmem pointer, abort flag
+    static constexpr int OFF_BAR = OFF_B2 + C * 4;    // 1 + 3 NG mbarriers, tmem pointer, abort flag
+    static constexpr int NBAR = 1 + 3 * NG;
     // + slack for the 1 KiB alignment; at least 120 KiB so that two CTAs (each wanting all of
     // tensor memory) never share an SM
-    static constexpr int SMEM_NEED = OFF_BAR + 128 + 1024;
+    static constexpr int SMEM_NEED = OFF_BAR + 8 * NBAR + 64 + 1024;
     static constexpr int SMEM = SMEM_NEED < 120 * 1024 ? 120 * 1024 : SMEM_NEED;
-    static constexpr int TMEM_D1 = 0, TMEM_D2 = 128, TMEM_GROUP = 256;
+    static constexpr int TMEM_D1 = 0, TMEM_D2 = 64, TMEM_GROUP = 128;
 };
 
+// GELU in its erf form, 0.5 x (1 + erf(x / sqrt 2)), with erf(z) = tanh(c1 z + c3 z^3 + c5 z^5)
+// (|error| < 4.1e-5 for the fit, z^2 clamped at 16 where erf is 1 to eight digits) and the
+// hardware tanh (relative error about 2^-11).  The result is rounded to bf16 (relative
+// 2^-9) right after, and the library erff costs 2.5x the instructions in an epilogue that
+// is bound by instruction issue.
 __device__ __forceinline__ float mlp_gelu(float x)
 {
-    return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
+    // coefficients of the fit in z, rescaled to x = z sqrt 2
+    const float c1 = 1.12812329f * 0.70710678f, c3 = 0.10414445f * 0.35355339f, c5 = -0.00181548f * 0.17677670f;
+    const float x2 = fminf(x * x, 32.f);
+    const float p = fmaf(fmaf(c5, x2, c3), x2, c1) * x;
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(p));
+    const float hx = 0.5f * x;
+    return fmaf(hx, th, hx);
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 template <int C>
-__global__ void __launch_bounds__(256, 1) mlp_tc05_kernel(
+__global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
     const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w1,
     const __grid_constant__ CUtensorMap map_w2, const __nv_bfloat16* __restrict__ b1,
     const __nv_bfloat16* __restrict__ b2, const __nv_bfloat16* __restrict__ residual,
@@ -69,25 +84,27 @@ __global__ void __launch_bounds__(256, 1) mlp_tc05_kernel(
     float* b1s = reinterpret_cast<float*>(smem + Cfg::OFF_B1);
     float* b2s = reinterpret_cast<float*>(smem + Cfg::OFF_B2);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::OFF_BAR);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + Cfg::NBAR);
+    constexpr int NT = 128 * Cfg::NG;
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int g = tid >> 7, t = tid & 127;
     const uint32_t wbar = sbase + Cfg::OFF_BAR;
-    const uint32_t xbar = wbar + 8 * (1 + g), m1bar = wbar + 8 * (3 + g), m2bar = wbar + 8 * (5 + g);
+    const uint32_t xbar = wbar + 8 * (1 + g), m1bar = wbar + 8 * (1 + Cfg::NG + g),
+                   m2bar = wbar + 8 * (1 + 2 * Cfg::NG + g);
 
     if (tid == 0) {
-        for (int i = 0; i < 7; ++i) mbar_init(wbar + 8 * i, 1);
+        for (int i = 0; i < Cfg::NBAR; ++i) mbar_init(wbar + 8 * i, 1);
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_w1);
         prefetch_tensormap(&map_w2);
     }
-    for (int i = tid; i < Cfg::HD; i += 256) b1s[i] = __bfloat162float(b1[i]);
-    for (int i = tid; i < C; i += 256) b2s[i] = __bfloat162float(b2[i]);
-    if (warp == 0) tmem_alloc(sbase + Cfg::OFF_BAR + 56, 512);
+    for (int i = tid; i < Cfg::HD; i += NT) b1s[i] = __bfloat162float(b1[i]);
+    for (int i = tid; i < C; i += NT) b2s[i] = __bfloat162float(b2[i]);
+    if (warp == 0) tmem_alloc(sbase + Cfg::OFF_BAR + 8 * Cfg::NBAR, 512);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -137,7 +154,8 @@ __global__ void __launch_bounds__(256, 1) mlp_tc05_kernel(
     };
 
     const int64_t ntiles = (n + 127) / 128;
-    for (int64_t tile = (int64_t)blockIdx.x * 2 + g; tile < ntiles; tile += (int64_t)gridDim.x * 2) {
+    for (int64_t tile = (int64_t)blockIdx.x * Cfg::NG + g; tile < ntiles;
+         tile += (int64_t)gridDim.x * Cfg::NG) {
         const int64_t row0 = tile * 128;
         if (t == 0) {
             mbar_expect_tx(xbar, Cfg::X_BYTES);
@@ -235,9 +253,9 @@ static int launch_mlp(const void* x, const void* w1, const void* b1, const void*
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM) != cudaSuccess)
         return check_launch("ptv3_mlp_fwd: shared memory attribute");
     const int64_t ntiles = (n + 127) / 128;
-    int64_t grid = (ntiles + 1) / 2;
+    int64_t grid = (ntiles + Cfg::NG - 1) / Cfg::NG;
     if (grid > 148) grid = 148;
-    kern<<<(unsigned)grid, 256, Cfg::SMEM, stream>>>(mx, mw1, mw2, (const __nv_bfloat16*)b1,
+    kern<<<(unsigned)grid, 128 * Cfg::NG, Cfg::SMEM, stream>>>(mx, mw1, mw2, (const __nv_bfloat16*)b1,
                                                      (const __nv_bfloat16*)b2, (const __nv_bfloat16*)residual,
                                                      (__nv_bfloat16*)out, n, status);
     count_launches(1);
