@@ -82,11 +82,19 @@ class PointSequential(PointModule):
 
 
 def _bn_eval_affine(bn):
-    """Per-channel (scale, shift) of a BatchNorm1d in eval mode, fp32."""
+    """Per-channel (scale, shift) of a BatchNorm1d in eval mode, fp32.  Cached on
+    the module and recomputed when a parameter or buffer was modified or moved."""
+    tensors = (bn.weight, bn.bias, bn.running_mean, bn.running_var)
+    key = tuple((t._version, t.data_ptr(), t.dtype) if t is not None else None for t in tensors)
+    cached = bn.__dict__.get("_ptv3_affine")
+    if cached is not None and cached[0] == key:
+        return cached[1], cached[2]
     w = bn.weight.float() if bn.weight is not None else torch.ones_like(bn.running_var)
     b = bn.bias.float() if bn.bias is not None else torch.zeros_like(bn.running_var)
-    scale = w * torch.rsqrt(bn.running_var.float() + bn.eps)
-    return scale.contiguous(), (b - bn.running_mean.float() * scale).contiguous()
+    scale = (w * torch.rsqrt(bn.running_var.float() + bn.eps)).contiguous()
+    shift = (b - bn.running_mean.float() * scale).contiguous()
+    bn.__dict__["_ptv3_affine"] = (key, scale, shift)
+    return scale, shift
 
 
 def _is_bn_gelu(norm, act):

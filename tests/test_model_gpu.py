@@ -213,3 +213,40 @@ def test_flash_flag_uses_full_patch_and_short_sequences():
         outp[a:b] = (w @ v).transpose(0, 1).reshape(b - a, C)
     ref = torch.nn.functional.linear(outp[unpad[inverse]], sd["proj.weight"], sd["proj.bias"])
     assert_close(got, ref, what="varlen attention", **TOL[torch.float32])
+
+
+def test_lidar_like_scenes_vs_oracle():
+    """Sparse outdoor-like sweeps (grid 0.05, 4 input channels, three scenes): the
+    whole small backbone against the CPU oracle in fp32."""
+    from pointtransformerv3_b200 import synthetic
+    scenes = [synthetic.lidar_scene(seed=s, grid_size=0.05, n_sweeps=1, beams=32, azimuth_steps=256)
+              for s in (0, 1, 2)]
+    data = synthetic.make_batch(scenes, 1, 0)
+    cfg = dict(SMALL_CFG, enc_patch_size=(256,) * 5, dec_patch_size=(256,) * 4)
+    net = P.PointTransformerV3(in_channels=4, enable_flash=False, **cfg).eval()
+    sd = weights.fill_state_dict(net, prefix="lidar.")
+    net = net.cuda()
+    with torch.inference_mode():
+        torch.manual_seed(3)
+        out = net(cuda_data(data))
+        torch.manual_seed(3)
+        ref, levels = O.ptv3_forward(sd, data, dict(cfg, in_channels=4), return_levels=True)
+    assert torch.equal(out.serialized_order.cpu(), levels[0].order)
+    assert torch.equal(out.serialized_code.cpu(), levels[0].code)
+    assert_close(out.feat, ref, atol=5e-4, rtol=5e-4, what="lidar-like backbone fp32")
+
+
+def test_cls_mode_and_single_order():
+    """Encoder-only mode with one serialization order and no shuffling."""
+    data = small_batch([3000, 1500], seed=71)
+    cfg = dict(enc_depths=(1, 1, 1, 1, 1), enc_channels=(32, 32, 64, 64, 128), enc_num_head=(2, 2, 4, 4, 8),
+               enc_patch_size=(128,) * 5, cls_mode=True, order="hilbert", shuffle_orders=False)
+    net = P.PointTransformerV3(in_channels=6, enable_flash=False, **cfg).eval()
+    sd = weights.fill_state_dict(net, prefix="cls.")
+    net = net.cuda()
+    with torch.inference_mode():
+        out = net(cuda_data(data))
+        ocfg = dict(cfg, order=("hilbert",), dec_depths=(), dec_channels=(), dec_num_head=(), dec_patch_size=())
+        ref = O.ptv3_forward(sd, data, ocfg)
+    assert out.feat.shape == ref.shape
+    assert_close(out.feat, ref, atol=5e-4, rtol=5e-4, what="encoder-only backbone")
