@@ -378,6 +378,43 @@ def run_operator_case(args):
                    roofline_kmap={"kernel": "km_insert + km_probe", "bound": "hbm",
                                   "achieved": 124.0 * n / t_map / 1e6, "peak": hbm, "unit": "GB/s",
                                   "frac": 124.0 * n / t_map / 1e6 / hbm, "traffic": None})
+    elif args.case == "pooling":
+        # stride-2 pooling of a 4-scene indoor batch: plan (clusters, pooled orders) and feature side
+        data = synthetic.indoor_batch(4, target_voxels=(args.points or 400_000) // 4, grid_size=GRID)
+        n, c = int(data["offset"][-1]), 64
+        off = [0] + data["offset"].tolist()
+        batch = torch.cat([torch.full((off[i + 1] - off[i],), i, dtype=torch.int64) for i in range(4)]).to(dev)
+        gc = data["grid_coord"].to(dev)
+        depth = int(gc.max()).bit_length()
+        codes = ops.encode(gc, batch, depth, orders)
+        order, _ = ops.argsort_inverse(codes, 3 * depth + 3)
+        t_plan = _time_device(lambda: ops.pool_plan(codes, order, gc, batch, 4, 1, [2, 0, 3, 1]), args.steps,
+                              args.warmup, flush)
+        plan = ops.pool_plan(codes, order, gc, batch, 4, 1, [2, 0, 3, 1])
+        m = plan["m"]
+        x = torch.randn(n, c, generator=torch.Generator().manual_seed(0)).bfloat16().to(dev)
+        coord = data["coord"].to(dev)
+        scale = torch.ones(c, device=dev)
+        shift = torch.zeros(c, device=dev)
+        t_pool = _time_device(lambda: ops.pool(x, coord, order[0], plan["idx_ptr"], scale, shift), args.steps,
+                              args.warmup, flush)
+        child = torch.randn(m, c, generator=torch.Generator().manual_seed(1)).bfloat16().to(dev)
+        t_unpool = _time_device(lambda: ops.unpool(x, child, plan["cluster"], scale, shift, scale, shift),
+                                args.steps, args.warmup, flush)
+        pool_b = n * (c * 2 + 8 + 12) + m * (c * 2 + 12 + 8)     # rows + order + coord in, pooled rows + coord out
+        unpool_b = n * (c * 2 * 3 + 8) + m * c * 2                # skip in, two outputs, cluster ids, child rows
+        plan_b = n * (4 * 8 * 2 + 12 + 8 + 8) + m * (4 * 8 * 3 + 12 + 8 + 8)
+        out.update(config={"workload": "stride-2 pooling, 4 indoor scenes, C=64, bf16", "points": n, "clusters": m},
+                   metric="pooling_points_per_sec", unit="points/s", value=n / ((t_plan + t_pool) * 1e-3),
+                   plan_ms=t_plan, pool_ms=t_pool, unpool_ms=t_unpool,
+                   roofline={"kernel": "pool_max_kernel + pool_coord_mean_kernel", "bound": "hbm",
+                             "achieved": pool_b / t_pool / 1e6, "peak": hbm, "unit": "GB/s",
+                             "frac": pool_b / t_pool / 1e6 / hbm, "traffic": None},
+                   roofline_unpool={"kernel": "unpool_kernel", "bound": "hbm", "achieved": unpool_b / t_unpool / 1e6,
+                                    "peak": hbm, "unit": "GB/s", "frac": unpool_b / t_unpool / 1e6 / hbm},
+                   roofline_plan={"kernel": "pool plan (7 launches, one host read)", "bound": "hbm",
+                                  "achieved": plan_b / t_plan / 1e6, "peak": hbm, "unit": "GB/s",
+                                  "frac": plan_b / t_plan / 1e6 / hbm})
     elif args.case == "mlp":
         n, c = args.points or 407_000, 64
         g = torch.Generator().manual_seed(0)
@@ -402,7 +439,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
-    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv", "mlp"],
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv", "mlp", "pooling"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
     args = ap.parse_args()

@@ -70,6 +70,16 @@ int ptv3_encode(const int32_t* grid_coord, const int64_t* batch, int64_t n, int 
                 const int* orders, int n_orders, int64_t* codes, void* stream);
 
 /*
+ * Inverse of ptv3_encode for the orders PTV3_ORDER_Z and PTV3_ORDER_HILBERT.
+ * Replaces serialization/default.py:27-38 (decode), z_order.py:104-126 (key2xyz),
+ * hilbert.py:201-303 (decode).  (The reference's z-order wrapper, default.py:48-51,
+ * fails on its own return value; this is what it is meant to return.)
+ *   grid_coord  n x 3 int64; batch  n int64 (code >> 3*depth) or NULL
+ */
+int ptv3_decode(const int64_t* codes, int64_t n, int depth, int order, int64_t* grid_coord, int64_t* batch,
+                void* stream);
+
+/*
  * Stable argsort of every code row and its inverse permutation.
  * Replaces model.py:118-126 (torch.argsort + scatter_) and :667-674.
  *   codes     k x n int64, non-negative, nothing set above bit sig_bits-1

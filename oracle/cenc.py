@@ -29,6 +29,7 @@ def lib():
         _lib.oracle_encode.argtypes = [i32p, i64p, ctypes.c_int64, ctypes.c_int, ctypes.c_int, i64p]
         _lib.oracle_argsort_stable.argtypes = [i64p, ctypes.c_int64, i64p]
         _lib.oracle_inverse.argtypes = [i64p, ctypes.c_int64, i64p]
+        _lib.oracle_decode.argtypes = [i64p, ctypes.c_int64, ctypes.c_int, ctypes.c_int, i64p, i64p]
     return _lib
 
 
@@ -65,3 +66,15 @@ def inverse(order):
     if rc != 0:
         raise ValueError("oracle_inverse rc=%d" % rc)
     return inv
+
+
+def decode(code, depth, order):
+    """(N,) int64 codes -> (grid_coord (N,3) int64, batch (N,) int64); order "z" or "hilbert"."""
+    c = np.ascontiguousarray(code, dtype=np.int64).reshape(-1)
+    grid = np.empty((c.shape[0], 3), dtype=np.int64)
+    batch = np.empty(c.shape[0], dtype=np.int64)
+    rc = lib().oracle_decode(_p(c, ctypes.c_int64), c.shape[0], int(depth), ORDER_IDS[order],
+                             _p(grid, ctypes.c_int64), _p(batch, ctypes.c_int64))
+    if rc != 0:
+        raise ValueError("oracle_decode rc=%d" % rc)
+    return grid, batch

@@ -17,6 +17,11 @@
  *                                    interleave, Gray decode by prefix XOR
  *   model.py:118-126                 argsort of every code row + inverse
  *                                    permutation by scatter
+ *   serialization/default.py:27-38   decode(): batch = code >> 3*depth, curve
+ *                                    inverse of the low bits
+ *   serialization/z_order.py:52-60   inverse Morton bit placement
+ *   serialization/hilbert.py:201-303 binary -> Gray, de-interleave, the
+ *                                    transform undone from the lowest level up
  */
 #include <stdint.h>
 #include <stdlib.h>
@@ -116,6 +121,47 @@ int oracle_inverse(const int64_t *order, int64_t n, int64_t *inverse)
     for (int64_t j = 0; j < n; ++j) {
         if (order[j] < 0 || order[j] >= n) return -1;
         inverse[order[j]] = j;
+    }
+    return 0;
+}
+
+/*
+ * Inverse of oracle_encode for order 0 ("z") and 2 ("hilbert"), default.py:27-38.
+ * grid: n x 3 int64, batch: n int64 (may be NULL).
+ */
+int oracle_decode(const int64_t *code, int64_t n, int depth, int order, int64_t *grid, int64_t *batch)
+{
+    if (depth < 1 || depth > 21 || (order != ORDER_Z && order != ORDER_HILBERT)) return -1;
+    const uint64_t mask = (depth * 3 >= 64) ? ~0ull : ((1ull << (3 * depth)) - 1);
+    for (int64_t i = 0; i < n; ++i) {
+        uint64_t c = (uint64_t)code[i];
+        if (batch) batch[i] = (int64_t)(c >> (3 * depth));         /* default.py:30 */
+        c &= mask;                                                  /* default.py:31 */
+        if (order == ORDER_HILBERT) c ^= c >> 1;                    /* hilbert.py:46-66 binary2gray */
+        uint64_t X[3] = { 0, 0, 0 };
+        for (int b = 0; b < depth; ++b) {                           /* z_order.py:52-60 */
+            X[0] |= ((c >> (3 * b + 2)) & 1ull) << b;
+            X[1] |= ((c >> (3 * b + 1)) & 1ull) << b;
+            X[2] |= ((c >> (3 * b + 0)) & 1ull) << b;
+        }
+        if (order == ORDER_HILBERT) {
+            for (int bit = depth - 1; bit >= 0; --bit) {            /* hilbert.py:262 */
+                uint64_t Q = 1ull << (depth - 1 - bit);
+                uint64_t P = Q - 1;
+                for (int dim = 2; dim >= 0; --dim) {                /* hilbert.py:264 */
+                    if (X[dim] & Q) {
+                        X[0] ^= P;
+                    } else {
+                        uint64_t t = (X[0] ^ X[dim]) & P;
+                        X[0] ^= t;
+                        X[dim] ^= t;
+                    }
+                }
+            }
+        }
+        grid[3 * i + 0] = (int64_t)X[0];
+        grid[3 * i + 1] = (int64_t)X[1];
+        grid[3 * i + 2] = (int64_t)X[2];
     }
     return 0;
 }

@@ -105,7 +105,50 @@ __global__ void __launch_bounds__(256) encode_kernel(const int32_t* __restrict__
     }
 }
 
+__global__ void __launch_bounds__(256) decode_kernel(const int64_t* __restrict__ codes, int64_t n, int depth,
+                                                     int hilbert, int64_t* __restrict__ grid,
+                                                     int64_t* __restrict__ batch)
+{
+    const uint64_t mask = (1ull << (3 * depth)) - 1ull;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const uint64_t c = (uint64_t)codes[i];
+        if (batch) batch[i] = (int64_t)(c >> (3 * depth));
+        const uint64_t low = c & mask;
+        uint32_t x, y, z;
+        if (hilbert) {
+            hilbert3_inverse(low, depth, x, y, z);
+        } else {
+            x = compact3(low >> 2);
+            y = compact3(low >> 1);
+            z = compact3(low);
+        }
+        grid[3 * i + 0] = x;
+        grid[3 * i + 1] = y;
+        grid[3 * i + 2] = z;
+    }
+}
+
 }  // namespace ptv3
+
+extern "C" int ptv3_decode(const int64_t* codes, int64_t n, int depth, int order, int64_t* grid_coord,
+                           int64_t* batch, void* stream)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0, PTV3_ERR_INVALID_ARGUMENT, "ptv3_decode: n < 0");
+    PTV3_REQUIRE(depth >= 1 && depth <= 16, PTV3_ERR_INVALID_ARGUMENT, "ptv3_decode: depth %d outside [1, 16]",
+                 depth);
+    PTV3_REQUIRE(order == PTV3_ORDER_Z || order == PTV3_ORDER_HILBERT, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_decode: order %d (decodable: z = 0, hilbert = 2)", order);
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(codes && grid_coord, PTV3_ERR_INVALID_ARGUMENT, "ptv3_decode: null pointer");
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    decode_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(codes, n, depth, order == PTV3_ORDER_HILBERT,
+                                                                      grid_coord, batch);
+    count_launches(1);
+    return check_launch("ptv3_decode");
+}
 
 extern "C" int ptv3_encode(const int32_t* grid_coord, const int64_t* batch, int64_t n, int depth,
                            const int* orders, int n_orders, int64_t* codes, void* stream)

@@ -22,21 +22,22 @@ __device__ __forceinline__ float gelu_exact(float x)
     return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
 }
 
-// C must be a multiple of Vec<T>::N.
-template <typename T>
-__global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x,
+// LANES lanes own a cluster (LANES * Vec<T>::N channels per pass); the first three
+// lanes of a group also average the coordinates.  C must be a multiple of Vec<T>::N.
+template <typename T, int LANES>
+__global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x, const float* __restrict__ coord,
                                                        const int64_t* __restrict__ indices,
-                                                       const int64_t* __restrict__ idx_ptr, int64_t m,
-                                                       int C, const float* __restrict__ scale,
-                                                       const float* __restrict__ shift,
-                                                       T* __restrict__ out)
+                                                       const int64_t* __restrict__ idx_ptr, int64_t m, int C,
+                                                       const float* __restrict__ scale,
+                                                       const float* __restrict__ shift, T* __restrict__ out,
+                                                       float* __restrict__ coord_out)
 {
     using V = Vec<T>;
-    const int lane = threadIdx.x & 31;
-    const int64_t c = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int sub = threadIdx.x % LANES;
+    const int64_t c = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) / LANES;
     if (c >= m) return;
     const int64_t lo = idx_ptr[c], hi = idx_ptr[c + 1];
-    for (int ch = lane * V::N; ch < C; ch += 32 * V::N) {
+    for (int ch = sub * V::N; ch < C; ch += LANES * V::N) {
         float best[V::N];
 #pragma unroll
         for (int i = 0; i < V::N; ++i) best[i] = -INFINITY;
@@ -56,27 +57,11 @@ __global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x,
         }
         *reinterpret_cast<typename V::Raw*>(out + c * C + ch) = V::pack(best);
     }
-}
-
-__global__ void __launch_bounds__(256) pool_coord_mean_kernel(const float* __restrict__ coord,
-                                                              const int64_t* __restrict__ indices,
-                                                              const int64_t* __restrict__ idx_ptr,
-                                                              int64_t m, float* __restrict__ out)
-{
-    const int64_t c = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (c >= m) return;
-    const int64_t lo = idx_ptr[c], hi = idx_ptr[c + 1];
-    float sx = 0.f, sy = 0.f, sz = 0.f;
-    for (int64_t j = lo; j < hi; ++j) {
-        const int64_t p = indices[j];
-        sx += coord[3 * p + 0];
-        sy += coord[3 * p + 1];
-        sz += coord[3 * p + 2];
+    if (coord_out && sub < 3) {
+        float acc = 0.f;
+        for (int64_t j = lo; j < hi; ++j) acc += coord[3 * indices[j] + sub];
+        coord_out[3 * c + sub] = acc / (float)(hi - lo);
     }
-    const float inv = 1.f / (float)(hi - lo);
-    out[3 * c + 0] = sx * inv;
-    out[3 * c + 1] = sy * inv;
-    out[3 * c + 2] = sz * inv;
 }
 
 template <typename T>
@@ -91,11 +76,19 @@ __global__ void __launch_bounds__(256) unpool_kernel(const T* __restrict__ skip,
 {
     using V = Vec<T>;
     const int vec_per_row = C / V::N;
+    const int vpr_shift = (vec_per_row & (vec_per_row - 1)) == 0 ? __ffs(vec_per_row) - 1 : -1;
     const int64_t total = n * vec_per_row;
     for (int64_t t = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; t < total;
          t += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t i = t / vec_per_row;
-        const int ch = (int)(t % vec_per_row) * V::N;
+        int64_t i;
+        int ch;
+        if (vpr_shift >= 0) {
+            i = t >> vpr_shift;
+            ch = (int)(t & (vec_per_row - 1)) * V::N;
+        } else {
+            i = t / vec_per_row;
+            ch = (int)(t % vec_per_row) * V::N;
+        }
         const int64_t cl = cluster[i];
         float a[V::N], b[V::N], o[V::N];
         V::unpack(*reinterpret_cast<const typename V::Raw*>(skip + i * C + ch), a);
@@ -133,18 +126,30 @@ extern "C" int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* i
     if (m == 0) return PTV3_OK;
     PTV3_REQUIRE(x && indices && idx_ptr && out, PTV3_ERR_INVALID_ARGUMENT, "ptv3_pool_fwd: null pointer");
     cudaStream_t stream = (cudaStream_t)stream_;
-    const unsigned blocks = (unsigned)((m * 32 + 255) / 256);
-    if (dtype == PTV3_DTYPE_F32)
-        pool_max_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, indices, idx_ptr, m, channels,
-                                                           bn_scale, bn_shift, (float*)out);
-    else
-        pool_max_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
-            (const __nv_bfloat16*)x, indices, idx_ptr, m, channels, bn_scale, bn_shift,
-            (__nv_bfloat16*)out);
-    if (coord && coord_out)
-        pool_coord_mean_kernel<<<(unsigned)((m + 255) / 256), 256, 0, stream>>>(coord, indices, idx_ptr,
-                                                                               m, coord_out);
-    count_launches((coord && coord_out) ? 2 : 1);
+    const bool with_coord = coord && coord_out;
+    const int vectors = channels / vn;
+    int lanes = 4;   // at least 3 for the coordinate lanes
+    while (lanes < 32 && lanes < vectors) lanes *= 2;
+    const unsigned blocks = (unsigned)((m * lanes + 255) / 256);
+#define PTV3_POOL_LAUNCH(T, L)                                                                          \
+    pool_max_kernel<T, L><<<blocks, 256, 0, stream>>>((const T*)x, with_coord ? coord : nullptr, indices, \
+                                                      idx_ptr, m, channels, bn_scale, bn_shift, (T*)out, \
+                                                      with_coord ? coord_out : nullptr)
+#define PTV3_POOL_DISPATCH(T)                      \
+    switch (lanes) {                               \
+        case 4: PTV3_POOL_LAUNCH(T, 4); break;     \
+        case 8: PTV3_POOL_LAUNCH(T, 8); break;     \
+        case 16: PTV3_POOL_LAUNCH(T, 16); break;   \
+        default: PTV3_POOL_LAUNCH(T, 32); break;   \
+    }
+    if (dtype == PTV3_DTYPE_F32) {
+        PTV3_POOL_DISPATCH(float)
+    } else {
+        PTV3_POOL_DISPATCH(__nv_bfloat16)
+    }
+#undef PTV3_POOL_DISPATCH
+#undef PTV3_POOL_LAUNCH
+    count_launches(1);
     return check_launch("ptv3_pool_fwd");
 }
 

@@ -66,6 +66,19 @@ def encode(grid_coord, batch, depth, orders):
     return codes
 
 
+def decode(code, depth, order):
+    """(N,) int64 codes -> (grid_coord (N,3) int64, batch (N,) int64); order "z" or "hilbert"."""
+    _lib.require_cuda(code)
+    lib = _lib.load()
+    code = code.to(torch.int64).contiguous().reshape(-1)
+    n = code.shape[0]
+    grid = torch.empty((n, 3), dtype=torch.int64, device=code.device)
+    batch = torch.empty(n, dtype=torch.int64, device=code.device)
+    _lib.check(lib.ptv3_decode(_lib.ptr(code), n, int(depth), ORDER_IDS[order], _lib.ptr(grid), _lib.ptr(batch),
+                               _lib.stream()), "ptv3_decode")
+    return grid, batch
+
+
 def argsort_inverse(codes, sig_bits):
     """codes (k,N) int64 -> (order, inverse), both (k,N) int64, stable."""
     _lib.require_cuda(codes)

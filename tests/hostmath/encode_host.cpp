@@ -53,3 +53,21 @@ extern "C" void host_encode(const int32_t* grid, int64_t n, int depth, int order
         out[i] = (int64_t)c;
     }
 }
+
+extern "C" void host_decode(const int64_t* code, int64_t n, int depth, int hilbert, int64_t* out)
+{
+    for (int64_t i = 0; i < n; ++i) {
+        uint32_t x, y, z;
+        const uint64_t c = (uint64_t)code[i] & ((1ull << (3 * depth)) - 1ull);
+        if (hilbert) {
+            hilbert3_inverse(c, depth, x, y, z);
+        } else {
+            x = compact3(c >> 2);
+            y = compact3(c >> 1);
+            z = compact3(c);
+        }
+        out[3 * i] = x;
+        out[3 * i + 1] = y;
+        out[3 * i + 2] = z;
+    }
+}

@@ -20,6 +20,7 @@ def hostlib(tmp_path_factory):
     lib = ctypes.CDLL(so)
     lib.host_encode.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                 ctypes.c_void_p]
+    lib.host_decode.argtypes = [ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
     return lib
 
 
@@ -32,3 +33,15 @@ def test_kernel_integer_math_matches_oracle(hostlib, use_lut):
             out = np.empty(4000, dtype=np.int64)
             hostlib.host_encode(g.ctypes.data, 4000, depth, oid, use_lut, out.ctypes.data)
             assert (out == cenc.encode(g, None, depth, name)).all(), (depth, name)
+
+
+def test_kernel_decode_math_inverts_encode(hostlib):
+    rng = np.random.default_rng(6)
+    for depth in range(1, 17):
+        g = rng.integers(0, 1 << depth, size=(3000, 3)).astype(np.int64)
+        for hilbert, name in ((0, "z"), (1, "hilbert")):
+            code = cenc.encode(g, None, depth, name)
+            out = np.empty((3000, 3), dtype=np.int64)
+            hostlib.host_decode(code.ctypes.data, 3000, depth, hilbert, out.ctypes.data)
+            assert (out == g).all(), (depth, name)
+            assert (cenc.decode(code, depth, name)[0] == g).all()

@@ -79,3 +79,19 @@ def test_large_sort_properties():
     codes = ops.encode(gc, batch, 11, ORDERS)
     order, inverse = ops.argsort_inverse(codes, 33 + 4)
     _check_sorted(codes, order, inverse)
+
+
+@pytest.mark.parametrize("depth", [1, 4, 9, 16])
+def test_decode_inverts_encode(depth):
+    """serialization.decode for "z" and "hilbert": coordinates and scene ids back."""
+    from pointtransformerv3_b200 import serialization
+    rng = np.random.default_rng(depth)
+    g = rng.integers(0, 1 << depth, size=(4000, 3)).astype(np.int32)
+    b = rng.integers(0, 6, size=4000).astype(np.int64)
+    for name in ("z", "hilbert"):
+        code = serialization.encode(torch.from_numpy(g).cuda(), torch.from_numpy(b).cuda(), depth, name)
+        grid, batch = serialization.decode(code, depth, name)
+        assert grid.dtype == torch.int64 and grid.shape == (4000, 3)
+        assert (grid.cpu().numpy() == g).all() and (batch.cpu().numpy() == b).all()
+        og, ob = cenc.decode(code.cpu().numpy(), depth, name)
+        assert (grid.cpu().numpy() == og).all() and (batch.cpu().numpy() == ob).all()
