@@ -121,9 +121,9 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
             qa[1] = scale_bf16x2(qp[t], scale);
             qa[3] = scale_bf16x2(qp[4 + t], scale);
         }
-        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0, l1;
         float o[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-        float osum[4] = {0.f, 0.f, 0.f, 0.f};   // PACKED: row sums from a ones column of V
+        float osum[4] = {0.f, 0.f, 0.f, 0.f};   // row sums of the rounded probabilities: a ones column of V
 
         for (int kc = 0; kc < Lp; kc += AM_KC) {
             float s[8][4];
@@ -144,11 +144,12 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
                     if (col + 1 >= L) s[j][1] = s[j][3] = -INFINITY;
                 }
             }
-            float mx0 = s[0][0], mx1 = s[0][2];
+            // three-input maxima (one instruction each on this architecture)
+            float mx0 = fmaxf(s[0][0], s[0][1]), mx1 = fmaxf(s[0][2], s[0][3]);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
-                mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+            for (int j = 1; j < 8; ++j) {
+                mx0 = fmaxf(fmaxf(mx0, s[j][0]), s[j][1]);
+                mx1 = fmaxf(fmaxf(mx1, s[j][2]), s[j][3]);
             }
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
             mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
@@ -159,8 +160,6 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
             const float c0 = fast_exp2((m0 - mn0) * sl2), c1 = fast_exp2((m1 - mn1) * sl2);
             m0 = mn0;
             m1 = mn1;
-            l0 *= c0;
-            l1 *= c1;
             osum[0] *= c0;
             osum[2] *= c1;
 #pragma unroll
@@ -184,8 +183,6 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
                     const float p1 = fast_exp2(fmaf(s[j][1], sl2, -b0));
                     const float p2 = fast_exp2(fmaf(s[j][2], sl2, -b1));
                     const float p3 = fast_exp2(fmaf(s[j][3], sl2, -b1));
-                    l0 += p0 + p1;
-                    l1 += p2 + p3;
                     pa[j][0] = pack_bf16(p0, p1);
                     pa[j][1] = pack_bf16(p2, p3);
                 }
@@ -198,18 +195,11 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
                 mma_bf16(o[0], a, vb[0], vb[1]);
                 mma_bf16(o[1], a, vb[2], vb[3]);
                 // a column of ones appended to V: the tensor core sums the rounded probabilities
-                if (PACKED) mma_bf16(osum, a, 0x3f803f80u, 0x3f803f80u);
+                mma_bf16(osum, a, 0x3f803f80u, 0x3f803f80u);
             }
         }
-        if (PACKED) {
-            l0 = osum[0];
-            l1 = osum[2];
-        } else {
-            l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-            l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-            l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-        }
+        l0 = osum[0];
+        l1 = osum[2];
         if (ok0 && own0) {
             const float inv = 1.f / l0;
             uint32_t* op = reinterpret_cast<uint32_t*>(out + src0 * (int64_t)C + h * AM_D);
