@@ -302,6 +302,28 @@ int ptv3_mlp_fwd(const void* x, const void* fc1_weight, const void* fc1_bias, co
                  const void* fc2_bias, const void* residual, void* out, int64_t n, int channels,
                  int hidden, int dtype, uint32_t* status, void* stream);
 
+/*
+ * Linear layers of a block on the tcgen05 tensor cores (bf16, input width k in
+ * {32, 64, 128}), weight in nn.Linear layout (n_out x k).
+ *   ptv3_linear_fwd      out = x W^T + b, n_out a multiple of 32 up to 384.
+ *                        Replaces the qkv projection, model.py:456.
+ *   ptv3_linear_ln_fwd   y = x W^T + b (square, channels = k);
+ *                        t = LayerNorm(y; ln1) if ln1 given else y;
+ *                        sum_out = residual + t;  norm_out = LayerNorm(sum_out; ln2).
+ *                        Replaces cpe.1 + cpe.2 + shortcut + norm1 (model.py:553-554,
+ *                        589-592) and attn.proj + shortcut + norm2 (model.py:487, 594,
+ *                        598-600).  sum_out may be NULL; it may alias residual.
+ * ptv3_linear_supported() tells whether a shape is covered; other shapes use a
+ * library GEMM followed by ptv3_add_layernorm_fwd.
+ */
+int ptv3_linear_supported(int k, int n_out, int residual_mode, int dtype);
+int ptv3_linear_fwd(const void* x, const void* weight, const void* bias, void* out, int64_t n, int k,
+                    int n_out, int dtype, uint32_t* status, void* stream);
+int ptv3_linear_ln_fwd(const void* x, const void* weight, const void* bias, const void* residual,
+                       const void* ln1_weight, const void* ln1_bias, float ln1_eps, void* sum_out,
+                       const void* ln2_weight, const void* ln2_bias, float ln2_eps, void* norm_out,
+                       int64_t n, int channels, int dtype, uint32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

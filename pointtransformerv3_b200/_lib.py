@@ -49,6 +49,10 @@ SIGNATURES = {
                               c_ptr]),
     "ptv3_add_layernorm_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_f32, c_ptr,
                                        c_i64, c_int, c_int, c_ptr]),
+    "ptv3_linear_supported": (c_int, [c_int, c_int, c_int, c_int]),
+    "ptv3_linear_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int, c_ptr, c_ptr]),
+    "ptv3_linear_ln_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_f32,
+                                   c_ptr, c_i64, c_int, c_int, c_ptr, c_ptr]),
     "ptv3_mlp_supported": (c_int, [c_int, c_int, c_int]),
     "ptv3_mlp_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int, c_ptr,
                              c_ptr]),

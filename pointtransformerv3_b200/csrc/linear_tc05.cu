@@ -1,0 +1,455 @@
+// Linear layers of a block on the 5th-generation tensor cores, with the row-wise
+// glue that follows them fused into the epilogue:
+//
+//   plain      out = x W^T + b                                  (qkv, model.py:456)
+//   residual   y   = x W^T + b
+//              t   = ln1 ? LayerNorm(y; ln1) : y
+//              s   = residual + t                   -> sum_out
+//              out = LayerNorm(s; ln2)              -> norm_out
+//     which is  cpe.1 + cpe.2 + shortcut + norm1     (model.py:553-554, 589-592)
+//     and       attn.proj + shortcut + norm2         (model.py:487, 594, 598-600)
+//
+// bf16, input width K in {32, 64, 128}.  A persistent CTA keeps W in shared memory
+// (TMA, once) and runs up to four independent 128-thread groups; a group loads a
+// 128-row x tile by TMA, issues K/16 tcgen05.mma into its slice of tensor memory and
+// owns one accumulator row per thread, so LayerNorm statistics are thread-local
+// (no shuffles).  The residual sum is parked in tensor memory (tcgen05.st) between the
+// pass that forms it and the pass that normalises it.  Every intermediate the unfused
+// sequence would round to bf16 is rounded at the same place.  Waits are bounded.
+#include "common.cuh"
+#include "tc05.cuh"
+#include "vec.cuh"
+
+namespace ptv3 {
+
+using namespace tc05;
+
+struct LinearArgs {
+    const __nv_bfloat16* bias;       // n_out or NULL
+    __nv_bfloat16* out;              // plain mode: n x n_out
+    const __nv_bfloat16* residual;   // residual mode: n x n_out
+    const __nv_bfloat16* ln1_w;      // optional
+    const __nv_bfloat16* ln1_b;
+    const __nv_bfloat16* ln2_w;      // required in residual mode
+    const __nv_bfloat16* ln2_b;
+    __nv_bfloat16* sum_out;
+    __nv_bfloat16* norm_out;
+    float eps1, eps2;
+    int64_t n;
+    int n_out;
+    int groups;       // 128-thread groups that work (1..4)
+    int w_box_rows;   // rows per TMA box of W
+    int residual_mode;
+    uint32_t* status;
+};
+
+__device__ __forceinline__ float lin_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// Staging tile of a group: 128 rows x 64 bf16 columns, rows 144 bytes apart, so that
+// both the row-per-thread accesses of the epilogue and the coalesced copies to and
+// from global memory (consecutive threads on consecutive 16-byte pieces) are free of
+// bank conflicts.  Global rows are `pitch` elements wide; `col0` is the slab's column.
+constexpr int LIN_STAGE_ROW = 144;
+constexpr int LIN_STAGE_BYTES = 128 * LIN_STAGE_ROW;
+
+__device__ __forceinline__ void stage_to_global(const unsigned char* stage, __nv_bfloat16* dst, int64_t row0,
+                                                int64_t n, int pitch, int col0, int t)
+{
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+        if (row0 + r < n)
+            *reinterpret_cast<uint4*>(dst + (row0 + r) * pitch + col0 + c * 8) =
+                *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
+    }
+}
+
+__device__ __forceinline__ void global_to_stage(unsigned char* stage, const __nv_bfloat16* src, int64_t row0,
+                                                int64_t n, int pitch, int col0, int t)
+{
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row0 + r < n) v = *reinterpret_cast<const uint4*>(src + (row0 + r) * pitch + col0 + c * 8);
+        *reinterpret_cast<uint4*>(stage + r * LIN_STAGE_ROW + c * 16) = v;
+    }
+}
+
+template <int K>
+__global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_constant__ CUtensorMap map_x,
+                                                             const __grid_constant__ CUtensorMap map_w,
+                                                             const LinearArgs a)
+{
+    constexpr int SW = K >= 64 ? 128 : 64;       // bytes per shared-memory row (swizzle span)
+    constexpr int KB = K >= 64 ? K / 64 : 1;     // 64-wide K blocks
+    constexpr int KCOLS = K >= 64 ? 64 : K;      // columns per K block
+    constexpr int X_BLOCK = 128 * SW;            // one K block of an x tile
+    constexpr int X_BYTES = KB * X_BLOCK;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = smem_u32_generic(smem);
+    const int n_out = a.n_out;
+    const int w_block = n_out * SW;              // one K block of W
+    const int off_x = KB * w_block;              // x tiles of the groups
+    const int off_stage = off_x + 2 * a.groups * X_BYTES;   // (x tiles are double buffered) one staging tile per group
+    const int off_par = off_stage + a.groups * LIN_STAGE_BYTES;   // bias, ln1 w/b, ln2 w/b as floats (5 x n_out)
+    const int off_bar = off_par + 5 * n_out * 4;
+    float* par = reinterpret_cast<float*>(smem + off_par);
+    float *bias_s = par, *g1 = par + n_out, *b1 = par + 2 * n_out, *g2 = par + 3 * n_out, *b2 = par + 4 * n_out;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off_bar);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int g = tid >> 7, t = tid & 127;
+    const uint32_t wbar = sbase + off_bar;
+    const uint32_t xbar0 = wbar + 8 * (1 + 2 * g), mbar = wbar + 8 * (9 + g);   // xbar0 + 8: second x buffer
+
+    if (tid == 0) {
+        for (int i = 0; i < 13; ++i) mbar_init(wbar + 8 * i, 1);
+        *abort = 0;
+        fence_barrier_init();
+        prefetch_tensormap(&map_x);
+        prefetch_tensormap(&map_w);
+    }
+    for (int i = tid; i < n_out; i += 512) {
+        bias_s[i] = a.bias ? __bfloat162float(a.bias[i]) : 0.f;
+        g1[i] = a.ln1_w ? __bfloat162float(a.ln1_w[i]) : 1.f;
+        b1[i] = a.ln1_b ? __bfloat162float(a.ln1_b[i]) : 0.f;
+        g2[i] = a.ln2_w ? __bfloat162float(a.ln2_w[i]) : 1.f;
+        b2[i] = a.ln2_b ? __bfloat162float(a.ln2_b[i]) : 0.f;
+    }
+    if (warp == 0) tmem_alloc(sbase + off_bar + 104, 512);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (tid == 0) {   // weights: once per CTA
+        mbar_expect_tx(wbar, (uint32_t)(KB * w_block));
+        for (int kb = 0; kb < KB; ++kb)
+            for (int r = 0; r < n_out; r += a.w_box_rows)
+                tma_load_2d(sbase + kb * w_block + r * SW, &map_w, kb * KCOLS, r, wbar);
+    }
+    bool ok = mbar_wait(wbar, 0, abort);
+
+    // columns of tensor memory per group: n_out rounded up to 32, groups side by side
+    const int tm_cols = (n_out + 31) / 32 * 32;
+    const uint32_t tm_lane = (uint32_t)((warp & 3) * 32) << 16;
+    const uint32_t tm_acc = tmem_base + tm_lane + g * tm_cols;
+    const uint32_t tm_acc_mma = tmem_base + g * tm_cols;
+    const uint32_t xs0 = sbase + off_x + 2 * g * X_BYTES;   // two x buffers
+    unsigned char* stage = smem + off_stage + g * LIN_STAGE_BYTES;
+    unsigned char* my_row = stage + t * LIN_STAGE_ROW;
+    // columns are handled in slabs of 64 (32 when n_out is 32 or 96 leaves a half slab)
+    const int nslabs = (n_out + 63) / 64;
+    // one MMA covers at most 256 output columns
+    const int n_half = n_out > 256 ? n_out / 2 : n_out;
+    const uint32_t idesc = umma_idesc_bf16(128, n_half);
+    uint32_t xph[2] = {0, 0}, mph = 0;
+    const float inv_c = 1.f / (float)n_out;
+    const int nchunks = n_out / 32;
+
+    const int64_t ntiles = (a.n + 127) / 128;
+    if (g < a.groups) {
+        const int64_t tile_step = (int64_t)gridDim.x * a.groups;
+        const int64_t tile0 = (int64_t)blockIdx.x * a.groups + g;
+        auto load_x = [&](int64_t tile, int b) {
+            mbar_expect_tx(xbar0 + 8 * b, X_BYTES);
+            for (int kb = 0; kb < KB; ++kb)
+                tma_load_2d(xs0 + b * X_BYTES + kb * X_BLOCK, &map_x, kb * KCOLS, (int)(tile * 128), xbar0 + 8 * b);
+        };
+        if (t == 0 && tile0 < ntiles) load_x(tile0, 0);
+        int buf = 0;
+        for (int64_t tile = tile0; tile < ntiles; tile += tile_step, buf ^= 1) {
+            const int64_t row0 = tile * 128;
+            const uint32_t xs = xs0 + buf * X_BYTES;
+            ok &= mbar_wait(xbar0 + 8 * buf, xph[buf], abort);
+            xph[buf] ^= 1;
+            if (t == 0) {
+                // the other buffer was consumed by the previous tile's MMAs, which have completed:
+                // fetch the next tile into it while this tile is multiplied and written out
+                if (tile + tile_step < ntiles) load_x(tile + tile_step, buf ^ 1);
+                fence_after_sync();
+                for (int h = 0; h < n_out; h += n_half) {
+#pragma unroll
+                    for (int k = 0; k < K / 16; ++k) {
+                        const int kb = (k * 16) / KCOLS, kk = (k * 16) % KCOLS;
+                        const uint64_t da = umma_desc_kmajor(xs + kb * X_BLOCK + kk * 2, SW);
+                        const uint64_t db = umma_desc_kmajor(sbase + kb * w_block + h * SW + kk * 2, SW);
+                        umma_bf16(tm_acc_mma + h, da, db, idesc, k > 0);
+                    }
+                }
+                umma_commit(mbar);
+            }
+            ok &= mbar_wait(mbar, mph, abort);
+            mph ^= 1;
+            fence_after_sync();
+            const int64_t row = row0 + t;
+            const bool live = row < a.n;
+            if (!a.residual_mode) {
+                for (int sl = 0; sl < nslabs; ++sl) {
+                    const int cw = min(64, n_out - sl * 64);   // 64 or 32 columns in this slab
+                    for (int c = 0; c < cw / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tm_acc + sl * 64 + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i)
+                                f[i] = __uint_as_float(v[q * 8 + i]) + bias_s[sl * 64 + c * 32 + q * 8 + i];
+                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = Vec<__nv_bfloat16>::pack(f);
+                        }
+                    }
+                    named_barrier(1 + g, 128);
+                    if (cw == 64) {
+                        stage_to_global(stage, a.out, row0, a.n, n_out, sl * 64, t);
+                    } else {   // half slab: 4 pieces per row
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                            if (row0 + r < a.n)
+                                *reinterpret_cast<uint4*>(a.out + (row0 + r) * n_out + sl * 64 + c * 8) =
+                                    *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
+                        }
+                    }
+                    named_barrier(1 + g, 128);
+                }
+            } else {
+                // ---- first LayerNorm (optional): statistics of y = round(acc + bias)
+                float mean1 = 0.f, rstd1 = 1.f;
+                if (a.ln1_w) {
+                    // one pass with sums shifted by the row's first value (no cancellation)
+                    float sh = 0.f, s1 = 0.f, q1 = 0.f;
+                    for (int c = 0; c < nchunks; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tm_acc + c * 32, v);
+                        tmem_ld_wait();
+                        if (c == 0) sh = lin_round(__uint_as_float(v[0]) + bias_s[0]);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            const float d = lin_round(__uint_as_float(v[i]) + bias_s[c * 32 + i]) - sh;
+                            s1 += d;
+                            q1 = fmaf(d, d, q1);
+                        }
+                    }
+                    const float md1 = s1 * inv_c;
+                    mean1 = sh + md1;
+                    rstd1 = rsqrtf(fmaxf(q1 * inv_c - md1 * md1, 0.f) + a.eps1);
+                }
+                // ---- s = residual + t, stored and parked in tensor memory; shifted sums for LN2
+                float shift = 0.f, s2 = 0.f, q2 = 0.f;
+                for (int sl = 0; sl < nslabs; ++sl) {
+                    const int cw = min(64, n_out - sl * 64);
+                    // residual slab: coalesced into the staging tile
+                    if (cw == 64) {
+                        global_to_stage(stage, a.residual, row0, a.n, n_out, sl * 64, t);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                            uint4 v = make_uint4(0, 0, 0, 0);
+                            if (row0 + r < a.n)
+                                v = *reinterpret_cast<const uint4*>(a.residual + (row0 + r) * n_out + sl * 64 + c * 8);
+                            *reinterpret_cast<uint4*>(stage + r * LIN_STAGE_ROW + c * 16) = v;
+                        }
+                    }
+                    named_barrier(1 + g, 128);
+                    for (int c = 0; c < cw / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tm_acc + sl * 64 + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float r[8], f[8];
+                            Vec<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(my_row + c * 64 + q * 16), r);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int ch = sl * 64 + c * 32 + q * 8 + i;
+                                float y = lin_round(__uint_as_float(v[q * 8 + i]) + bias_s[ch]);
+                                if (a.ln1_w) y = lin_round(fmaf((y - mean1) * rstd1, g1[ch], b1[ch]));
+                                const float sv = lin_round(r[i] + y);
+                                if (ch == 0) shift = sv;
+                                const float d = sv - shift;
+                                s2 += d;
+                                q2 = fmaf(d, d, q2);
+                                f[i] = sv;
+                                v[q * 8 + i] = __float_as_uint(sv);
+                            }
+                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = Vec<__nv_bfloat16>::pack(f);
+                        }
+                        tmem_st32(tm_acc + sl * 64 + c * 32, v);
+                    }
+                    named_barrier(1 + g, 128);
+                    if (a.sum_out) {
+                        if (cw == 64) {
+                            stage_to_global(stage, a.sum_out, row0, a.n, n_out, sl * 64, t);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                                if (row0 + r < a.n)
+                                    *reinterpret_cast<uint4*>(a.sum_out + (row0 + r) * n_out + sl * 64 + c * 8) =
+                                        *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
+                            }
+                        }
+                    }
+                    named_barrier(1 + g, 128);
+                }
+                tmem_st_wait();
+                const float md = s2 * inv_c;                      // mean - shift
+                const float var = fmaxf(q2 * inv_c - md * md, 0.f);
+                const float mean2 = shift + md, rstd2 = rsqrtf(var + a.eps2);
+                for (int sl = 0; sl < nslabs; ++sl) {
+                    const int cw = min(64, n_out - sl * 64);
+                    for (int c = 0; c < cw / 32; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tm_acc + sl * 64 + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            float f[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int ch = sl * 64 + c * 32 + q * 8 + i;
+                                f[i] = fmaf((__uint_as_float(v[q * 8 + i]) - mean2) * rstd2, g2[ch], b2[ch]);
+                            }
+                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = Vec<__nv_bfloat16>::pack(f);
+                        }
+                    }
+                    named_barrier(1 + g, 128);
+                    if (cw == 64) {
+                        stage_to_global(stage, a.norm_out, row0, a.n, n_out, sl * 64, t);
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                            if (row0 + r < a.n)
+                                *reinterpret_cast<uint4*>(a.norm_out + (row0 + r) * n_out + sl * 64 + c * 8) =
+                                    *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
+                        }
+                    }
+                    named_barrier(1 + g, 128);
+                }
+            }
+            fence_before_sync();
+            named_barrier(1 + g, 128);
+        }
+    }
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+    if (tid == 0 && (*abort || !ok)) atomicOr(a.status, PTV3_STATUS_WAIT_LIMIT);
+}
+
+static bool linear_shape_ok(int k, int n_out, bool residual_mode)
+{
+    if (k != 32 && k != 64 && k != 128) return false;
+    if (residual_mode) return n_out == k;
+    return n_out % 32 == 0 && n_out >= 32 && n_out <= 384 && (n_out <= 256 || (n_out / 2) % 16 == 0);
+}
+
+static int launch_linear(const void* x, const void* w, LinearArgs a, int k, cudaStream_t stream)
+{
+    const int sw = k >= 64 ? 128 : 64, kb = k >= 64 ? k / 64 : 1, kcols = k >= 64 ? 64 : k;
+    a.w_box_rows = a.n_out <= 256 ? a.n_out : a.n_out / 2;
+    const int tm_cols = (a.n_out + 31) / 32 * 32;
+    int groups = 512 / tm_cols;
+    if (groups > 4) groups = 4;
+    // ... and as many as fit in shared memory next to the resident weights
+    while (groups > 1 && (size_t)kb * a.n_out * sw + (size_t)groups * (2 * kb * 128 * sw + LIN_STAGE_BYTES) +
+                                 5 * (size_t)a.n_out * 4 + 128 + 1024 > 220 * 1024)
+        --groups;
+    a.groups = groups;
+    CUtensorMap mx, mw;
+    int rc = make_tensor_map_bf16(&mx, x, (uint64_t)a.n, k, (uint64_t)k * 2, 128, kcols);
+    if (rc) return rc;
+    rc = make_tensor_map_bf16(&mw, w, a.n_out, k, (uint64_t)k * 2, a.w_box_rows, kcols);
+    if (rc) return rc;
+    const size_t smem = (size_t)kb * a.n_out * sw + (size_t)groups * (2 * kb * 128 * sw + LIN_STAGE_BYTES) +
+                        5 * (size_t)a.n_out * 4 + 128 + 1024;
+    const size_t smem_req = smem < 120 * 1024 ? 120 * 1024 : smem;   // one CTA per SM (it takes all of tensor memory)
+    const int64_t ntiles = (a.n + 127) / 128;
+    int64_t grid = (ntiles + groups - 1) / groups;
+    if (grid > 148) grid = 148;
+#define LIN_LAUNCH(KK)                                                                                       \
+    do {                                                                                                     \
+        auto kern = linear_tc05_kernel<KK>;                                                                  \
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req) !=        \
+            cudaSuccess)                                                                                     \
+            return check_launch("ptv3_linear_fwd: shared memory attribute");                                 \
+        kern<<<(unsigned)grid, 512, smem_req, stream>>>(mx, mw, a);                                          \
+    } while (0)
+    if (k == 32) LIN_LAUNCH(32);
+    else if (k == 64) LIN_LAUNCH(64);
+    else LIN_LAUNCH(128);
+#undef LIN_LAUNCH
+    count_launches(1);
+    return check_launch("ptv3_linear_fwd");
+}
+
+}  // namespace ptv3
+
+extern "C" int ptv3_linear_supported(int k, int n_out, int residual_mode, int dtype)
+{
+    return dtype == PTV3_DTYPE_BF16 && ptv3::linear_shape_ok(k, n_out, residual_mode != 0);
+}
+
+extern "C" int ptv3_linear_fwd(const void* x, const void* weight, const void* bias, void* out, int64_t n, int k,
+                               int n_out, int dtype, uint32_t* status, void* stream)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0 && n < (1ll << 31), PTV3_ERR_INVALID_ARGUMENT, "ptv3_linear_fwd: bad n");
+    PTV3_REQUIRE(ptv3_linear_supported(k, n_out, 0, dtype), PTV3_ERR_UNSUPPORTED,
+                 "ptv3_linear_fwd: supported: bf16, k in {32, 64, 128}, n_out a multiple of 32 up to 384");
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(x && weight && out && status, PTV3_ERR_INVALID_ARGUMENT, "ptv3_linear_fwd: null pointer");
+    PTV3_REQUIRE((((uintptr_t)x | (uintptr_t)weight | (uintptr_t)out) & 15) == 0, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_linear_fwd: tensors must be 16-byte aligned");
+    LinearArgs a{};
+    a.bias = (const __nv_bfloat16*)bias;
+    a.out = (__nv_bfloat16*)out;
+    a.n = n;
+    a.n_out = n_out;
+    a.residual_mode = 0;
+    a.status = status;
+    return launch_linear(x, weight, a, k, (cudaStream_t)stream);
+}
+
+extern "C" int ptv3_linear_ln_fwd(const void* x, const void* weight, const void* bias, const void* residual,
+                                  const void* ln1_weight, const void* ln1_bias, float ln1_eps, void* sum_out,
+                                  const void* ln2_weight, const void* ln2_bias, float ln2_eps, void* norm_out,
+                                  int64_t n, int channels, int dtype, uint32_t* status, void* stream)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n >= 0 && n < (1ll << 31), PTV3_ERR_INVALID_ARGUMENT, "ptv3_linear_ln_fwd: bad n");
+    PTV3_REQUIRE(ptv3_linear_supported(channels, channels, 1, dtype), PTV3_ERR_UNSUPPORTED,
+                 "ptv3_linear_ln_fwd: supported: bf16, channels in {32, 64, 128}");
+    PTV3_REQUIRE((ln1_weight == nullptr) == (ln1_bias == nullptr), PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_linear_ln_fwd: LayerNorm weight and bias go together");
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(x && weight && residual && ln2_weight && ln2_bias && norm_out && status,
+                 PTV3_ERR_INVALID_ARGUMENT, "ptv3_linear_ln_fwd: null pointer");
+    PTV3_REQUIRE((((uintptr_t)x | (uintptr_t)weight | (uintptr_t)residual | (uintptr_t)norm_out |
+                   (uintptr_t)sum_out) & 15) == 0,
+                 PTV3_ERR_INVALID_ARGUMENT, "ptv3_linear_ln_fwd: tensors must be 16-byte aligned");
+    LinearArgs a{};
+    a.bias = (const __nv_bfloat16*)bias;
+    a.residual = (const __nv_bfloat16*)residual;
+    a.ln1_w = (const __nv_bfloat16*)ln1_weight;
+    a.ln1_b = (const __nv_bfloat16*)ln1_bias;
+    a.ln2_w = (const __nv_bfloat16*)ln2_weight;
+    a.ln2_b = (const __nv_bfloat16*)ln2_bias;
+    a.sum_out = (__nv_bfloat16*)sum_out;
+    a.norm_out = (__nv_bfloat16*)norm_out;
+    a.eps1 = ln1_eps;
+    a.eps2 = ln2_eps;
+    a.n = n;
+    a.n_out = channels;
+    a.residual_mode = 1;
+    a.status = status;
+    return launch_linear(x, weight, a, channels, (cudaStream_t)stream);
+}

@@ -152,17 +152,19 @@ class SerializedAttention(PointModule):
             point["pad"], point["unpad"], point["cu_seqlens_key"] = pad, unpad, cu
         return point["pad"], point["unpad"], point["cu_seqlens_key"]
 
-    def attend(self, point, feat):
-        """qkv projection, patch attention over ``point``'s serialized order and
-        output projection of the feature matrix ``feat``."""
+    def core(self, point, qkv):
+        """Patch attention of an already projected (N, 3C) qkv matrix over
+        ``point``'s serialized order; the output projection is not applied."""
         assert not self.training, "inference only"
         if not self.enable_flash:
             self.patch_size = min(min(point.host_counts()), self.patch_size_max)
         pad, unpad, cu_seqlens = self.get_padding_and_inverse(point)
-        qkv = self.qkv(feat)
-        feat = ops.attention(qkv, point.serialized_order[self.order_index], pad, unpad, cu_seqlens,
+        return ops.attention(qkv, point.serialized_order[self.order_index], pad, unpad, cu_seqlens,
                              self.num_heads, self.patch_size, self.scale, self.algo)
-        return self.proj_drop(self.proj(feat))
+
+    def attend(self, point, feat):
+        """qkv projection, patch attention and output projection of ``feat``."""
+        return self.proj_drop(self.proj(self.core(point, self.qkv(feat))))
 
     def forward(self, point):
         point.feat = self.attend(point, point.feat)
@@ -233,12 +235,23 @@ class Block(PointModule):
         additions done by the fused row kernel (three launches instead of eight)."""
         shortcut = point.feat
         sparse = point.sparse_conv_feat
+        status = point.device_status()
+        C, dt = self.channels, shortcut.dtype
+        attn, lin = self.attn, self.cpe[1]
         # the convolution reads the sparse tensor's features, which differ from
         # `feat` right after an unpooling (model.py:233-236, 744-746)
-        x = self.cpe[1](self.cpe[0](sparse).features)
-        feat, normed = ops.add_layernorm(x, shortcut, self.cpe[2], self.norm1[0])
-        x = self.attn.attend(point, normed)
-        feat, normed = ops.add_layernorm(x, feat, None, self.norm2[0])
+        x = self.cpe[0](sparse).features
+        if (lin.bias is not None and attn.qkv.bias is not None and ops.linear_supported(C, C, True, dt)
+                and ops.linear_supported(C, 3 * C, False, dt)):
+            # Linear layers with their LayerNorm / residual glue in the GEMM epilogue (tcgen05)
+            feat, normed = ops.linear_ln(x, lin.weight, lin.bias, shortcut, self.cpe[2], self.norm1[0], status)
+            x = attn.core(point, ops.linear(normed, attn.qkv.weight, attn.qkv.bias, status))
+            feat, normed = ops.linear_ln(x, attn.proj.weight, attn.proj.bias, feat, None, self.norm2[0], status)
+            point.check_status("tcgen05 linear layers")
+        else:
+            feat, normed = ops.add_layernorm(lin(x), shortcut, self.cpe[2], self.norm1[0])
+            x = attn.attend(point, normed)
+            feat, normed = ops.add_layernorm(x, feat, None, self.norm2[0])
         mlp = self.mlp[0]
         if (mlp.fc1.bias is not None and mlp.fc2.bias is not None
                 and ops.mlp_supported(mlp.fc1.in_features, mlp.fc1.out_features, normed.dtype)

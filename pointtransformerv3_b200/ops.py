@@ -394,3 +394,49 @@ def subm_conv_pairs(feat, pairs, weight, bias=None):
             _lib.ptr(ws), nbytes, n, cin, cout, pairs["kvol"], _lib.dtype_id(feat), _lib.stream()),
             "ptv3_subm_conv_pairs_fwd")
     return out
+
+
+def linear_supported(k, n_out, residual_mode, dtype):
+    return dtype in _lib.DTYPE_IDS and bool(
+        _lib.load().ptv3_linear_supported(int(k), int(n_out), int(bool(residual_mode)), _lib.DTYPE_IDS[dtype]))
+
+
+def linear(x, weight, bias, status=None):
+    """out = x W^T + b on the tcgen05 path (see ptv3_linear_fwd)."""
+    _lib.require_cuda(x, weight, bias)
+    lib = _lib.load()
+    x = x.contiguous()
+    n, k = x.shape
+    n_out = weight.shape[0]
+    out = torch.empty((n, n_out), dtype=x.dtype, device=x.device)
+    own = status is None
+    if own:
+        status = new_status(x.device)
+    with timed("linear", 2.0 * n * k * n_out):
+        _lib.check(lib.ptv3_linear_fwd(_lib.ptr(x), _lib.ptr(weight.contiguous()), _lib.ptr(bias), _lib.ptr(out), n, k,
+                                       n_out, _lib.dtype_id(x), _lib.ptr(status), _lib.stream()), "ptv3_linear_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_linear_fwd")
+    return out
+
+
+def linear_ln(x, weight, bias, residual, ln1, ln2, status=None, want_sum=True):
+    """(sum, normed) with y = x W^T + b, sum = residual + LN1(y) (or + y), normed = LN2(sum)."""
+    _lib.require_cuda(x, weight, bias, residual)
+    lib = _lib.load()
+    x, residual = x.contiguous(), residual.contiguous()
+    n, c = x.shape
+    s = torch.empty_like(x) if want_sum else None
+    y = torch.empty_like(x)
+    own = status is None
+    if own:
+        status = new_status(x.device)
+    w1, b1, e1 = (ln1.weight, ln1.bias, float(ln1.eps)) if ln1 is not None else (None, None, 0.0)
+    with timed("linear_ln", 2.0 * n * c * c):
+        _lib.check(lib.ptv3_linear_ln_fwd(_lib.ptr(x), _lib.ptr(weight.contiguous()), _lib.ptr(bias),
+                                          _lib.ptr(residual), _lib.ptr(w1), _lib.ptr(b1), e1, _lib.ptr(s),
+                                          _lib.ptr(ln2.weight), _lib.ptr(ln2.bias), float(ln2.eps), _lib.ptr(y), n, c,
+                                          _lib.dtype_id(x), _lib.ptr(status), _lib.stream()), "ptv3_linear_ln_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_linear_ln_fwd")
+    return s, y

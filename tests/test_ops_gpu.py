@@ -351,3 +351,45 @@ def test_subm_conv_pair_list_path(c, permuted):
     got = ops.subm_conv_pairs(feat.cuda(), pairs, w.cuda(), b.cuda())
     assert_close(got, ref, what="pair-list conv", **TOL[torch.bfloat16])
     assert rel_l2(got, ref) < 4e-3
+
+
+@pytest.mark.parametrize("k,n_out", [(32, 96), (64, 192), (128, 384), (64, 64), (32, 32), (128, 128), (128, 256)])
+@pytest.mark.parametrize("n", [100, 5000])
+def test_linear_tcgen05(k, n_out, n):
+    g = torch.Generator().manual_seed(k + n_out + n)
+    x = torch.randn(n, k, generator=g).bfloat16()
+    w = (torch.randn(n_out, k, generator=g) / k ** 0.5).bfloat16()
+    b = (0.1 * torch.randn(n_out, generator=g)).bfloat16()
+    assert ops.linear_supported(k, n_out, False, torch.bfloat16)
+    got = ops.linear(x.cuda(), w.cuda(), b.cuda())
+    assert_close(got, F.linear(x, w, b), what="linear", **TOL[torch.bfloat16])
+    assert rel_l2(got, F.linear(x.float(), w.float(), b.float())) < 5e-3
+
+
+@pytest.mark.parametrize("C", [32, 64, 128])
+@pytest.mark.parametrize("with_ln1", [True, False])
+def test_linear_ln_tcgen05(C, with_ln1):
+    n = 3000
+    g = torch.Generator().manual_seed(C * 2 + with_ln1)
+    x = torch.randn(n, C, generator=g).bfloat16()
+    res = (torch.randn(n, C, generator=g) * 2 + 0.5).bfloat16()
+    w = (torch.randn(C, C, generator=g) / C ** 0.5).bfloat16()
+    b = (0.1 * torch.randn(C, generator=g)).bfloat16()
+    ln1, ln2 = torch.nn.LayerNorm(C), torch.nn.LayerNorm(C)
+    for ln in (ln1, ln2):
+        ln.weight.data = 1 + 0.1 * torch.randn(C, generator=g)
+        ln.bias.data = 0.1 * torch.randn(C, generator=g)
+    ln1, ln2 = ln1.bfloat16(), ln2.bfloat16()
+    y = F.linear(x, w, b)
+    ref_s = res + (ln1(y) if with_ln1 else y)
+    ref_n = ln2(ref_s)
+    import copy
+    c1, c2 = copy.deepcopy(ln1).cuda(), copy.deepcopy(ln2).cuda()
+    s, nrm = ops.linear_ln(x.cuda(), w.cuda(), b.cuda(), res.cuda(), c1 if with_ln1 else None, c2)
+    assert_close(s, ref_s, what="sum", atol=4e-2, rtol=1e-2)
+    assert_close(nrm, ref_n, what="norm", atol=4e-2, rtol=1e-2)
+    # against fp32 arithmetic: as close as the bf16 reference sequence is
+    y32 = F.linear(x.float(), w.float(), b.float())
+    s32 = res.float() + (F.layer_norm(y32, (C,), ln1.weight.float(), ln1.bias.float()) if with_ln1 else y32)
+    n32 = F.layer_norm(s32, (C,), ln2.weight.float(), ln2.bias.float())
+    assert rel_l2(nrm, n32) <= 1.5 * rel_l2(ref_n, n32) + 1e-3
