@@ -154,13 +154,14 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
     };
 
     const int64_t ntiles = (n + 127) / 128;
-    for (int64_t tile = (int64_t)blockIdx.x * Cfg::NG + g; tile < ntiles;
-         tile += (int64_t)gridDim.x * Cfg::NG) {
+    const int64_t tile_step = (int64_t)gridDim.x * Cfg::NG;
+    const int64_t tile0 = (int64_t)blockIdx.x * Cfg::NG + g;
+    if (t == 0 && tile0 < ntiles) {
+        mbar_expect_tx(xbar, Cfg::X_BYTES);
+        tma_load_2d(xs, &map_x, 0, (int)(tile0 * 128), xbar);
+    }
+    for (int64_t tile = tile0; tile < ntiles; tile += tile_step) {
         const int64_t row0 = tile * 128;
-        if (t == 0) {
-            mbar_expect_tx(xbar, Cfg::X_BYTES);
-            tma_load_2d(xs, &map_x, 0, (int)row0, xbar);
-        }
         ok &= mbar_wait(xbar, xph, abort);
         xph ^= 1;
         if (t == 0) {
@@ -173,6 +174,12 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
             ok &= mbar_wait(m1bar, m1ph, abort);
             m1ph ^= 1;
             fence_after_sync();
+            // the x tile has been consumed once the last first-GEMM is done: fetch the next one
+            // while this tile's activation, second GEMM and output are still in progress
+            if (t == 0 && ch == Cfg::NCH - 1 && tile + tile_step < ntiles) {
+                mbar_expect_tx(xbar, Cfg::X_BYTES);
+                tma_load_2d(xs, &map_x, 0, (int)((tile + tile_step) * 128), xbar);
+            }
             // D1 -> + b1 -> GELU -> bf16 -> activation tile (K-major, 128-byte swizzle)
 #pragma unroll 1
             for (int cg = 0; cg < Cfg::HC / 32; ++cg) {
@@ -208,25 +215,41 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
         ok &= mbar_wait(m2bar, m2ph, abort);
         m2ph ^= 1;
         fence_after_sync();
-        // D2 -> + b2 -> + residual -> out
-        const int64_t row = row0 + t;
+        // D2 -> + b2 -> + residual -> out.  The activation tile is free now and serves as a
+        // staging tile (same 128-byte-pitch swizzle): the residual comes in and the result goes
+        // out with coalesced 16-byte pieces, the row-per-thread arithmetic runs on shared memory.
+        constexpr int PIECES = C / 8;   // 16-byte pieces per row
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+            const int idx = i * 128 + t, r = idx / PIECES, c = idx % PIECES;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row0 + r < n) v = *reinterpret_cast<const uint4*>(residual + (row0 + r) * C + c * 8);
+            *reinterpret_cast<uint4*>(hs_ptr + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+        }
+        named_barrier(1 + g, 128);
 #pragma unroll 1
         for (int cg = 0; cg < C / 32; ++cg) {
             uint32_t v[32];
             tmem_ld32(tm_d2 + cg * 32, v);
             tmem_ld_wait();
-            if (row < n) {
 #pragma unroll
-                for (int q = 0; q < 4; ++q) {
-                    float r[8], f[8];
-                    const int64_t off = row * C + cg * 32 + q * 8;
-                    Vec<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(residual + off), r);
+            for (int q = 0; q < 4; ++q) {
+                float r[8], f[8];
+                unsigned char* slot = hs_ptr + t * 128 + (((cg * 4 + q) ^ (t & 7)) << 4);
+                Vec<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(slot), r);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        f[i] = r[i] + bf16_round(__uint_as_float(v[q * 8 + i]) + b2s[cg * 32 + q * 8 + i]);
-                    *reinterpret_cast<uint4*>(out + off) = Vec<__nv_bfloat16>::pack(f);
-                }
+                for (int i = 0; i < 8; ++i)
+                    f[i] = r[i] + bf16_round(__uint_as_float(v[q * 8 + i]) + b2s[cg * 32 + q * 8 + i]);
+                *reinterpret_cast<uint4*>(slot) = Vec<__nv_bfloat16>::pack(f);
             }
+        }
+        named_barrier(1 + g, 128);
+#pragma unroll
+        for (int i = 0; i < PIECES; ++i) {
+            const int idx = i * 128 + t, r = idx / PIECES, c = idx % PIECES;
+            if (row0 + r < n)
+                *reinterpret_cast<uint4*>(out + (row0 + r) * C + c * 8) =
+                    *reinterpret_cast<const uint4*>(hs_ptr + r * 128 + ((c ^ (r & 7)) << 4));
         }
         fence_before_sync();
         named_barrier(1 + g, 128);
