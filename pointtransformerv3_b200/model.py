@@ -543,6 +543,12 @@ class PointTransformerV3(PointModule):
                                   upcast_softmax=upcast_softmax), name=f"block{i}")
                 self.dec.add(module=dec, name=f"dec{s}")
 
+    def _side_stream(self, device):
+        streams = self.__dict__.setdefault("_ptv3_side_streams", {})
+        if device not in streams:
+            streams[device] = torch.cuda.Stream(device=device)
+        return streams[device]
+
     def forward(self, data_dict):
         """data_dict: ``feat``, ``grid_coord`` (or ``coord`` + ``grid_size``) and
         ``offset`` or ``batch``; returns the Point of the finest level.
@@ -568,18 +574,35 @@ class PointTransformerV3(PointModule):
             off = [0] + stats[3:]
             point["_counts"] = [off[i + 1] - off[i] for i in range(len(off) - 1)]
         point.serialization(order=self.order, depth=depth, shuffle_orders=self.shuffle_orders)
-        level = point
-        for s in range(1, self.num_stages):
-            down = self.enc[s][0] if isinstance(self.enc[s][0], SerializedPooling) else None
-            if down is None:
-                break
-            child = down.plan(level)
-            level["_pooled_child"] = child
-            level = child
-        # -- feature phase
+        # -- feature phase, part 1: the stem and the first encoder stage need no pooling plan;
+        #    they are queued first so that the GPU is busy while the plans are made
+        main = torch.cuda.current_stream()
+        serialized = torch.cuda.Event()
+        serialized.record(main)
+        stages = list(self.enc._modules.values())
         point.sparsify()
         point = self.embedding(point)
-        point = self.enc(point)
+        first_has_pooling = len(stages[0]) > 0 and isinstance(stages[0][0], SerializedPooling)
+        if not first_has_pooling:
+            point = stages[0](point)
+            stages = stages[1:]
+        # -- the pooling plans of all levels, on a second stream: their host reads wait only
+        #    for the small plan kernels, not for the feature work queued above
+        side = self._side_stream(main.device)
+        side.wait_event(serialized)
+        with torch.cuda.stream(side):
+            level = point
+            for stage in stages:
+                down = stage[0] if len(stage) > 0 and isinstance(stage[0], SerializedPooling) else None
+                if down is None:
+                    break
+                child = down.plan(level)
+                level["_pooled_child"] = child
+                level = child
+        main.wait_stream(side)
+        # -- feature phase, part 2
+        for stage in stages:
+            point = stage(point)
         if not self.cls_mode:
             point = self.dec(point)
         point["_defer_status"] = False
