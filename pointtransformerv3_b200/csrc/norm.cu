@@ -150,6 +150,7 @@ extern "C" int ptv3_add_layernorm_fwd(const void* x, const void* residual, const
     PTV3_REQUIRE(n >= 0 && channels >= 1, PTV3_ERR_INVALID_ARGUMENT, "ptv3_add_layernorm_fwd: bad sizes");
     PTV3_REQUIRE(dtype == PTV3_DTYPE_F32 || dtype == PTV3_DTYPE_BF16, PTV3_ERR_UNSUPPORTED,
                  "ptv3_add_layernorm_fwd: dtype %d", dtype);
+    if (n == 0) return PTV3_OK;   // empty tensors carry null pointers
     PTV3_REQUIRE((ln1_weight == nullptr) == (ln1_bias == nullptr) &&
                      (ln2_weight == nullptr) == (ln2_bias == nullptr),
                  PTV3_ERR_INVALID_ARGUMENT, "ptv3_add_layernorm_fwd: weight and bias go together");

@@ -250,3 +250,62 @@ def test_cls_mode_and_single_order():
         ref = O.ptv3_forward(sd, data, ocfg)
     assert out.feat.shape == ref.shape
     assert_close(out.feat, ref, atol=5e-4, rtol=5e-4, what="encoder-only backbone")
+
+
+@pytest.mark.parametrize("sizes", [[1, 60, 2500], [7], [300, 300]])
+def test_tiny_and_ragged_scenes_vs_oracle(sizes):
+    """Scenes of one point, scenes smaller than a patch, a single tiny scene: the
+    non-flash rule K = min(smallest scene, patch) degenerates gracefully
+    (model.py:441-444) and pooling levels shrink to a handful of voxels."""
+    data = small_batch(sizes, seed=sum(sizes))
+    cfg = dict(SMALL_CFG)
+    net = P.PointTransformerV3(in_channels=6, enable_flash=False, **cfg).eval()
+    sd = weights.fill_state_dict(net, prefix="tiny.")
+    net = net.cuda()
+    with torch.inference_mode():
+        torch.manual_seed(11)
+        out = net(cuda_data(data))
+        torch.manual_seed(11)
+        ref = O.ptv3_forward(sd, data, cfg)
+    assert out.feat.shape == ref.shape
+    assert_close(out.feat, ref, atol=5e-4, rtol=5e-4, what="tiny scenes")
+
+
+def test_empty_inputs_are_accepted_by_the_operators():
+    """n = 0 through the C ABI: every operator returns without launching."""
+    dev = torch.device("cuda")
+    e = lambda *shape, dtype=torch.float32: torch.empty(*shape, dtype=dtype, device=dev)
+    from pointtransformerv3_b200 import ops
+    assert ops.encode(e(0, 3, dtype=torch.int32), None, 16, ["z", "hilbert"]).shape == (2, 0)
+    order, inverse = ops.argsort_inverse(e(4, 0, dtype=torch.int64), 30)
+    assert order.shape == (4, 0) and inverse.shape == (4, 0)
+    assert ops.kmap_build(e(0, 4, dtype=torch.int32), 3).shape == (27, 0)
+    assert ops.subm_conv(e(0, 32), e(27, 0, dtype=torch.int32), e(32, 3, 3, 3, 32), e(32)).shape == (0, 32)
+    s, y = ops.add_layernorm(e(0, 32), e(0, 32), None, torch.nn.LayerNorm(32).cuda())
+    assert s.shape == (0, 32) and y.shape == (0, 32)
+    grid, batch = ops.decode(e(0, dtype=torch.int64), 9, "hilbert")
+    assert grid.shape == (0, 3) and batch.shape == (0,)
+
+
+def test_bad_arguments_raise_with_a_message():
+    """Host-side failure injection: wrong shapes / dtypes / sizes come back as a
+    Ptv3Error (or ValueError) carrying the library's message, never as a crash."""
+    from pointtransformerv3_b200 import _lib, ops
+    g = torch.zeros(10, 3, dtype=torch.int32, device="cuda")
+    with pytest.raises(_lib.Ptv3Error, match="depth"):
+        ops.encode(g, None, 17, ["z"])
+    with pytest.raises(ValueError):
+        ops.encode(torch.zeros(10, 2, dtype=torch.int32, device="cuda"), None, 8, ["z"])
+    with pytest.raises(_lib.Ptv3Error, match="head dim"):
+        qkv = torch.zeros(10, 3 * 24, device="cuda")
+        pad, unpad, cu = ops.pad_plan(torch.tensor([10], device="cuda"), [10], 10)
+        ops.attention(qkv, torch.arange(10, device="cuda"), pad, unpad, cu, 2, 10, 1.0)
+    with pytest.raises(_lib.Ptv3Error, match="status"):
+        # the totals the caller states do not match the offsets: the kernel reports it
+        ops.pad_plan(torch.tensor([10], device="cuda"), [12], 4)
+    with pytest.raises(_lib.Ptv3Error, match="status"):
+        ops.kmap_build(torch.tensor([[0, 70000, 0, 0]], dtype=torch.int32, device="cuda"), 3)
+    with pytest.raises(_lib.Ptv3Error):
+        ops.mlp(torch.zeros(8, 48, device="cuda").bfloat16(), torch.zeros(192, 48, device="cuda").bfloat16(),
+                torch.zeros(192, device="cuda").bfloat16(), torch.zeros(48, 192, device="cuda").bfloat16(),
+                torch.zeros(48, device="cuda").bfloat16(), torch.zeros(8, 48, device="cuda").bfloat16())
