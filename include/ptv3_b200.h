@@ -130,6 +130,19 @@ int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad
                        int algo, void* stream);
 
 /*
+ * ptv3_attention_fwd with the relative position bias of model.py:297-316, 372-380,
+ * 468-469 added to the scaled scores (CUDA-core path, either dtype):
+ *   bias(i, j, h) = sum over axes a of
+ *                   rpe_table[clamp(g_i[a] - g_j[a], -pos_bnd, pos_bnd) + pos_bnd + a * (2 pos_bnd + 1)][h]
+ *   grid_coord  n x 3 int32 (point-major, like qkv)
+ *   rpe_table   3 * (2 pos_bnd + 1) x heads fp32; pos_bnd <= 64
+ */
+int ptv3_attention_rpe_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
+                           const int64_t* unpad, const int32_t* cu_seqlens, const int32_t* grid_coord,
+                           const float* rpe_table, int pos_bnd, void* out, int64_t n, int n_seq,
+                           int max_seqlen, int channels, int heads, float scale, int dtype, void* stream);
+
+/*
  * Kernel map of a submanifold convolution.
  * Replaces spconv's indice-pair build behind model.py:546-552 and :767-774.
  *   indices     n x 4 int32 rows (batch, x, y, z), 16-byte aligned, each field

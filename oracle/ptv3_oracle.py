@@ -97,8 +97,18 @@ def effective_patch(offset, patch_size_max):
 # --------------------------------------------------------------------------- #
 # model.py:440-490  SerializedAttention.forward, non-flash branch
 # --------------------------------------------------------------------------- #
+def rpe_bias(grid_coord_patches, table, pos_bnd):
+    """model.py:297-316, 372-380: grid_coord_patches (N', K, 3) int -> (N', H, K, K)."""
+    num = 2 * pos_bnd + 1
+    rel = grid_coord_patches.unsqueeze(2) - grid_coord_patches.unsqueeze(1)
+    idx = rel.clamp(-pos_bnd, pos_bnd) + pos_bnd + torch.arange(3) * num
+    out = table.index_select(0, idx.reshape(-1).long()).view(idx.shape + (-1,)).sum(3)
+    return out.permute(0, 3, 1, 2)
+
+
 def attention(feat, w_qkv, b_qkv, w_proj, b_proj, order, inverse, offset, num_heads,
-              patch_size_max, scale=None, upcast_attention=False, upcast_softmax=False):
+              patch_size_max, scale=None, upcast_attention=False, upcast_softmax=False, rpe=None):
+    """``rpe``: None or (grid_coord (N,3), table (3*num, H), pos_bnd)."""
     N, C = feat.shape
     H = num_heads
     scale = scale or (C // H) ** -0.5
@@ -111,6 +121,9 @@ def attention(feat, w_qkv, b_qkv, w_proj, b_proj, order, inverse, offset, num_he
     if upcast_attention:
         q, k = q.float(), k.float()
     attn = (q * scale) @ k.transpose(-2, -1)                    # model.py:467
+    if rpe is not None:                                         # model.py:468-469
+        grid_coord, table, pos_bnd = rpe
+        attn = attn + rpe_bias(grid_coord[src].reshape(-1, K, 3), table, pos_bnd)
     if upcast_softmax:
         attn = attn.float()
     attn = torch.softmax(attn, dim=-1).to(qkv.dtype)            # model.py:470-473

@@ -107,6 +107,28 @@ def _is_bn_gelu(norm, act):
             and type(a) is nn.GELU and getattr(a, "approximate", "none") == "none")
 
 
+class RPE(nn.Module):
+    """Relative position bias table (model.py:297-316).  The lookup and the sum
+    over the three axes happen inside the attention kernel; ``forward`` keeps the
+    reference's tensor form for stand-alone use."""
+
+    def __init__(self, patch_size, num_heads):
+        super().__init__()
+        self.patch_size = patch_size
+        self.num_heads = num_heads
+        self.pos_bnd = int((4 * patch_size) ** (1 / 3) * 2)
+        self.rpe_num = 2 * self.pos_bnd + 1
+        self.rpe_table = nn.Parameter(torch.zeros(3 * self.rpe_num, num_heads))
+        nn.init.trunc_normal_(self.rpe_table, std=0.02)
+
+    def forward(self, coord):
+        idx = (coord.clamp(-self.pos_bnd, self.pos_bnd) + self.pos_bnd
+               + torch.arange(3, device=coord.device) * self.rpe_num)
+        out = self.rpe_table.index_select(0, idx.reshape(-1))
+        out = out.view(idx.shape + (-1,)).sum(3)
+        return out.permute(0, 3, 1, 2)
+
+
 class SerializedAttention(PointModule):
     """Multi-head self-attention inside patches of a serialized order
     (model.py:319-490).  Both settings of ``enable_flash`` run the same CUDA
@@ -127,9 +149,8 @@ class SerializedAttention(PointModule):
         self.upcast_softmax = upcast_softmax
         self.enable_rpe = enable_rpe
         self.enable_flash = enable_flash
-        if enable_rpe:
-            raise NotImplementedError("relative position bias (enable_rpe) is not implemented")
         if enable_flash:
+            assert enable_rpe is False, "Set enable_rpe to False when enable Flash Attention"
             assert upcast_attention is False, "Set upcast_attention to False when enable Flash Attention"
             assert upcast_softmax is False, "Set upcast_softmax to False when enable Flash Attention"
             self.patch_size = patch_size
@@ -140,6 +161,7 @@ class SerializedAttention(PointModule):
         self.qkv = nn.Linear(channels, channels * 3, bias=qkv_bias)
         self.proj = nn.Linear(channels, channels)
         self.proj_drop = nn.Dropout(proj_drop)
+        self.rpe = RPE(patch_size, num_heads) if self.enable_rpe else None
         self.algo = 0
 
     @torch.no_grad()
@@ -159,6 +181,10 @@ class SerializedAttention(PointModule):
         if not self.enable_flash:
             self.patch_size = min(min(point.host_counts()), self.patch_size_max)
         pad, unpad, cu_seqlens = self.get_padding_and_inverse(point)
+        if self.enable_rpe:
+            return ops.attention_rpe(qkv, point.serialized_order[self.order_index], pad, unpad, cu_seqlens,
+                                     point.grid_coord, self.rpe.rpe_table, self.rpe.pos_bnd, self.num_heads,
+                                     self.patch_size, self.scale)
         return ops.attention(qkv, point.serialized_order[self.order_index], pad, unpad, cu_seqlens,
                              self.num_heads, self.patch_size, self.scale, self.algo)
 

@@ -150,6 +150,26 @@ def attention(qkv, order_row, pad, unpad, cu_seqlens, heads, max_seqlen, scale, 
     return out
 
 
+def attention_rpe(qkv, order_row, pad, unpad, cu_seqlens, grid_coord, rpe_table, pos_bnd, heads, max_seqlen,
+                  scale):
+    """Patch attention with the relative position bias (see ptv3_attention_rpe_fwd)."""
+    _lib.require_cuda(qkv, order_row, pad, unpad, cu_seqlens, grid_coord, rpe_table)
+    lib = _lib.load()
+    qkv = qkv.contiguous()
+    n, c3 = qkv.shape
+    C = c3 // 3
+    grid_coord = grid_coord.to(torch.int32).contiguous()
+    rpe_table = rpe_table.to(torch.float32).contiguous()
+    out = torch.empty((n, C), dtype=qkv.dtype, device=qkv.device)
+    with timed("attention_rpe", 4.0 * pad.numel() * max_seqlen * C):
+        _lib.check(lib.ptv3_attention_rpe_fwd(_lib.ptr(qkv), _lib.ptr(order_row.contiguous()), _lib.ptr(pad),
+                                              _lib.ptr(unpad), _lib.ptr(cu_seqlens), _lib.ptr(grid_coord),
+                                              _lib.ptr(rpe_table), int(pos_bnd), _lib.ptr(out), n,
+                                              cu_seqlens.numel() - 1, int(max_seqlen), C, int(heads), float(scale),
+                                              _lib.dtype_id(qkv), _lib.stream()), "ptv3_attention_rpe_fwd")
+    return out
+
+
 def kmap_build(indices, ksize, status=None):
     """indices (N,4) int32 (b,x,y,z) -> nbr (ksize^3, N) int32, offset-major."""
     _lib.require_cuda(indices)

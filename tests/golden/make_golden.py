@@ -71,6 +71,16 @@ def gen_attention(model):
             att = att.bfloat16()
             pt.feat = feat.bfloat16()
             out[name + "_bf16"] = bf16_bits(att(pt).feat)
+    # relative position bias (non-flash only), model.py:297-316, 468-469
+    data = small_batch([900, 500], seed=23)
+    pt = model.Point(dict(data))
+    pt.serialization(order=["z"], shuffle_orders=False)
+    att = model.SerializedAttention(32, 2, 128, enable_rpe=True, enable_flash=False, upcast_attention=False,
+                                    upcast_softmax=False).eval()
+    weights.fill_state_dict(att, prefix="attention.rpe.")
+    with torch.inference_mode():
+        pt.feat = weights.keyed_tensor("attention.feat.rpe", (pt.batch.shape[0], 32))
+        out["rpe_fp32"] = att(pt).feat.numpy()
     np.savez_compressed(os.path.join(HERE, "attention.npz"), **out)
 
 

@@ -309,3 +309,28 @@ def test_bad_arguments_raise_with_a_message():
         ops.mlp(torch.zeros(8, 48, device="cuda").bfloat16(), torch.zeros(192, 48, device="cuda").bfloat16(),
                 torch.zeros(192, device="cuda").bfloat16(), torch.zeros(48, 192, device="cuda").bfloat16(),
                 torch.zeros(48, device="cuda").bfloat16(), torch.zeros(8, 48, device="cuda").bfloat16())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_with_relative_position_bias(dtype):
+    """enable_rpe=True (non-flash): golden vector of the reference in fp32, oracle in bf16."""
+    g = load("attention.npz")
+    data = small_batch([900, 500], seed=23)
+    pt = P.Point(cuda_data(data))
+    pt.serialization(order=["z"], shuffle_orders=False)
+    att = P.SerializedAttention(32, 2, 128, enable_rpe=True, enable_flash=False, upcast_attention=False,
+                                upcast_softmax=False).eval()
+    sd = weights.fill_state_dict(att, prefix="attention.rpe.")
+    feat = weights.keyed_tensor("attention.feat.rpe", (pt.batch.shape[0], 32))
+    att = att.cuda().to(dtype)
+    with torch.inference_mode():
+        pt.feat = feat.cuda().to(dtype)
+        got = att(pt).feat
+    if dtype == torch.float32:
+        assert_close(got, torch.from_numpy(g["rpe_fp32"]), what="rpe attention fp32", **TOL[torch.float32])
+    else:
+        c = lambda k: sd[k].to(dtype)
+        ref = O.attention(feat.to(dtype), c("qkv.weight"), c("qkv.bias"), c("proj.weight"), c("proj.bias"),
+                          pt.serialized_order[0].cpu(), pt.serialized_inverse[0].cpu(), data["offset"], 2, 128,
+                          rpe=(data["grid_coord"], c("rpe.rpe_table"), att.rpe.pos_bnd))
+        assert_close(got, ref, what="rpe attention bf16", **TOL[torch.bfloat16])
