@@ -3,8 +3,8 @@
 // pass.  Replaces torch.argsort + scatter_ at model.py:118-126 and :667-674
 // (ties are resolved by original index, the canonical order).
 //
-// Per pass (digits of up to 11 bits, as few passes as the significant bits
-// allow): tile histogram -> per-digit scan over tiles -> stable scatter.  The first pass reads the caller's codes and takes the value
+// Per pass (8-bit digits, spread evenly over the significant bits): tile histogram ->
+// per-digit scan over tiles -> stable scatter.  The first pass reads the caller's codes and takes the value
 // of an element to be its index; the last pass writes order/inverse as int64
 // and drops the keys.  HBM-bound: 8 B key + 4 B value read and written per
 // element and pass.
@@ -176,7 +176,11 @@ struct SortPlan {
 static SortPlan sort_plan(int k, int64_t n, int sig_bits)
 {
     SortPlan p;
-    p.passes = sig_bits <= 0 ? 1 : (sig_bits + RS_MAX_BITS - 1) / RS_MAX_BITS;
+    // The kernels take digits of up to RS_MAX_BITS bits; measured on B200, 10-bit digits (5 instead
+    // of 7 passes at 49 bits) are no faster at 16 M keys and slower at 0.4 M, because the per-tile
+    // histogram table grows with the digit while a tile stays 2048 keys: 8-bit digits are used.
+    constexpr int kDigitBits = 8;
+    p.passes = sig_bits <= 0 ? 1 : (sig_bits + kDigitBits - 1) / kDigitBits;
     p.bits = sig_bits <= 0 ? 8 : (sig_bits + p.passes - 1) / p.passes;   // spread evenly
     p.ntiles = ceil_div(n, RS_TILE);
     size_t b = 0;
