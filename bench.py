@@ -211,15 +211,21 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step_resident()
     sampler = ClockSampler(local) if rank == 0 else None
-    ops.TIMERS = {}
+    # timed region: only the dominant kernel (attention) carries CUDA events, so that the
+    # step time is not inflated by hundreds of event records
+    ops.TIMERS, ops.TIMER_FILTER = {}, {"attention"}
     launches0 = lib.ptv3_launch_count()
     torch.cuda.profiler.start()       # lets a profiler restrict itself to the timed steps
     ms, t0, t1 = timed(step_resident, args.steps)
     torch.cuda.profiler.stop()
     launches = lib.ptv3_launch_count() - launches0
     timers = ops.timer_summary()
-    ops.TIMERS = None
     clocks = sampler.stop(t0, t1) if sampler else None
+    # second pass (not part of `value`): every operator timed, for the per-kernel breakdown
+    ops.TIMERS, ops.TIMER_FILTER = {}, None
+    timed(step_resident, args.steps)
+    all_timers = ops.timer_summary()
+    ops.TIMERS = None
 
     ms_e2e = None
     if not args.no_e2e:
@@ -251,7 +257,7 @@ def run_ours(args):
                     "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch",
                     "peak_source": "measured (sustained)" if peaks else "fallback",
                     "launches": att["calls"], "avg_launch_ms": att["ms"] / max(att["calls"], 1)}
-        breakdown = {k: {"calls": v["calls"], "ms_per_step": v["ms"] / args.steps} for k, v in timers.items()}
+        breakdown = {k: {"calls": v["calls"], "ms_per_step": v["ms"] / args.steps} for k, v in all_timers.items()}
         line = {
             "metric": METRIC, "value": total_points * args.steps / (ms * 1e-3), "unit": UNIT,
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),

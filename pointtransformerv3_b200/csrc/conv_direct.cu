@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "convert.cuh"
 #include "kmap.cuh"
+#include "voxel_index.cuh"
 #include "vec.cuh"
 
 namespace ptv3 {
@@ -31,94 +32,6 @@ __device__ __forceinline__ float cd_gelu(float x)
 }
 
 constexpr int CD_CHUNK = 25;   // kernel offsets staged per round
-
-// ---- two-level voxel index: hash of 4x4x4 blocks -> 64-entry cell tables ----------
-// A (2r+1)^3 neighbourhood with r <= 3 touches at most 2 blocks per axis, so a voxel
-// needs 8 hash probes instead of one per kernel offset; each offset then costs a
-// few integer operations and one load from a 256-byte cell table.
-constexpr uint32_t CD_NO_ROW = 0xffffffffu;
-
-__device__ __forceinline__ bool cd_block_key(int b, int bx, int by, int bz, uint64_t& key)
-{
-    if ((unsigned)b > 0xfffeu || (unsigned)bx > 0x3fffu || (unsigned)by > 0x3fffu || (unsigned)bz > 0x3fffu)
-        return false;
-    key = ((uint64_t)b << 48) | ((uint64_t)bx << 32) | ((uint64_t)by << 16) | (uint64_t)bz;
-    return true;
-}
-
-// every voxel claims its block: the first claimant takes the next table and clears it
-__global__ void __launch_bounds__(256) cd_block_insert_kernel(const int32_t* __restrict__ indices, int64_t n,
-                                                              unsigned long long* __restrict__ keys,
-                                                              uint32_t* __restrict__ vals, uint64_t cap_mask,
-                                                              uint32_t* __restrict__ counter,
-                                                              uint32_t* __restrict__ cells,
-                                                              uint32_t* __restrict__ status)
-{
-    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const int4 v = reinterpret_cast<const int4*>(indices)[i];
-    uint64_t key;
-    if ((unsigned)v.y > 0xffffu || (unsigned)v.z > 0xffffu || (unsigned)v.w > 0xffffu ||
-        !cd_block_key(v.x, v.y >> 2, v.z >> 2, v.w >> 2, key)) {
-        atomicOr(status, PTV3_STATUS_BAD_INDEX);
-        return;
-    }
-    uint64_t slot = km_mix(key) & cap_mask;
-    for (uint64_t probe = 0; probe <= cap_mask; ++probe) {
-        const unsigned long long prev = atomicCAS(&keys[slot], KM_EMPTY, key);
-        if (prev == KM_EMPTY) {
-            const uint32_t id = atomicAdd(counter, 1u);
-            uint4* tab = reinterpret_cast<uint4*>(cells + (size_t)id * 64);
-#pragma unroll
-            for (int q = 0; q < 16; ++q) tab[q] = make_uint4(CD_NO_ROW, CD_NO_ROW, CD_NO_ROW, CD_NO_ROW);
-            __threadfence();
-            vals[slot] = id;
-            return;
-        }
-        if (prev == key) return;
-        slot = (slot + 1) & cap_mask;
-    }
-    atomicOr(status, PTV3_STATUS_PROBE_LIMIT);
-}
-
-__device__ __forceinline__ uint32_t cd_block_lookup(const unsigned long long* __restrict__ keys,
-                                                    const uint32_t* __restrict__ vals, uint64_t cap_mask,
-                                                    uint64_t key, bool* overflow)
-{
-    uint64_t slot = km_mix(key) & cap_mask;
-    for (uint64_t probe = 0; probe <= cap_mask; ++probe) {
-        const unsigned long long kk = keys[slot];
-        if (kk == key) return vals[slot];
-        if (kk == KM_EMPTY) return CD_NO_ROW;
-        slot = (slot + 1) & cap_mask;
-    }
-    *overflow = true;
-    return CD_NO_ROW;
-}
-
-// second pass (all tables exist now): every voxel writes its row into its cell;
-// duplicates resolve to the lowest row
-__global__ void __launch_bounds__(256) cd_cell_fill_kernel(const int32_t* __restrict__ indices, int64_t n,
-                                                           const unsigned long long* __restrict__ keys,
-                                                           const uint32_t* __restrict__ vals, uint64_t cap_mask,
-                                                           uint32_t* __restrict__ cells,
-                                                           uint32_t* __restrict__ status)
-{
-    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const int4 v = reinterpret_cast<const int4*>(indices)[i];
-    uint64_t key;
-    if ((unsigned)v.y > 0xffffu || (unsigned)v.z > 0xffffu || (unsigned)v.w > 0xffffu ||
-        !cd_block_key(v.x, v.y >> 2, v.z >> 2, v.w >> 2, key))
-        return;
-    bool overflow = false;
-    const uint32_t id = cd_block_lookup(keys, vals, cap_mask, key, &overflow);
-    if (id == CD_NO_ROW) {
-        atomicOr(status, overflow ? PTV3_STATUS_PROBE_LIMIT : PTV3_STATUS_BAD_INDEX);
-        return;
-    }
-    atomicMin(&cells[(size_t)id * 64 + ((v.y & 3) << 4 | (v.z & 3) << 2 | (v.w & 3))], (uint32_t)i);
-}
 
 // [cout][kvol][cin] -> [kvol][cin][cout], once per call (a few thousand elements)
 template <typename T>
@@ -174,13 +87,13 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_kernel(
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
         const int bi = half * 4 + q;   // bit 2: x, bit 1: y, bit 0: z  (0 = block of coord - r)
-        uint32_t id = CD_NO_ROW;
+        uint32_t id = VI_NO_ROW;
         if (c.x >= 0) {
             const int bx = ((c.y - r) >> 2) + ((bi >> 2) & 1);
             const int by = ((c.z - r) >> 2) + ((bi >> 1) & 1);
             const int bz = ((c.w - r) >> 2) + (bi & 1);
             uint64_t key;
-            if (cd_block_key(c.x, bx, by, bz, key)) id = cd_block_lookup(keys, vals, cap_mask, key, &overflow);
+            if (vi_block_key(c.x, bx, by, bz, key)) id = vi_block_lookup(keys, vals, cap_mask, key, &overflow);
         }
         block_s[bi][v] = id;
     }
@@ -197,17 +110,17 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_kernel(
             const int ol = idx / CD_TM, vv = idx % CD_TM;
             const int4 cc = coord_s[vv];
             const char4 d = delta_s[o0 + ol];
-            uint32_t j = CD_NO_ROW;
+            uint32_t j = VI_NO_ROW;
             if (cc.x >= 0) {
                 const int x = cc.y + d.x, y = cc.z + d.y, z = cc.w + d.z;
                 const int bi = (((x >> 2) - ((cc.y - r) >> 2)) << 2) | (((y >> 2) - ((cc.z - r) >> 2)) << 1) |
                                ((z >> 2) - ((cc.w - r) >> 2));
                 const uint32_t id = block_s[bi][vv];
-                if (id != CD_NO_ROW) j = cells[(size_t)id * 64 + ((x & 3) << 4 | (y & 3) << 2 | (z & 3))];
+                if (id != VI_NO_ROW) j = cells[(size_t)id * 64 + ((x & 3) << 4 | (y & 3) << 2 | (z & 3))];
             }
             T* dst = x_s + ((size_t)ol * CD_TM + vv) * CD_MAX_CIN;
-            has_s[ol * CD_TM + vv] = j != CD_NO_ROW;
-            if (j != CD_NO_ROW) {
+            has_s[ol * CD_TM + vv] = j != VI_NO_ROW;
+            if (j != VI_NO_ROW) {
                 const T* src = feat + (int64_t)j * cin;
 #pragma unroll
                 for (int ci = 0; ci < CD_MAX_CIN; ++ci) dst[ci] = ci < cin ? src[ci] : from_f<T>(0.f);
@@ -305,7 +218,7 @@ static int launch_conv_direct(const void* feat, const int32_t* indices, const vo
 
 static size_t conv_direct_weight_bytes(int ksize) { return align_up((size_t)ksize * ksize * ksize * 8 * 64 * 4, 256); }
 // hash table of blocks (sized for one block per voxel), block counter, one 64-entry table per block
-static size_t conv_direct_index_bytes(int64_t n) { return km_table_bytes(n) + 256 + align_up((size_t)n * 256, 256); }
+static size_t conv_direct_index_bytes(int64_t n) { return voxel_index_bytes(n); }
 
 }  // namespace ptv3
 
@@ -342,19 +255,15 @@ extern "C" int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indice
                  "ptv3_subm_conv_direct_fwd: weight size must be a multiple of 8 elements");
     void* wt = static_cast<char*>(workspace) + conv_direct_index_bytes(n);
     cudaStream_t stream = (cudaStream_t)stream_;
-    const uint64_t cap = km_capacity(n);
-    const uint64_t cap_mask = cap - 1;
-    Carver cv(workspace);
-    unsigned long long* keys = cv.take<unsigned long long>(cap);
-    uint32_t* vals = cv.take<uint32_t>(cap);
-    uint32_t* counter = cv.take<uint32_t>(64);
-    uint32_t* cells = cv.take<uint32_t>((size_t)n * 64);
-    cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
-    cudaMemsetAsync(counter, 0, sizeof(uint32_t), stream);
-    const unsigned vb = (unsigned)((n + 255) / 256);
-    cd_block_insert_kernel<<<vb, 256, 0, stream>>>(indices, n, keys, vals, cap_mask, counter, cells, status);
-    cd_cell_fill_kernel<<<vb, 256, 0, stream>>>(indices, n, keys, vals, cap_mask, cells, status);
-    count_launches(2);
+    VoxelIndex vi;
+    {
+        const int rc = build_voxel_index(indices, n, workspace, status, stream, &vi);
+        if (rc != PTV3_OK) return rc;
+    }
+    const unsigned long long* keys = vi.keys;
+    const uint32_t* vals = vi.vals;
+    const uint64_t cap_mask = vi.cap_mask;
+    const uint32_t* cells = vi.cells;
     if (dtype == PTV3_DTYPE_F32)
         return launch_conv_direct<float>(feat, indices, weight, bias, bn_scale, bn_shift, apply_gelu, out,
                                          row_order, n, c_in, c_out, ksize, keys, vals, cap_mask, cells, status,

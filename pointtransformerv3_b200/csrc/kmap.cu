@@ -9,6 +9,7 @@
 // Offset index o = ((dx+r)*k + (dy+r))*k + (dz+r), r = k/2.
 #include "common.cuh"
 #include "kmap.cuh"
+#include "voxel_index.cuh"
 
 namespace ptv3 {
 
@@ -77,6 +78,43 @@ __global__ void __launch_bounds__(256) km_probe_kernel(const int32_t* __restrict
     nbr[(int64_t)o * n + i] = found;
 }
 
+// Neighbour table from the two-level voxel index: one thread per voxel looks up the 8 blocks
+// its neighbourhood touches, then every offset is one cell-table load (kernel sizes up to 5).
+__global__ void __launch_bounds__(256) km_block_probe_kernel(const int32_t* __restrict__ indices, int64_t n,
+                                                             int ksize, VoxelIndex vi,
+                                                             int32_t* __restrict__ nbr,
+                                                             uint32_t* __restrict__ status)
+{
+    __shared__ uint32_t block_s[8][256];
+    const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int r = ksize / 2;
+    const int4 c = reinterpret_cast<const int4*>(indices)[i];
+    bool overflow = false;
+#pragma unroll
+    for (int bi = 0; bi < 8; ++bi) {
+        uint64_t key;
+        uint32_t id = VI_NO_ROW;
+        if (vi_block_key(c.x, ((c.y - r) >> 2) + ((bi >> 2) & 1), ((c.z - r) >> 2) + ((bi >> 1) & 1),
+                         ((c.w - r) >> 2) + (bi & 1), key))
+            id = vi_block_lookup(vi.keys, vi.vals, vi.cap_mask, key, &overflow);
+        block_s[bi][threadIdx.x] = id;
+    }
+    if (overflow) atomicOr(status, PTV3_STATUS_PROBE_LIMIT);
+    const int bx0 = (c.y - r) >> 2, by0 = (c.z - r) >> 2, bz0 = (c.w - r) >> 2;
+    int o = 0;
+    for (int dx = -r; dx <= r; ++dx)
+        for (int dy = -r; dy <= r; ++dy)
+            for (int dz = -r; dz <= r; ++dz, ++o) {
+                const int x = c.y + dx, y = c.z + dy, z = c.w + dz;
+                const int bi = (((x >> 2) - bx0) << 2) | (((y >> 2) - by0) << 1) | ((z >> 2) - bz0);
+                const uint32_t id = block_s[bi][threadIdx.x];
+                uint32_t j = VI_NO_ROW;
+                if (id != VI_NO_ROW) j = vi.cells[(size_t)id * 64 + vi_cell(x, y, z)];
+                nbr[(int64_t)o * n + i] = (int32_t)j;   // VI_NO_ROW is -1 as an int32
+            }
+}
+
 uint64_t km_capacity(int64_t n)
 {
     uint64_t c = 1024;
@@ -114,8 +152,7 @@ int km_build_table(const int32_t* indices, int64_t n, void* workspace, uint32_t*
 extern "C" size_t ptv3_kmap_workspace_bytes(int64_t n)
 {
     if (n <= 0) return 0;
-    const uint64_t cap = ptv3::km_capacity(n);
-    return ptv3::align_up(cap * sizeof(uint64_t), 256) + ptv3::align_up(cap * sizeof(uint32_t), 256);
+    return ptv3::voxel_index_bytes(n);   // covers the plain hash table of the 7x7x7 path too
 }
 
 extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int32_t* nbr,
@@ -135,13 +172,21 @@ extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int
     PTV3_REQUIRE(workspace_bytes >= need, PTV3_ERR_WORKSPACE,
                  "ptv3_kmap_build: workspace %zu < %zu bytes", workspace_bytes, need);
     cudaStream_t stream = (cudaStream_t)stream_;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    if (ksize <= 5) {
+        VoxelIndex vi;
+        const int rc = build_voxel_index(indices, n, workspace, status, stream, &vi);
+        if (rc != PTV3_OK) return rc;
+        km_block_probe_kernel<<<blocks, 256, 0, stream>>>(indices, n, ksize, vi, nbr, status);
+        count_launches(1);
+        return check_launch("ptv3_kmap_build");
+    }
     const uint64_t cap = km_capacity(n);
     Carver cv(workspace);
     unsigned long long* keys = cv.take<unsigned long long>(cap);
     uint32_t* vals = cv.take<uint32_t>(cap);
     cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
     cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream);
-    const unsigned blocks = (unsigned)((n + 255) / 256);
     km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
     km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(
         indices, n, ksize, keys, vals, cap - 1, nbr, status);

@@ -14,6 +14,7 @@ ORDER_IDS = {"z": 0, "z-trans": 1, "hilbert": 2, "hilbert-trans": 3}
 # records a CUDA event pair on the current stream under the operator's name,
 # together with the `work` figure (algorithmic FLOPs or bytes) of the call.
 TIMERS = None
+TIMER_FILTER = None     # optional set of operator names to time (None = all)
 
 
 class timed:
@@ -21,14 +22,15 @@ class timed:
         self.name, self.work = name, work
 
     def __enter__(self):
-        if TIMERS is not None:
+        self.on = TIMERS is not None and (TIMER_FILTER is None or self.name in TIMER_FILTER)
+        if self.on:
             self.start = torch.cuda.Event(enable_timing=True)
             self.end = torch.cuda.Event(enable_timing=True)
             self.start.record()
         return self
 
     def __exit__(self, *exc):
-        if TIMERS is not None:
+        if self.on:
             self.end.record()
             TIMERS.setdefault(self.name, []).append((self.start, self.end, self.work))
         return False
