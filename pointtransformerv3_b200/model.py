@@ -625,6 +625,12 @@ class PointTransformerV3(PointModule):
                 child = down.plan(level)
                 level["_pooled_child"] = child
                 level = child
+                # the coarse level's 3x3x3 kernel map (and pair list where the pair-list
+                # convolution will be taken) only needs its coordinates: make it here too
+                child["_prebuilt_kmaps"] = spconv.prebuild_kernel_map(
+                    torch.cat([child.batch.unsqueeze(-1).int(), child.grid_coord.int()], dim=1).contiguous(),
+                    child.serialized_order[0], 3, status,
+                    with_pairs=child.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
         main.wait_stream(side)
         # -- feature phase, part 2
         for stage in stages:

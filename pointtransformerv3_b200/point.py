@@ -151,4 +151,5 @@ class Point(AttrDict):
             row_order=self.serialized_order[0] if "serialized_order" in self.keys() else None,
             status=self.device_status(),
             defer_status=self.get("_defer_status", False),
+            prebuilt=self.pop("_prebuilt_kmaps", None),
         )

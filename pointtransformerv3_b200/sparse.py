@@ -21,7 +21,7 @@ class SparseConvTensor:
     by every tensor derived with ``replace_feature``."""
 
     def __init__(self, features, indices, spatial_shape, batch_size, indice_dict=None, row_order=None,
-                 status=None, defer_status=False):
+                 status=None, defer_status=False, prebuilt=None):
         self.features = features
         self.indices = indices
         self.spatial_shape = spatial_shape
@@ -34,10 +34,13 @@ class SparseConvTensor:
         # owner reads it once at the end of its forward pass
         self.status = status
         self.defer_status = defer_status
+        # kernel maps / pair lists made ahead of time for this voxel set, by kernel size
+        # (whatever indice_key a convolution names): {ksize: (nbr, row_order)}, {(ksize, "pairs"): ...}
+        self.prebuilt = {} if prebuilt is None else prebuilt
 
     def replace_feature(self, feature):
         return SparseConvTensor(feature, self.indices, self.spatial_shape, self.batch_size, self.indice_dict,
-                                self.row_order, self.status, self.defer_status)
+                                self.row_order, self.status, self.defer_status, self.prebuilt)
 
     def kernel_map(self, kernel_size, indice_key=None):
         """(nbr, row_order): the offset-major neighbour table with its columns in
@@ -45,6 +48,11 @@ class SparseConvTensor:
         key = (indice_key, kernel_size)
         if indice_key is not None and key in self.indice_dict:
             return self.indice_dict[key]
+        if kernel_size in self.prebuilt:
+            entry = self.prebuilt[kernel_size]
+            if indice_key is not None:
+                self.indice_dict[key] = entry
+            return entry
         nbr = ops.kmap_build(self.indices, kernel_size, self.status)
         if self.status is not None and not self.defer_status:
             from . import _lib
@@ -61,6 +69,11 @@ class SparseConvTensor:
         key = (indice_key, kernel_size, "pairs")
         if indice_key is not None and key in self.indice_dict:
             return self.indice_dict[key]
+        if (kernel_size, "pairs") in self.prebuilt:
+            pairs = self.prebuilt[(kernel_size, "pairs")]
+            if indice_key is not None:
+                self.indice_dict[key] = pairs
+            return pairs
         nbr, row_order = self.kernel_map(kernel_size, indice_key)
         pairs = ops.conv_pairs_build(nbr, row_order)
         if indice_key is not None:
@@ -133,3 +146,15 @@ class _Modules:
 
 
 modules = _Modules()
+
+
+def prebuild_kernel_map(indices, row_order, kernel_size, status, with_pairs):
+    """Kernel map (and optionally its pair list) of a voxel set, in the form
+    SparseConvTensor(prebuilt=...) takes."""
+    nbr = ops.kmap_build(indices, kernel_size, status)
+    if row_order is not None:
+        nbr = nbr.index_select(1, row_order)
+    out = {kernel_size: (nbr, row_order)}
+    if with_pairs:
+        out[(kernel_size, "pairs")] = ops.conv_pairs_build(nbr, row_order)
+    return out
