@@ -262,7 +262,8 @@ int ptv3_pool_plan(const int64_t* code, const int64_t* order, const int32_t* gri
                    uint32_t* status, void* workspace, size_t workspace_bytes, void* stream);
 
 /*
- * Segment max over clusters fused with BatchNorm(eval) + GELU, and the mean
+ * Segment reduction over clusters (reduce: 0 max, 1 min, 2 sum, 3 mean, as
+ * torch_scatter.segment_csr's `reduce`) fused with BatchNorm(eval) + GELU, and the mean
  * coordinate.  Replaces torch_scatter.segment_csr at model.py:684-689 and the
  * norm/act at model.py:707-710.
  *   x           (points) x channels, already projected (model.py:685)
@@ -273,7 +274,7 @@ int ptv3_pool_plan(const int64_t* code, const int64_t* order, const int32_t* gri
  */
 int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* indices, const int64_t* idx_ptr,
                   int64_t m, int channels, const float* bn_scale, const float* bn_shift, void* out,
-                  float* coord_out, int dtype, void* stream);
+                  float* coord_out, int reduce, int dtype, void* stream);
 
 /*
  * out[i] = GELU(BN(skip[i])) + GELU(BN(child[cluster[i]])); skip_act (optional)

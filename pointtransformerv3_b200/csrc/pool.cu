@@ -24,7 +24,8 @@ __device__ __forceinline__ float gelu_exact(float x)
 
 // LANES lanes own a cluster (LANES * Vec<T>::N channels per pass); the first three
 // lanes of a group also average the coordinates.  C must be a multiple of Vec<T>::N.
-template <typename T, int LANES>
+// REDUCE: 0 max, 1 min, 2 sum, 3 mean (torch_scatter.segment_csr's reduce argument)
+template <typename T, int LANES, int REDUCE>
 __global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x, const float* __restrict__ coord,
                                                        const int64_t* __restrict__ indices,
                                                        const int64_t* __restrict__ idx_ptr, int64_t m, int C,
@@ -40,18 +41,21 @@ __global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x, 
     for (int ch = sub * V::N; ch < C; ch += LANES * V::N) {
         float best[V::N];
 #pragma unroll
-        for (int i = 0; i < V::N; ++i) best[i] = -INFINITY;
+        for (int i = 0; i < V::N; ++i) best[i] = REDUCE == 0 ? -INFINITY : (REDUCE == 1 ? INFINITY : 0.f);
         for (int64_t j = lo; j < hi; ++j) {
             const int64_t p = indices[j];
             const typename V::Raw raw = *reinterpret_cast<const typename V::Raw*>(x + p * C + ch);
             float f[V::N];
             V::unpack(raw, f);
 #pragma unroll
-            for (int i = 0; i < V::N; ++i) best[i] = fmaxf(best[i], f[i]);
+            for (int i = 0; i < V::N; ++i)
+                best[i] = REDUCE == 0 ? fmaxf(best[i], f[i]) : (REDUCE == 1 ? fminf(best[i], f[i]) : best[i] + f[i]);
         }
 #pragma unroll
         for (int i = 0; i < V::N; ++i) {
             float v = best[i];
+            if (REDUCE == 3) v = v / (float)(hi - lo);
+            if (REDUCE >= 2) v = to_f<T>(from_f<T>(v));   // the reduction's output is rounded before the norm
             if (scale) v = gelu_exact(fmaf(v, scale[ch + i], shift[ch + i]));
             best[i] = v;
         }
@@ -111,10 +115,12 @@ __global__ void __launch_bounds__(256) unpool_kernel(const T* __restrict__ skip,
 
 extern "C" int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* indices,
                              const int64_t* idx_ptr, int64_t m, int channels, const float* bn_scale,
-                             const float* bn_shift, void* out, float* coord_out, int dtype,
+                             const float* bn_shift, void* out, float* coord_out, int reduce, int dtype,
                              void* stream_)
 {
     using namespace ptv3;
+    PTV3_REQUIRE(reduce >= 0 && reduce <= 3, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_pool_fwd: reduce %d (0 max, 1 min, 2 sum, 3 mean)", reduce);
     PTV3_REQUIRE(m >= 0 && channels >= 1, PTV3_ERR_INVALID_ARGUMENT, "ptv3_pool_fwd: bad sizes");
     PTV3_REQUIRE(dtype == PTV3_DTYPE_F32 || dtype == PTV3_DTYPE_BF16, PTV3_ERR_UNSUPPORTED,
                  "ptv3_pool_fwd: dtype %d", dtype);
@@ -132,9 +138,19 @@ extern "C" int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* i
     while (lanes < 32 && lanes < vectors) lanes *= 2;
     const unsigned blocks = (unsigned)((m * lanes + 255) / 256);
 #define PTV3_POOL_LAUNCH(T, L)                                                                          \
-    pool_max_kernel<T, L><<<blocks, 256, 0, stream>>>((const T*)x, with_coord ? coord : nullptr, indices, \
-                                                      idx_ptr, m, channels, bn_scale, bn_shift, (T*)out, \
-                                                      with_coord ? coord_out : nullptr)
+    do {                                                                                                 \
+        auto args = [&](auto kern) {                                                                     \
+            kern<<<blocks, 256, 0, stream>>>((const T*)x, with_coord ? coord : nullptr, indices, idx_ptr, m, \
+                                             channels, bn_scale, bn_shift, (T*)out,                      \
+                                             with_coord ? coord_out : nullptr);                          \
+        };                                                                                               \
+        switch (reduce) {                                                                                \
+            case 0: args(pool_max_kernel<T, L, 0>); break;                                               \
+            case 1: args(pool_max_kernel<T, L, 1>); break;                                               \
+            case 2: args(pool_max_kernel<T, L, 2>); break;                                               \
+            default: args(pool_max_kernel<T, L, 3>); break;                                              \
+        }                                                                                                \
+    } while (0)
 #define PTV3_POOL_DISPATCH(T)                      \
     switch (lanes) {                               \
         case 4: PTV3_POOL_LAUNCH(T, 4); break;     \

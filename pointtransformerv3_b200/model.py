@@ -330,8 +330,6 @@ class SerializedPooling(PointModule):
         assert stride == 2 ** (math.ceil(stride) - 1).bit_length()
         self.stride = stride
         assert reduce in ["sum", "mean", "min", "max"]
-        if reduce != "max":
-            raise NotImplementedError("only reduce='max' is implemented")
         self.reduce = reduce
         self.shuffle_orders = shuffle_orders
         self.traceable = traceable
@@ -385,7 +383,7 @@ class SerializedPooling(PointModule):
         if fused:
             scale, shift = _bn_eval_affine(self.norm[0])
         feat, coord = ops.pool(self.proj(point.feat), point.coord if "coord" in point.keys() else None,
-                               point.serialized_order[0], child.pop("_idx_ptr"), scale, shift)
+                               point.serialized_order[0], child.pop("_idx_ptr"), scale, shift, self.reduce)
         cluster = child.pop("_cluster")
         child["feat"] = feat
         if coord is not None:

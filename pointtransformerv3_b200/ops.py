@@ -260,8 +260,11 @@ def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=
                 counts=host[1:-1], m=m, offset=torch.cumsum(meta[1:], 0))
 
 
-def pool(x, coord, indices, idx_ptr, bn_scale=None, bn_shift=None):
-    """Segment max (+ BN + GELU) of x and mean of coord over clusters."""
+REDUCE_IDS = {"max": 0, "min": 1, "sum": 2, "mean": 3}
+
+
+def pool(x, coord, indices, idx_ptr, bn_scale=None, bn_shift=None, reduce="max"):
+    """Segment reduction (+ BN + GELU) of x and mean of coord over clusters."""
     _lib.require_cuda(x, indices, idx_ptr)
     lib = _lib.load()
     x = x.contiguous()
@@ -274,7 +277,7 @@ def pool(x, coord, indices, idx_ptr, bn_scale=None, bn_shift=None):
         cout = torch.empty((m, 3), dtype=torch.float32, device=x.device)
     _lib.check(lib.ptv3_pool_fwd(_lib.ptr(x), _lib.ptr(coord), _lib.ptr(indices), _lib.ptr(idx_ptr), m, C,
                                  _lib.ptr(bn_scale), _lib.ptr(bn_shift), _lib.ptr(out), _lib.ptr(cout),
-                                 _lib.dtype_id(x), _lib.stream()), "ptv3_pool_fwd")
+                                 REDUCE_IDS[reduce], _lib.dtype_id(x), _lib.stream()), "ptv3_pool_fwd")
     return out, cout
 
 

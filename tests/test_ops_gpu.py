@@ -393,3 +393,17 @@ def test_linear_ln_tcgen05(C, with_ln1):
     s32 = res.float() + (F.layer_norm(y32, (C,), ln1.weight.float(), ln1.bias.float()) if with_ln1 else y32)
     n32 = F.layer_norm(s32, (C,), ln2.weight.float(), ln2.bias.float())
     assert rel_l2(nrm, n32) <= 1.5 * rel_l2(ref_n, n32) + 1e-3
+
+
+@pytest.mark.parametrize("reduce", ["max", "min", "sum", "mean"])
+def test_pool_reduce_modes(reduce):
+    """All four reductions of SerializedPooling (model.py:626, 684-686)."""
+    data = small_batch([3000, 800], 15)
+    batch = O.offset_to_batch(data["offset"])
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ORDERS)
+    plan = O.pooling_plan(code, depth, 2)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(batch.shape[0], 32, generator=g)
+    ref = O.segment_reduce(x[plan["indices"]], plan["idx_ptr"], reduce)
+    got, _ = ops.pool(x.cuda(), None, order[0].cuda(), plan["idx_ptr"].cuda(), None, None, reduce)
+    assert_close(got, ref, atol=1e-5, rtol=1e-5, what="pool " + reduce)
