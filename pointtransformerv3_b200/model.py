@@ -81,6 +81,43 @@ class PointSequential(PointModule):
         return input
 
 
+class PDNorm(PointModule):
+    """Per-dataset normalisation with optional context modulation (model.py:255-294):
+    one norm layer per entry of ``conditions``, selected by ``point.condition``; with
+    ``adaptive`` the result is scaled and shifted by a projection of ``point.context``.
+    With ``decouple=False`` a single norm layer is shared (the reference stores the
+    layer class itself there, which cannot be applied to a tensor)."""
+
+    def __init__(self, num_features, norm_layer, context_channels=256,
+                 conditions=("ScanNet", "S3DIS", "Structured3D"), decouple=True, adaptive=False):
+        super().__init__()
+        self.conditions = conditions
+        self.decouple = decouple
+        self.adaptive = adaptive
+        if decouple:
+            self.norm = nn.ModuleList([norm_layer(num_features) for _ in conditions])
+        else:
+            self.norm = norm_layer(num_features)
+        if adaptive:
+            self.modulation = nn.Sequential(nn.SiLU(), nn.Linear(context_channels, 2 * num_features, bias=True))
+
+    def forward(self, point):
+        assert {"feat", "condition"}.issubset(point.keys())
+        condition = point.condition if isinstance(point.condition, str) else point.condition[0]
+        if self.decouple:
+            assert condition in self.conditions
+            norm = self.norm[self.conditions.index(condition)]
+        else:
+            norm = self.norm
+        feat = norm(point.feat)
+        if self.adaptive:
+            assert "context" in point.keys()
+            shift, scale = self.modulation(point.context).chunk(2, dim=1)
+            feat = feat * (1.0 + scale) + shift
+        point.feat = feat
+        return point
+
+
 def _bn_eval_affine(bn):
     """Per-channel (scale, shift) of a BatchNorm1d in eval mode, fp32.  Cached on
     the module and recomputed when a parameter or buffer was modified or moved."""
@@ -516,10 +553,19 @@ class PointTransformerV3(PointModule):
         assert self.cls_mode or self.num_stages == len(dec_channels) + 1
         assert self.cls_mode or self.num_stages == len(dec_num_head) + 1
         assert self.cls_mode or self.num_stages == len(dec_patch_size) + 1
-        if pdnorm_bn or pdnorm_ln:
-            raise NotImplementedError("per-dataset normalisation (pdnorm_*) is not implemented")
-        bn_layer = partial(nn.BatchNorm1d, eps=1e-3, momentum=0.01)
-        ln_layer = nn.LayerNorm
+        # per-dataset normalisation runs on torch's norm layers (the fused kernels take
+        # over only for plain LayerNorm / BatchNorm1d, i.e. when these flags are off)
+        if pdnorm_bn:
+            bn_layer = partial(PDNorm, norm_layer=partial(nn.BatchNorm1d, eps=1e-3, momentum=0.01,
+                                                          affine=pdnorm_affine),
+                               conditions=pdnorm_conditions, decouple=pdnorm_decouple, adaptive=pdnorm_adaptive)
+        else:
+            bn_layer = partial(nn.BatchNorm1d, eps=1e-3, momentum=0.01)
+        if pdnorm_ln:
+            ln_layer = partial(PDNorm, norm_layer=partial(nn.LayerNorm, elementwise_affine=pdnorm_affine),
+                               conditions=pdnorm_conditions, decouple=pdnorm_decouple, adaptive=pdnorm_adaptive)
+        else:
+            ln_layer = nn.LayerNorm
         act_layer = nn.GELU
 
         self.embedding = Embedding(in_channels=in_channels, embed_channels=enc_channels[0],

@@ -135,6 +135,15 @@ def gen_backbone(model):
         d["feat"] = d["feat"].bfloat16()
         torch.manual_seed(1)
         out["bf16"] = bf16_bits(net(d).feat)
+    # per-dataset normalisation with context modulation (model.py:255-294), small cloud
+    data = small_batch([1500, 1000], seed=43)
+    net = model.PointTransformerV3(in_channels=6, enable_flash=False, pdnorm_bn=True, pdnorm_ln=True,
+                                   pdnorm_adaptive=True, **SMALL_CFG).eval()
+    weights.fill_state_dict(net, prefix="ptv3pd.")
+    with torch.inference_mode():
+        torch.manual_seed(2)
+        d = dict(data, condition="S3DIS", context=weights.keyed_tensor("ptv3pd.context", (1, 256)))
+        out["pdnorm_fp32"] = net(d).feat.numpy()
     np.savez_compressed(os.path.join(HERE, "backbone.npz"), **out)
 
 

@@ -334,3 +334,21 @@ def test_attention_with_relative_position_bias(dtype):
                           pt.serialized_order[0].cpu(), pt.serialized_inverse[0].cpu(), data["offset"], 2, 128,
                           rpe=(data["grid_coord"], c("rpe.rpe_table"), att.rpe.pos_bnd))
         assert_close(got, ref, what="rpe attention bf16", **TOL[torch.bfloat16])
+
+
+def test_backbone_with_per_dataset_norm_golden():
+    """pdnorm_bn / pdnorm_ln / pdnorm_adaptive (model.py:255-294, 834-857): the generic module
+    path with the CUDA point operators, against the reference's output."""
+    g = load("backbone.npz")
+    data = small_batch([1500, 1000], seed=43)
+    net = P.PointTransformerV3(in_channels=6, enable_flash=False, pdnorm_bn=True, pdnorm_ln=True,
+                               pdnorm_adaptive=True, **SMALL_CFG).eval()
+    weights.fill_state_dict(net, prefix="ptv3pd.")
+    net = net.cuda()
+    d = cuda_data(data)
+    d["condition"] = "S3DIS"
+    d["context"] = weights.keyed_tensor("ptv3pd.context", (1, 256)).cuda()
+    with torch.inference_mode():
+        torch.manual_seed(2)
+        out = net(d).feat
+    assert_close(out, torch.from_numpy(g["pdnorm_fp32"]), atol=5e-4, rtol=5e-4, what="PDNorm backbone")
