@@ -307,7 +307,7 @@ def _time_device(fn, steps, warmup, flush):
 
 def run_operator_case(args):
     """--case serialization | attention | conv: one operator of the path on the
-    configuration BASELINE.json gives for it, timed on the device."""
+    configuration of the benchmark plan for that operator, timed on the device."""
     from pointtransformerv3_b200 import ops, synthetic
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -330,7 +330,9 @@ def run_operator_case(args):
         codes = ops.encode(gc, batch, 16, orders)
         t_enc = _time_device(lambda: ops.encode(gc, batch, 16, orders), args.steps, args.warmup, flush)
         t_sort = _time_device(lambda: ops.argsort_inverse(codes, 49), args.steps, args.warmup, flush)
-        enc_b, sort_b = 52.0 * n, 128.0 * n          # algorithmic bytes
+        # algorithmic bytes: encode 20 B read + 32 B written per point; argsort + inverse 32 B of
+        # codes read and 2 x 32 B of order / inverse written, plus the order read once more
+        enc_b, sort_b = 52.0 * n, 128.0 * n
         out.update(config={"workload": "encode x4 orders + stable argsort + inverse, depth 16", "points": n},
                    metric="serialization_points_per_sec", unit="points/s", value=n / ((t_enc + t_sort) * 1e-3),
                    encode_ms=t_enc, argsort_inverse_ms=t_sort,

@@ -9,7 +9,10 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def reference_root():
-    return os.environ.get("PTV3_REFERENCE_ROOT", "/root/reference")
+    """Directory of the reference checkout: $PTV3_REFERENCE_ROOT, else a `reference`
+    directory next to this repository."""
+    default = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    return os.environ.get("PTV3_REFERENCE_ROOT", default)
 
 
 def load_serialization():
