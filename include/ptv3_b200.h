@@ -119,15 +119,21 @@ int ptv3_pad_plan(const int64_t* offset, int n_scenes, int patch, int64_t n, int
  *   out         n x channels, every row written exactly once
  *   max_seqlen  longest patch (rows); head_dim = channels / heads in {8,16,32,64}
  *   dtype       PTV3_DTYPE_*; algo 0 = automatic, 1 = CUDA-core path,
- *               2 = tensor-core path (bf16 only), 3 = tensor-core path with the
- *               exponent arguments rounded to bf16 and two exps per instruction
- *               (measured no faster on B200: the exp unit's rate per element
- *               is the same; kept for comparison)
+ *               2 = mma.sync tensor-core path (bf16, head_dim 16, max_seqlen
+ *               <= 2048; what "automatic" takes when it applies), 3 = the same
+ *               with the exponent arguments rounded to bf16 and two exps per
+ *               instruction (measured no faster on B200: the exp unit's rate
+ *               per element is the same; kept for comparison), 4 = tcgen05 /
+ *               tensor-memory path (bf16, head_dim 16, max_seqlen <= 1024,
+ *               needs `status`; measured 12 % slower than 2 on B200)
+ *   status      one uint32 or NULL; path 4 ORs PTV3_STATUS_WAIT_LIMIT into it
+ *               when one of its bounded waits ran out (the output is then
+ *               undefined); the other paths do not touch it
  */
 int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
                        const int64_t* unpad, const int32_t* cu_seqlens, void* out, int64_t n,
                        int n_seq, int max_seqlen, int channels, int heads, float scale, int dtype,
-                       int algo, void* stream);
+                       int algo, uint32_t* status, void* stream);
 
 /*
  * ptv3_attention_fwd with the relative position bias of model.py:297-316, 372-380,

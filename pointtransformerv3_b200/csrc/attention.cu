@@ -168,7 +168,7 @@ static int launch_attn_fma(const void* qkv, const int64_t* order, const int64_t*
 static int attention_impl(const void* qkv, const int64_t* order, const int64_t* pad, const int64_t* unpad,
                           const int32_t* cu_seqlens, void* out, int64_t n, int n_seq, int max_seqlen,
                           int channels, int heads, float scale, int dtype, int algo, ptv3::RpeArgs rpe,
-                          void* stream)
+                          uint32_t* status, void* stream)
 {
     using namespace ptv3;
     PTV3_REQUIRE(n >= 0 && n_seq >= 0 && max_seqlen >= 1 && channels >= 1 && heads >= 1 &&
@@ -181,10 +181,18 @@ static int attention_impl(const void* qkv, const int64_t* order, const int64_t* 
     if (n == 0 || n_seq == 0) return PTV3_OK;
     PTV3_REQUIRE(qkv && order && pad && unpad && cu_seqlens && out, PTV3_ERR_INVALID_ARGUMENT,
                  "ptv3_attention_fwd: null pointer");
-    PTV3_REQUIRE(algo >= 0 && algo <= 3, PTV3_ERR_INVALID_ARGUMENT, "ptv3_attention_fwd: algo %d", algo);
+    PTV3_REQUIRE(algo >= 0 && algo <= 4, PTV3_ERR_INVALID_ARGUMENT, "ptv3_attention_fwd: algo %d", algo);
     const bool mma_ok = rpe.grid_coord == nullptr && dtype == PTV3_DTYPE_BF16 &&
                         attn_mma_supported(channels, heads, max_seqlen) &&
                         n_seq <= 2147483647 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)out & 3) == 0;
+    const bool tc05_ok = mma_ok && status != nullptr && attn_tc05_supported(channels, heads, max_seqlen) &&
+                         ((uintptr_t)out & 15) == 0;
+    PTV3_REQUIRE(algo != 4 || tc05_ok, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_attention_fwd: the tcgen05 path needs bf16, head dim 16, max_seqlen <= %d, 16-byte "
+                 "aligned qkv and out, and a status word", ATTN_TC05_MAX_SEQLEN);
+    if (algo == 4)
+        return launch_attn_tc05(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen, channels,
+                                heads, scale, status, (cudaStream_t)stream);
     PTV3_REQUIRE(algo < 2 || mma_ok, PTV3_ERR_UNSUPPORTED,
                  "ptv3_attention_fwd: the tensor-core path needs bf16, head dim 16, max_seqlen <= %d and "
                  "16-byte aligned qkv", ATTN_MMA_MAX_SEQLEN);
@@ -201,10 +209,10 @@ static int attention_impl(const void* qkv, const int64_t* order, const int64_t* 
 extern "C" int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
                                   const int64_t* unpad, const int32_t* cu_seqlens, void* out,
                                   int64_t n, int n_seq, int max_seqlen, int channels, int heads,
-                                  float scale, int dtype, int algo, void* stream)
+                                  float scale, int dtype, int algo, uint32_t* status, void* stream)
 {
     return attention_impl(qkv, order, pad, unpad, cu_seqlens, out, n, n_seq, max_seqlen, channels, heads,
-                          scale, dtype, algo, ptv3::RpeArgs{nullptr, nullptr, 0, 0, 0}, stream);
+                          scale, dtype, algo, ptv3::RpeArgs{nullptr, nullptr, 0, 0, 0}, status, stream);
 }
 
 extern "C" int ptv3_attention_rpe_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
@@ -219,5 +227,5 @@ extern "C" int ptv3_attention_rpe_fwd(const void* qkv, const int64_t* order, con
                  "ptv3_attention_rpe_fwd: pos_bnd %d outside [0, 64]", pos_bnd);
     return attention_impl(qkv, order, pad, unpad, cu_seqlens, out, n, n_seq, max_seqlen, channels, heads,
                           scale, dtype, 1, RpeArgs{grid_coord, rpe_table, pos_bnd, 2 * pos_bnd + 1, heads},
-                          stream);
+                          nullptr, stream);
 }

@@ -223,7 +223,8 @@ class SerializedAttention(PointModule):
                                      point.grid_coord, self.rpe.rpe_table, self.rpe.pos_bnd, self.num_heads,
                                      self.patch_size, self.scale)
         return ops.attention(qkv, point.serialized_order[self.order_index], pad, unpad, cu_seqlens,
-                             self.num_heads, self.patch_size, self.scale, self.algo)
+                             self.num_heads, self.patch_size, self.scale, self.algo,
+                             status=point.device_status())
 
     def attend(self, point, feat):
         """qkv projection, patch attention and output projection of ``feat``."""

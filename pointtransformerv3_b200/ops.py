@@ -134,21 +134,29 @@ def pad_plan(offset, counts, patch, status=None):
     return pad, unpad, cu
 
 
-def attention(qkv, order_row, pad, unpad, cu_seqlens, heads, max_seqlen, scale, algo=0):
-    """qkv (N, 3C) -> (N, C): the attention core between the two Linear layers."""
+def attention(qkv, order_row, pad, unpad, cu_seqlens, heads, max_seqlen, scale, algo=0, status=None):
+    """qkv (N, 3C) -> (N, C): the attention core between the two Linear layers.
+    status: the caller's device status word (checked by the caller); without
+    one a private word is made and checked here."""
     _lib.require_cuda(qkv, order_row, pad, unpad, cu_seqlens)
     lib = _lib.load()
     qkv = qkv.contiguous()
     n, c3 = qkv.shape
     C = c3 // 3
     out = torch.empty((n, C), dtype=qkv.dtype, device=qkv.device)
+    own = status is None
+    if own:
+        status = new_status(qkv.device)
     # algorithmic work: QK^T and PV over every padded row against its whole patch
     with timed("attention", 4.0 * pad.numel() * max_seqlen * C):
         _lib.check(lib.ptv3_attention_fwd(_lib.ptr(qkv), _lib.ptr(order_row.contiguous()), _lib.ptr(pad),
                                           _lib.ptr(unpad), _lib.ptr(cu_seqlens), _lib.ptr(out), n,
                                           cu_seqlens.numel() - 1, int(max_seqlen), C, int(heads),
-                                          float(scale), _lib.dtype_id(qkv), int(algo), _lib.stream()),
+                                          float(scale), _lib.dtype_id(qkv), int(algo), _lib.ptr(status),
+                                          _lib.stream()),
                    "ptv3_attention_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_attention_fwd")
     return out
 
 

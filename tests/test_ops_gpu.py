@@ -190,9 +190,51 @@ def test_attention_tensor_core_path_matches_cuda_core_path(sizes, C, H, K):
     assert rel_l2(b, a) < 5e-3
 
 
-def test_attention_config2_size_bf16():
+@pytest.mark.parametrize("sizes,C,H,K", [([3000], 64, 4, 1024), ([1100, 90, 2049], 32, 2, 1024),
+                                         ([5000], 128, 8, 512), ([777], 16, 1, 100), ([130, 129, 128, 127], 32, 2, 1024),
+                                         ([2048, 1025], 64, 4, 1024), ([300], 512, 32, 1024)])
+def test_attention_tcgen05_path_matches_cuda_core_path(sizes, C, H, K):
+    """Same inputs through the tcgen05 kernel (algo 4) and the CUDA-core kernel
+    (algo 1), bf16: full and ragged patches, patches shorter than a key block,
+    borrowed rows of a last patch."""
+    data = small_batch(sizes, 11)
+    offset = data["offset"]
+    counts = O.offset_to_counts(offset).tolist()
+    batch = O.offset_to_batch(offset)
+    code, order, inverse, depth = O.serialization(data["grid_coord"], batch, ["hilbert-trans"])
+    g = torch.Generator().manual_seed(2)
+    qkv = (torch.randn(batch.shape[0], 3 * C, generator=g) * 1.5).bfloat16().cuda()
+    # flash semantics (patch size kept, short scenes are one short patch) and the
+    # non-flash rule (patch shrunk to the smallest scene)
+    for Ke in (K, min(min(counts), K)):
+        pad, unpad, cu = ops.pad_plan(offset.cuda(), counts, Ke)
+        a = ops.attention(qkv, order[0].cuda(), pad, unpad, cu, H, Ke, (C // H) ** -0.5, algo=1)
+        b = ops.attention(qkv, order[0].cuda(), pad, unpad, cu, H, Ke, (C // H) ** -0.5, algo=4)
+        assert_close(b, a, atol=1e-2, rtol=1e-2, what="tcgen05 vs CUDA-core attention")
+        assert rel_l2(b, a) < 5e-3
+
+
+def test_attention_tcgen05_large_scores():
+    """Scores far from zero (|s| up to a few hundred): the running maximum and the
+    rescaling of the output across key blocks must hold."""
+    n, C, H, K = 4096, 32, 2, 1024
+    g = torch.Generator().manual_seed(5)
+    grid = torch.randint(0, 64, (n, 3), generator=g, dtype=torch.int32)
+    order = O.serialization(grid, torch.zeros(n, dtype=torch.int64), ["z"])[1]
+    qkv = torch.randn(n, 3 * C, generator=g)
+    qkv[:, :2 * C] *= 6.0
+    qkv = qkv.bfloat16().cuda()
+    pad, unpad, cu = ops.pad_plan(torch.tensor([n]).cuda(), [n], K)
+    a = ops.attention(qkv, order[0].cuda(), pad, unpad, cu, H, K, 0.25, algo=1)
+    b = ops.attention(qkv, order[0].cuda(), pad, unpad, cu, H, K, 0.25, algo=4)
+    assert bool(torch.isfinite(b.float()).all())
+    assert rel_l2(b, a) < 1e-2
+
+
+@pytest.mark.parametrize("ALGO", [2, 4])
+def test_attention_config2_size_bf16(ALGO):
     """N = 120 000, C = 64, 4 heads, patch 1024 (118 patches, the last one padded by
-    borrowing): tensor-core path against the fp32 oracle on a row sample."""
+    borrowing): both tensor-core paths against the fp32 oracle on a row sample."""
     n, C, H, K = 120_000, 64, 4, 1024
     g = torch.Generator().manual_seed(0)
     grid = torch.randint(0, 512, (n, 3), generator=g, dtype=torch.int32)
@@ -202,7 +244,7 @@ def test_attention_config2_size_bf16():
     qkv = torch.randn(n, 3 * C, generator=g)
     pad, unpad, cu = ops.pad_plan(offset.cuda(), [n], K)
     assert pad.numel() == 120_832 and cu.numel() == 119
-    got = ops.attention(qkv.bfloat16().cuda(), order[0].cuda(), pad, unpad, cu, H, K, 0.25, algo=2).float().cpu()
+    got = ops.attention(qkv.bfloat16().cuda(), order[0].cuda(), pad, unpad, cu, H, K, 0.25, algo=ALGO).float().cpu()
     # oracle for the first, a middle and the (borrowing) last patch
     rp, ru, rc = O.pad_plan(offset, K)
     x = qkv.bfloat16().float()
