@@ -29,12 +29,15 @@
 //
 // Measured on B200 (407 000 points, C = 64, 4 heads): 0.65 ms against 0.57 ms of the
 // mma.sync kernel (attention_mma.cu), i.e. 2.6e12 against 2.9e12 exponentials per
-// second of the unit's 4.5e12.  Cycle stamps show where it goes: inside the key-block
-// loop the unit is about 75 % busy (a block costs a group ~1100 cycles of mbarrier
-// waits, tensor-memory loads / stores and the row maximum around 512 cycles of
-// exponentials, and only four groups fit), and a CTA spends ~20 % of its time in the
-// exposed K / V gather and query staging, which three co-resident CTAs hide in the
-// mma.sync kernel.  The automatic choice therefore stays with the mma.sync kernel.
+// second of the unit's 4.5e12.  Cycle stamps of one thread show why: a key block takes
+// a group ~2600 cycles, of which the exponentials are 1100-1300 (512 alone); every
+// round trip through an mbarrier (try_wait on a completed phase) or tensor memory
+// (tcgen05.ld / st + wait) costs 100-300 cycles, there are seven of them per block, and
+// only four groups fit in the 512 columns to hide them.  With the exponentials removed
+// altogether the kernel still takes 0.52 ms; moving a third of them to the FMA pipe or
+// staggering the groups changes nothing.  A CTA also spends ~15 % of its life in the
+// exposed K / V gather, which three co-resident CTAs hide in the mma.sync kernel.  The
+// automatic choice therefore stays with the mma.sync kernel.
 #include "common.cuh"
 #include "attention_mma.cuh"
 #include "mma_util.cuh"
@@ -272,9 +275,6 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
         }
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
-#ifdef AT_STAGGER
-        if (wg) __nanosleep(wg * AT_STAGGER);
-#endif
         // ---- softmax groups: thread t owns query row t of the tile ---------------------
         unsigned char* qs_ptr = smem + lay.off_q + wg * AT_Q_BYTES;
         const uint32_t tm_lane = (uint32_t)((warp & 3) * 32) << 16;
