@@ -5,9 +5,10 @@
 
 Workload per GPU: the default backbone, random init, eval, bf16, on a batch of
 four synthetic indoor scenes of about 100k voxels each (grid 0.02 m).  With N
-GPUs every rank runs its own four scenes (weak scaling) and the output features
-are all-gathered over NCCL at the end of every step.  One JSON line is printed
-by rank 0.
+GPUs every rank runs its own four scenes (weak scaling); scenes are independent,
+so the data path has no collective (`--gather-outputs` adds an NCCL all-gather of
+the output features to every step, for a caller that wants them on every rank).
+One JSON line is printed by rank 0.
 
 `--impl reference` times the CPU restatement of the reference path (the oracle)
 on the host cores, on a bounded sample of the same workload.
@@ -34,10 +35,11 @@ GRID = 0.02
 CPU_SAMPLE_VOXELS = 100_000
 
 
-def workload_config(n_gpus):
+def workload_config(n_gpus, gather=False):
     return {"workload": "full PTv3 backbone forward, default config, bf16 eval, random init; "
                         "%d synthetic indoor scenes of ~100k voxels per GPU, grid 0.02" % SCENES_PER_GPU,
-            "scenes_per_gpu": SCENES_PER_GPU, "parallelism": "scene-parallel x%d, outputs all-gathered" % n_gpus,
+            "scenes_per_gpu": SCENES_PER_GPU, "parallelism": "scene-parallel x%d, %s" % (
+                n_gpus, "outputs all-gathered" if gather else "no data-path collective"),
             "l2": "256 MiB buffer written between timed steps (outside the per-step events)"}
 
 
@@ -150,6 +152,7 @@ def run_ours(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     lib = _lib.load()
+    gather = world > 1 and args.gather_outputs
 
     data = synthetic.indoor_batch(SCENES_PER_GPU, first_seed=rank * SCENES_PER_GPU,
                                   target_voxels=TARGET_VOXELS, grid_size=GRID, dtype=torch.bfloat16)
@@ -167,7 +170,7 @@ def run_ours(args):
         torch.manual_seed(1)          # fixes the order-shuffle draws of every step
         with torch.inference_mode():
             feat = net(dict(d)).feat
-            if world > 1:
+            if gather:
                 feat, _ = distributed.gather_features(feat)
         return feat
 
@@ -180,7 +183,7 @@ def run_ours(args):
             torch.manual_seed(1)
             feat = net(d).feat
             out_host.copy_(feat, non_blocking=True)
-            if world > 1:
+            if gather:
                 distributed.gather_features(feat)
         torch.cuda.current_stream().synchronize()
 
@@ -263,7 +266,7 @@ def run_ours(args):
             "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": dict(workload_config(world), points_per_gpu=n_points),
+            "config": dict(workload_config(world, gather), points_per_gpu=n_points),
             "clocks": clocks,
             "e2e": None if ms_e2e is None else {
                 "value": total_points * args.steps / (ms_e2e * 1e-3), "unit": UNIT,
@@ -447,6 +450,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--gather-outputs", action="store_true",
+                    help="N > 1: all-gather the output features over NCCL inside every step")
     ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv", "mlp", "pooling"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
