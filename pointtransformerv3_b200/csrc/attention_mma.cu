@@ -26,6 +26,7 @@ constexpr int AM_WARPS = AM_THREADS / 32;
 constexpr int AM_KC = 64;           // keys per online-softmax step
 constexpr int AM_D = 16;
 constexpr float AM_LOG2E = 1.4426950408889634f;
+constexpr float AM_LAZY = 8.f;       // slack of the running maximum, in powers of two
 
 // byte offset of 16-byte chunk c (0/1) of row r in a [rows][16] bf16 tile whose
 // chunks are swapped in rows 4..7 (mod 8) so that 8-row ldmatrix reads hit 32
@@ -151,24 +152,33 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
                 mx0 = fmaxf(fmaxf(mx0, s[j][0]), s[j][1]);
                 mx1 = fmaxf(fmaxf(mx1, s[j][2]), s[j][3]);
             }
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-            // every chunk holds at least one real key, so mn is finite
-            const float c0 = fast_exp2((m0 - mn0) * sl2), c1 = fast_exp2((m1 - mn1) * sl2);
-            m0 = mn0;
-            m1 = mn1;
-            osum[0] *= c0;
-            osum[2] *= c1;
+            // Lazy reference: the running "maximum" m only has to keep the exponentials in
+            // range, so it is raised (and the output rescaled) only when some score of the
+            // chunk exceeds it by more than AM_LAZY in the exp2 domain; probabilities then
+            // stay below 2^AM_LAZY, exact in bf16's range and harmless in the fp32 sums.
+            // After the first chunks of a sequence this is rare, and the common path needs
+            // neither the cross-lane reduction nor the rescaling.
+            if (__any_sync(0xffffffffu, (mx0 - m0) * sl2 > AM_LAZY || (mx1 - m1) * sl2 > AM_LAZY)) {
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+                // every chunk holds at least one real key, so mn is finite
+                const float c0 = fast_exp2((m0 - mn0) * sl2), c1 = fast_exp2((m1 - mn1) * sl2);
+                m0 = mn0;
+                m1 = mn1;
+                osum[0] *= c0;
+                osum[2] *= c1;
 #pragma unroll
-            for (int n = 0; n < 2; ++n) {
-                o[n][0] *= c0;
-                o[n][1] *= c0;
-                o[n][2] *= c1;
-                o[n][3] *= c1;
+                for (int n = 0; n < 2; ++n) {
+                    o[n][0] *= c0;
+                    o[n][1] *= c0;
+                    o[n][2] *= c1;
+                    o[n][3] *= c1;
+                }
             }
+            const float mn0 = m0, mn1 = m1;
             const float b0 = mn0 * sl2, b1 = mn1 * sl2;
             uint32_t pa[8][2];
 #pragma unroll
