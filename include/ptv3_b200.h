@@ -344,6 +344,52 @@ int ptv3_linear_ln_fwd(const void* x, const void* weight, const void* bias, cons
                        const void* ln2_weight, const void* ln2_bias, float ln2_eps, void* norm_out,
                        int64_t n, int channels, int dtype, uint32_t* status, void* stream);
 
+/*
+ * One transformer block in one call (model.py:519-606, Block.forward, inference,
+ * pre-norm, bf16): xCPE convolution + Linear + LayerNorm, attention with its two
+ * Linear layers, MLP, the three residual additions.  The same kernels as the
+ * single-operator entry points, queued from C++ so that a block costs the host
+ * one call; channel widths outside the tcgen05 kernels' range take their Linear
+ * layers from cuBLASLt.  All pointers are device pointers except the struct.
+ */
+typedef struct ptv3_block_args {
+    int64_t n;                      /* voxels of the level */
+    int channels, heads, hidden;    /* hidden = MLP width */
+    int dtype;                      /* PTV3_DTYPE_BF16 */
+    int n_seq, max_seqlen;          /* patches, longest patch (as for ptv3_attention_fwd) */
+    int attention_algo;             /* algo of ptv3_attention_fwd, 0 = automatic */
+    float scale;                    /* attention scale */
+    float cpe_ln_eps, n1_eps, n2_eps;
+    const void* conv_in;            /* n x C rows the convolution reads (the sparse tensor's features) */
+    const void* feat;               /* n x C residual stream entering the block */
+    void* out;                      /* n x C result */
+    /* convolution geometry: the kernel map (nbr, optional row_order) or, when pair_in is
+       given, the pair list of ptv3_conv_pairs_build */
+    const int32_t* nbr;
+    const int64_t* row_order;
+    const int32_t *pair_in, *pair_out, *off_start, *tile_start;
+    /* attention geometry, as for ptv3_attention_fwd */
+    const int64_t *order, *pad, *unpad;
+    const int32_t* cu_seqlens;
+    /* parameters, in the layouts of the reference's state_dict */
+    const void *conv_weight, *conv_bias;      /* cpe.0 */
+    const void *cpe_w, *cpe_b;                /* cpe.1 */
+    const void *cpe_ln_w, *cpe_ln_b;          /* cpe.2 */
+    const void *n1_w, *n1_b;                  /* norm1.0 */
+    const void *qkv_w, *qkv_b;                /* attn.qkv */
+    const void *proj_w, *proj_b;              /* attn.proj */
+    const void *n2_w, *n2_b;                  /* norm2.0 */
+    const void *fc1_w, *fc1_b, *fc2_w, *fc2_b; /* mlp.0.fc1 / fc2 */
+    uint32_t* status;               /* device status word, OR-ed with PTV3_STATUS_* bits */
+    void* workspace;                /* ptv3_block_workspace_bytes(args) bytes, 256-byte aligned */
+    size_t workspace_bytes;
+} ptv3_block_args;
+
+int ptv3_block_supported(int channels, int heads, int hidden, int dtype);
+/* reads n, channels, hidden, dtype and pair_in (null or not) of the argument block */
+size_t ptv3_block_workspace_bytes(const ptv3_block_args* args);
+int ptv3_block_fwd(const ptv3_block_args* args, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -16,6 +16,22 @@ c_f32 = ctypes.c_float
 c_sz = ctypes.c_size_t
 c_ptr = ctypes.c_void_p
 
+
+
+class BlockArgs(ctypes.Structure):
+    """ptv3_block_args of include/ptv3_b200.h (same field order)."""
+    _fields_ = (
+        [("n", c_i64), ("channels", c_int), ("heads", c_int), ("hidden", c_int), ("dtype", c_int),
+         ("n_seq", c_int), ("max_seqlen", c_int), ("attention_algo", c_int), ("scale", c_f32),
+         ("cpe_ln_eps", c_f32), ("n1_eps", c_f32), ("n2_eps", c_f32)]
+        + [(name, c_ptr) for name in (
+            "conv_in", "feat", "out", "nbr", "row_order", "pair_in", "pair_out", "off_start", "tile_start",
+            "order", "pad", "unpad", "cu_seqlens", "conv_weight", "conv_bias", "cpe_w", "cpe_b", "cpe_ln_w",
+            "cpe_ln_b", "n1_w", "n1_b", "qkv_w", "qkv_b", "proj_w", "proj_b", "n2_w", "n2_b", "fc1_w", "fc1_b",
+            "fc2_w", "fc2_b", "status", "workspace")]
+        + [("workspace_bytes", c_sz)])
+
+
 # name -> (restype, argtypes); must list every symbol of include/ptv3_b200.h
 SIGNATURES = {
     "ptv3_last_error": (ctypes.c_char_p, []),
@@ -58,6 +74,9 @@ SIGNATURES = {
     "ptv3_mlp_supported": (c_int, [c_int, c_int, c_int]),
     "ptv3_mlp_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int, c_ptr,
                              c_ptr]),
+    "ptv3_block_supported": (c_int, [c_int, c_int, c_int, c_int]),
+    "ptv3_block_workspace_bytes": (c_sz, [ctypes.POINTER(BlockArgs)]),
+    "ptv3_block_fwd": (c_int, [ctypes.POINTER(BlockArgs), c_ptr]),
     "ptv3_unpool_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
                                 c_ptr, c_int, c_ptr]),
 }

@@ -294,9 +294,66 @@ class Block(PointModule):
                 and point.feat.dtype in (torch.float32, torch.bfloat16)
                 and "sparse_conv_feat" in point.keys())
 
+    def _native_args(self, dt, device):
+        """The argument block of ptv3_block_fwd with this block's parameters filled
+        in, cached until a parameter's storage changes."""
+        conv, lin, attn, mlp = self.cpe[0], self.cpe[1], self.attn, self.mlp[0]
+        names = ("conv_weight", "conv_bias", "cpe_w", "cpe_b", "cpe_ln_w", "cpe_ln_b", "n1_w", "n1_b", "qkv_w",
+                 "qkv_b", "proj_w", "proj_b", "n2_w", "n2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")
+        params = (conv.weight, conv.bias, lin.weight, lin.bias, self.cpe[2].weight, self.cpe[2].bias,
+                  self.norm1[0].weight, self.norm1[0].bias, attn.qkv.weight, attn.qkv.bias, attn.proj.weight,
+                  attn.proj.bias, self.norm2[0].weight, self.norm2[0].bias, mlp.fc1.weight, mlp.fc1.bias,
+                  mlp.fc2.weight, mlp.fc2.bias)
+        if any(p is None or p.dtype != dt or p.device != device or not p.is_contiguous() for p in params):
+            return None
+        ptrs = tuple(p.data_ptr() for p in params)
+        cached = self.__dict__.get("_ptv3_block_args")
+        if cached is None or cached[0] != ptrs:
+            a = _lib.BlockArgs()
+            a.channels, a.heads, a.hidden = self.channels, attn.num_heads, mlp.fc1.out_features
+            a.dtype = _lib.DTYPE_IDS[dt]
+            a.cpe_ln_eps, a.n1_eps, a.n2_eps = self.cpe[2].eps, self.norm1[0].eps, self.norm2[0].eps
+            for name, ptr in zip(names, ptrs):
+                setattr(a, name, ptr)
+            cached = (ptrs, a)
+            self.__dict__["_ptv3_block_args"] = cached
+        a = cached[1]
+        a.attention_algo, a.scale = attn.algo, attn.scale
+        return a
+
+    def _forward_native(self, point):
+        """The whole block queued by one C call (ptv3_block_fwd); None when the
+        configuration is outside what that entry point covers."""
+        shortcut, sparse = point.feat, point.sparse_conv_feat
+        attn, mlp, conv = self.attn, self.mlp[0], self.cpe[0]
+        dt = shortcut.dtype
+        if (ops.TIMERS is not None or attn.enable_rpe or conv.kernel_size != 3
+                or conv.in_channels != self.channels or conv.out_channels != self.channels
+                or mlp.fc2.out_features != self.channels or mlp.fc1.in_features != self.channels
+                or not ops.block_supported(self.channels, attn.num_heads, mlp.fc1.out_features, dt)):
+            return None
+        args = self._native_args(dt, shortcut.device)
+        if args is None:
+            return None
+        if not attn.enable_flash:
+            attn.patch_size = min(min(point.host_counts()), attn.patch_size_max)
+        pad, unpad, cu_seqlens = attn.get_padding_and_inverse(point)
+        feat = ops.block(args, sparse.features, shortcut, conv.geometry(sparse),
+                         {"order": point.serialized_order[attn.order_index], "pad": pad, "unpad": unpad,
+                          "cu_seqlens": cu_seqlens, "max_seqlen": attn.patch_size}, point.device_status())
+        point.check_status("ptv3_block_fwd")
+        point.feat = feat
+        point.sparse_conv_feat = sparse.replace_feature(feat)
+        return point
+
     def _forward_fused(self, point):
         """Same arithmetic as the generic path with the LayerNorms and residual
-        additions done by the fused row kernel (three launches instead of eight)."""
+        additions done by the fused row kernel (three launches instead of eight);
+        bf16 blocks go through one C call (the per-operator path below is kept for
+        fp32 and for per-operator timing)."""
+        done = self._forward_native(point)
+        if done is not None:
+            return done
         shortcut = point.feat
         sparse = point.sparse_conv_feat
         status = point.device_status()
@@ -657,34 +714,60 @@ class PointTransformerV3(PointModule):
         if not first_has_pooling:
             point = stages[0](point)
             stages = stages[1:]
-        # -- the pooling plans of all levels, on a second stream: their host reads wait only
-        #    for the small plan kernels, not for the feature work queued above
+        # -- the pooling plan of each coarser level, on a second stream and one level ahead of
+        #    the features: a plan has one host read (the coarse level's size), which then waits
+        #    only for the small plan kernels, while the GPU works on the stage queued before it
         side = self._side_stream(main.device)
         side.wait_event(serialized)
-        with torch.cuda.stream(side):
-            level = point
-            for stage in stages:
-                down = stage[0] if len(stage) > 0 and isinstance(stage[0], SerializedPooling) else None
-                if down is None:
-                    break
+
+        def plan_ahead(level, stage):
+            down = stage[0] if len(stage) > 0 and isinstance(stage[0], SerializedPooling) else None
+            if down is None:
+                return None
+            with torch.cuda.stream(side):
                 child = down.plan(level)
                 level["_pooled_child"] = child
-                level = child
                 # the coarse level's 3x3x3 kernel map (and pair list where the pair-list
                 # convolution will be taken) only needs its coordinates: make it here too
                 child["_prebuilt_kmaps"] = spconv.prebuild_kernel_map(
                     torch.cat([child.batch.unsqueeze(-1).int(), child.grid_coord.int()], dim=1).contiguous(),
                     child.serialized_order[0], 3, status,
                     with_pairs=child.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
-        main.wait_stream(side)
+            # Everything made here was allocated on the planning stream but is consumed (and
+            # some of it dropped) by work queued on the main stream: tell the allocator, or a
+            # block freed after its last main-stream use was *queued* could be handed to the
+            # next plan while that use has not run yet.
+            _record_stream(child, main)
+            planned = torch.cuda.Event()
+            planned.record(side)
+            return planned
+
         # -- feature phase, part 2
-        for stage in stages:
+        planned = plan_ahead(point, stages[0]) if stages else None
+        for i, stage in enumerate(stages):
+            if planned is not None:
+                main.wait_event(planned)
             point = stage(point)
+            planned = plan_ahead(point, stages[i + 1]) if i + 1 < len(stages) else None
         if not self.cls_mode:
             point = self.dec(point)
         point["_defer_status"] = False
         _lib.raise_on_status(status, "PointTransformerV3.forward")
         return point
+
+
+def _record_stream(obj, stream):
+    """tensor.record_stream(stream) for every CUDA tensor reachable through dicts,
+    lists and tuples of ``obj``."""
+    if isinstance(obj, torch.Tensor):
+        if obj.is_cuda:
+            obj.record_stream(stream)
+    elif isinstance(obj, dict):
+        for v in obj.values():
+            _record_stream(v, stream)
+    elif isinstance(obj, (list, tuple)):
+        for v in obj:
+            _record_stream(v, stream)
 
 
 GridPooling = SerializedPooling

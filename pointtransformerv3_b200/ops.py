@@ -473,3 +473,45 @@ def linear_ln(x, weight, bias, residual, ln1, ln2, status=None, want_sum=True):
     if own:
         _lib.raise_on_status(status, "ptv3_linear_ln_fwd")
     return s, y
+
+
+def block_supported(channels, heads, hidden, dtype):
+    return dtype in _lib.DTYPE_IDS and bool(
+        _lib.load().ptv3_block_supported(int(channels), int(heads), int(hidden), _lib.DTYPE_IDS[dtype]))
+
+
+def block(args, conv_in, feat, geometry, attention, status):
+    """One transformer block through ptv3_block_fwd.
+
+    args: a _lib.BlockArgs whose parameter pointers and static sizes the caller
+    has filled in (and keeps alive); conv_in, feat: (N, C) bf16; geometry:
+    dict(nbr, row_order) or a pair list of conv_pairs_build; attention:
+    dict(order, pad, unpad, cu_seqlens, max_seqlen).  Returns the (N, C) output."""
+    _lib.require_cuda(conv_in, feat, status)
+    lib = _lib.load()
+    conv_in, feat = conv_in.contiguous(), feat.contiguous()
+    n = feat.shape[0]
+    out = torch.empty_like(feat)
+    args.n = n
+    args.conv_in, args.feat, args.out = conv_in.data_ptr(), feat.data_ptr(), out.data_ptr()
+    if "pair_in" in geometry:
+        args.nbr = args.row_order = None
+        args.pair_in, args.pair_out = geometry["pair_in"].data_ptr(), geometry["pair_out"].data_ptr()
+        args.off_start, args.tile_start = geometry["off_start"].data_ptr(), geometry["tile_start"].data_ptr()
+    else:
+        args.pair_in = args.pair_out = args.off_start = args.tile_start = None
+        args.nbr = geometry["nbr"].data_ptr()
+        args.row_order = _lib.ptr(geometry["row_order"])
+    args.order, args.pad, args.unpad = (attention["order"].data_ptr(), attention["pad"].data_ptr(),
+                                        attention["unpad"].data_ptr())
+    args.cu_seqlens = attention["cu_seqlens"].data_ptr()
+    args.n_seq = attention["cu_seqlens"].numel() - 1
+    args.max_seqlen = int(attention["max_seqlen"])
+    args.status = status.data_ptr()
+    nbytes = lib.ptv3_block_workspace_bytes(ctypes.byref(args))
+    ws = _lib.workspace(nbytes, feat.device)
+    args.workspace, args.workspace_bytes = ws.data_ptr(), nbytes
+    C, H = args.channels, args.hidden
+    with timed("block", 2.0 * n * (27 * C * C + 4 * C * C + 2 * C * H)):
+        _lib.check(lib.ptv3_block_fwd(ctypes.byref(args), _lib.stream()), "ptv3_block_fwd")
+    return out

@@ -129,14 +129,22 @@ class SubMConv3d(SparseModule):
                 _lib.raise_on_status(x.status, "ptv3_subm_conv_direct_fwd")
             return x.replace_feature(out)
         assert bn_scale is None and not gelu
+        geo = self.geometry(x)
+        if "pair_in" in geo:
+            return x.replace_feature(ops.subm_conv_pairs(x.features, geo, self.weight, self.bias))
+        return x.replace_feature(ops.subm_conv(x.features, geo["nbr"], self.weight, self.bias,
+                                               row_order=geo["row_order"]))
+
+    def geometry(self, x):
+        """The index structure this convolution runs on for the sparse tensor ``x``:
+        the pair list on coarse levels (few voxels, wide channels: only the pairs
+        that exist are multiplied), else dict(nbr, row_order) of the kernel map."""
         n = x.features.shape[0]
-        # coarse levels (few voxels, wide channels): multiply only the pairs that exist
         if (x.features.dtype == torch.bfloat16 and self.kernel_size == 3 and n <= PAIR_PATH_MAX_VOXELS
                 and self.in_channels % 64 == 0 and self.out_channels % 128 == 0 and self.in_channels >= 128):
-            pairs = x.pair_list(self.kernel_size, self.indice_key)
-            return x.replace_feature(ops.subm_conv_pairs(x.features, pairs, self.weight, self.bias))
+            return x.pair_list(self.kernel_size, self.indice_key)
         nbr, row_order = x.kernel_map(self.kernel_size, self.indice_key)
-        return x.replace_feature(ops.subm_conv(x.features, nbr, self.weight, self.bias, row_order=row_order))
+        return {"nbr": nbr, "row_order": row_order}
 
 
 class _Modules:
