@@ -674,7 +674,9 @@ class PointTransformerV3(PointModule):
     def _side_stream(self, device):
         streams = self.__dict__.setdefault("_ptv3_side_streams", {})
         if device not in streams:
-            streams[device] = torch.cuda.Stream(device=device)
+            # high priority: the plan kernels are tiny and must not queue behind the blocks of a
+            # feature kernel that fills the GPU
+            streams[device] = torch.cuda.Stream(device=device, priority=-1)
         return streams[device]
 
     def forward(self, data_dict):
@@ -702,53 +704,64 @@ class PointTransformerV3(PointModule):
             off = [0] + stats[3:]
             point["_counts"] = [off[i + 1] - off[i] for i in range(len(off) - 1)]
         point.serialization(order=self.order, depth=depth, shuffle_orders=self.shuffle_orders)
-        # -- feature phase, part 1: the stem and the first encoder stage need no pooling plan;
-        #    they are queued first so that the GPU is busy while the plans are made
+        # -- Schedule.  The pooling plan of a coarser level needs only the codes of the level
+        #    above it; it has one host read (its size) and a few dozen small launches, which
+        #    run on a second, high-priority stream.  Plans are made two stages ahead of the
+        #    features (level 1 while the stem runs, level 2 while the first encoder stage runs,
+        #    level s + 2 while stage s runs), so that their host reads never wait behind, and
+        #    never hold up, the feature kernels.
         main = torch.cuda.current_stream()
         serialized = torch.cuda.Event()
         serialized.record(main)
-        stages = list(self.enc._modules.values())
-        point.sparsify()
-        point = self.embedding(point)
-        first_has_pooling = len(stages[0]) > 0 and isinstance(stages[0][0], SerializedPooling)
-        if not first_has_pooling:
-            point = stages[0](point)
-            stages = stages[1:]
-        # -- the pooling plan of each coarser level, on a second stream and one level ahead of
-        #    the features: a plan has one host read (the coarse level's size), which then waits
-        #    only for the small plan kernels, while the GPU works on the stage queued before it
         side = self._side_stream(main.device)
         side.wait_event(serialized)
+        stages = list(self.enc._modules.values())
+        events = {}
+        plan_state = {"cursor": point, "next": 0}
 
-        def plan_ahead(level, stage):
-            down = stage[0] if len(stage) > 0 and isinstance(stage[0], SerializedPooling) else None
-            if down is None:
-                return None
-            with torch.cuda.stream(side):
-                child = down.plan(level)
-                level["_pooled_child"] = child
-                # the coarse level's 3x3x3 kernel map (and pair list where the pair-list
-                # convolution will be taken) only needs its coordinates: make it here too
-                child["_prebuilt_kmaps"] = spconv.prebuild_kernel_map(
-                    torch.cat([child.batch.unsqueeze(-1).int(), child.grid_coord.int()], dim=1).contiguous(),
-                    child.serialized_order[0], 3, status,
-                    with_pairs=child.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
-            # Everything made here was allocated on the planning stream but is consumed (and
-            # some of it dropped) by work queued on the main stream: tell the allocator, or a
-            # block freed after its last main-stream use was *queued* could be handed to the
-            # next plan while that use has not run yet.
-            _record_stream(child, main)
-            planned = torch.cuda.Event()
-            planned.record(side)
-            return planned
+        def plan_upto(last):
+            """Plans the pooling at the head of stages[next .. last] on the planning stream."""
+            while plan_state["next"] <= min(last, len(stages) - 1):
+                i = plan_state["next"]
+                plan_state["next"] += 1
+                stage, level = stages[i], plan_state["cursor"]
+                down = stage[0] if len(stage) > 0 and isinstance(stage[0], SerializedPooling) else None
+                if down is None:
+                    if i == 0:
+                        continue            # the finest stage has no pooling
+                    plan_state["next"] = len(stages)
+                    return
+                with torch.cuda.stream(side):
+                    child = down.plan(level)
+                    level["_pooled_child"] = child
+                    # the coarse level's 3x3x3 kernel map (and pair list where the pair-list
+                    # convolution will be taken) only needs its coordinates: make it here too
+                    child["_prebuilt_kmaps"] = spconv.prebuild_kernel_map(
+                        torch.cat([child.batch.unsqueeze(-1).int(), child.grid_coord.int()], dim=1).contiguous(),
+                        child.serialized_order[0], 3, status,
+                        with_pairs=child.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
+                    # ... and the patch layout of the stage's attention blocks
+                    for m in stage:
+                        if isinstance(m, Block) and m.attn.enable_flash:
+                            m.attn.get_padding_and_inverse(child)
+                            break
+                # Everything made here was allocated on the planning stream but is consumed
+                # (and some of it dropped) by work queued on the main stream: tell the
+                # allocator, or a block freed after its last main-stream use was *queued*
+                # could be handed to a later plan while that use has not run yet.
+                _record_stream(child, main)
+                events[i] = torch.cuda.Event()
+                events[i].record(side)
+                plan_state["cursor"] = child
 
-        # -- feature phase, part 2
-        planned = plan_ahead(point, stages[0]) if stages else None
+        point.sparsify()
+        point = self.embedding(point)
+        plan_upto(1)
         for i, stage in enumerate(stages):
-            if planned is not None:
-                main.wait_event(planned)
+            if i in events:
+                main.wait_event(events[i])
             point = stage(point)
-            planned = plan_ahead(point, stages[i + 1]) if i + 1 < len(stages) else None
+            plan_upto(i + 2)
         if not self.cls_mode:
             point = self.dec(point)
         point["_defer_status"] = False
