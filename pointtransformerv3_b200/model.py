@@ -736,9 +736,9 @@ class PointTransformerV3(PointModule):
                     level["_pooled_child"] = child
                     # the coarse level's 3x3x3 kernel map (and pair list where the pair-list
                     # convolution will be taken) only needs its coordinates: make it here too
+                    child["_sparse_indices"] = child._sparse_indices()
                     child["_prebuilt_kmaps"] = spconv.prebuild_kernel_map(
-                        torch.cat([child.batch.unsqueeze(-1).int(), child.grid_coord.int()], dim=1).contiguous(),
-                        child.serialized_order[0], 3, status,
+                        child["_sparse_indices"], child.serialized_order[0], 3, status,
                         with_pairs=child.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
                     # ... and the patch layout of the stage's attention blocks
                     for m in stage:
@@ -756,11 +756,21 @@ class PointTransformerV3(PointModule):
 
         point.sparsify()
         point = self.embedding(point)
-        plan_upto(1)
         for i, stage in enumerate(stages):
             if i in events:
                 main.wait_event(events[i])
-            point = stage(point)
+            mods = list(stage._modules.values())
+            if i == 0 and len(mods) > 1 and all(isinstance(m, Block) for m in mods):
+                # the stem is one short kernel: queue the first block behind it before the
+                # host turns to the first plan
+                point = mods[0](point)
+                plan_upto(1)
+                for m in mods[1:]:
+                    point = m(point)
+            else:
+                if i == 0:
+                    plan_upto(1)
+                point = stage(point)
             plan_upto(i + 2)
         if not self.cls_mode:
             point = self.dec(point)

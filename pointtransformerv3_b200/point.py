@@ -132,6 +132,14 @@ class Point(AttrDict):
         self["serialized_order"] = sorted_order
         self["serialized_inverse"] = inverse
 
+    def _sparse_indices(self):
+        """(N, 4) int32 rows (batch, x, y, z); a copy prepared together with the level's
+        pooling plan is used when there is one."""
+        ready = self.pop("_sparse_indices", None)
+        if ready is not None:
+            return ready
+        return torch.cat([self.batch.unsqueeze(-1).int(), self.grid_coord.int()], dim=1).contiguous()
+
     def sparsify(self, pad=96):
         """model.py:138-174: wraps the features and (batch, x, y, z) indices in a
         SparseConvTensor for the submanifold convolutions."""
@@ -145,7 +153,7 @@ class Point(AttrDict):
         self["sparse_shape"] = sparse_shape
         self["sparse_conv_feat"] = SparseConvTensor(
             features=self.feat,
-            indices=torch.cat([self.batch.unsqueeze(-1).int(), self.grid_coord.int()], dim=1).contiguous(),
+            indices=self._sparse_indices(),
             spatial_shape=sparse_shape,
             batch_size=len(self.offset),
             row_order=self.serialized_order[0] if "serialized_order" in self.keys() else None,
