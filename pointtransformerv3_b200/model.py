@@ -296,41 +296,60 @@ class Block(PointModule):
 
     def _native_args(self, dt, device):
         """The argument block of ptv3_block_fwd with this block's parameters filled
-        in, cached until a parameter's storage changes."""
+        in.  It is rebuilt whenever a parameter object or its storage changed; the
+        check walks the submodules' parameter dicts directly, which costs a few
+        microseconds instead of the attribute lookups of a rebuild."""
+        cached = self.__dict__.get("_ptv3_block_args")
+        if cached is not None:
+            holders, params, ptrs, a = cached
+            for (owner, name), p, ptr in zip(holders, params, ptrs):
+                if owner[name] is not p or p.data_ptr() != ptr:
+                    break
+            else:
+                if params[0].dtype == dt and params[0].device == device:
+                    a.attention_algo, a.scale = self.attn.algo, self.attn.scale
+                    return a
         conv, lin, attn, mlp = self.cpe[0], self.cpe[1], self.attn, self.mlp[0]
         names = ("conv_weight", "conv_bias", "cpe_w", "cpe_b", "cpe_ln_w", "cpe_ln_b", "n1_w", "n1_b", "qkv_w",
                  "qkv_b", "proj_w", "proj_b", "n2_w", "n2_b", "fc1_w", "fc1_b", "fc2_w", "fc2_b")
-        params = (conv.weight, conv.bias, lin.weight, lin.bias, self.cpe[2].weight, self.cpe[2].bias,
-                  self.norm1[0].weight, self.norm1[0].bias, attn.qkv.weight, attn.qkv.bias, attn.proj.weight,
-                  attn.proj.bias, self.norm2[0].weight, self.norm2[0].bias, mlp.fc1.weight, mlp.fc1.bias,
-                  mlp.fc2.weight, mlp.fc2.bias)
+        owners = (conv, conv, lin, lin, self.cpe[2], self.cpe[2], self.norm1[0], self.norm1[0], attn.qkv, attn.qkv,
+                  attn.proj, attn.proj, self.norm2[0], self.norm2[0], mlp.fc1, mlp.fc1, mlp.fc2, mlp.fc2)
+        holders = tuple((m._parameters, "weight" if i % 2 == 0 else "bias") for i, m in enumerate(owners))
+        params = tuple(owner[name] for owner, name in holders)
         if any(p is None or p.dtype != dt or p.device != device or not p.is_contiguous() for p in params):
+            self.__dict__.pop("_ptv3_block_args", None)
             return None
         ptrs = tuple(p.data_ptr() for p in params)
-        cached = self.__dict__.get("_ptv3_block_args")
-        if cached is None or cached[0] != ptrs:
-            a = _lib.BlockArgs()
-            a.channels, a.heads, a.hidden = self.channels, attn.num_heads, mlp.fc1.out_features
-            a.dtype = _lib.DTYPE_IDS[dt]
-            a.cpe_ln_eps, a.n1_eps, a.n2_eps = self.cpe[2].eps, self.norm1[0].eps, self.norm2[0].eps
-            for name, ptr in zip(names, ptrs):
-                setattr(a, name, ptr)
-            cached = (ptrs, a)
-            self.__dict__["_ptv3_block_args"] = cached
-        a = cached[1]
+        a = _lib.BlockArgs()
+        a.channels, a.heads, a.hidden = self.channels, attn.num_heads, mlp.fc1.out_features
+        a.dtype = _lib.DTYPE_IDS[dt]
+        a.cpe_ln_eps, a.n1_eps, a.n2_eps = self.cpe[2].eps, self.norm1[0].eps, self.norm2[0].eps
+        for name, ptr in zip(names, ptrs):
+            setattr(a, name, ptr)
+        self.__dict__["_ptv3_block_args"] = (holders, params, ptrs, a)
         a.attention_algo, a.scale = attn.algo, attn.scale
         return a
+
+    def _native_static_ok(self, dt):
+        """Shape conditions of the single-call path that do not depend on the input."""
+        key = ("_ptv3_native_ok", dt)
+        ok = self.__dict__.get(key)
+        if ok is None:
+            attn, mlp, conv = self.attn, self.mlp[0], self.cpe[0]
+            ok = (conv.kernel_size == 3 and conv.in_channels == self.channels
+                  and conv.out_channels == self.channels and mlp.fc2.out_features == self.channels
+                  and mlp.fc1.in_features == self.channels
+                  and ops.block_supported(self.channels, attn.num_heads, mlp.fc1.out_features, dt))
+            self.__dict__[key] = ok
+        return ok
 
     def _forward_native(self, point):
         """The whole block queued by one C call (ptv3_block_fwd); None when the
         configuration is outside what that entry point covers."""
         shortcut, sparse = point.feat, point.sparse_conv_feat
-        attn, mlp, conv = self.attn, self.mlp[0], self.cpe[0]
+        attn = self.attn
         dt = shortcut.dtype
-        if (ops.TIMERS is not None or attn.enable_rpe or conv.kernel_size != 3
-                or conv.in_channels != self.channels or conv.out_channels != self.channels
-                or mlp.fc2.out_features != self.channels or mlp.fc1.in_features != self.channels
-                or not ops.block_supported(self.channels, attn.num_heads, mlp.fc1.out_features, dt)):
+        if ops.TIMERS is not None or attn.enable_rpe or not self._native_static_ok(dt):
             return None
         args = self._native_args(dt, shortcut.device)
         if args is None:
@@ -338,7 +357,7 @@ class Block(PointModule):
         if not attn.enable_flash:
             attn.patch_size = min(min(point.host_counts()), attn.patch_size_max)
         pad, unpad, cu_seqlens = attn.get_padding_and_inverse(point)
-        feat = ops.block(args, sparse.features, shortcut, conv.geometry(sparse),
+        feat = ops.block(args, sparse.features, shortcut, self.cpe[0].geometry(sparse),
                          {"order": point.serialized_order[attn.order_index], "pad": pad, "unpad": unpad,
                           "cu_seqlens": cu_seqlens, "max_seqlen": attn.patch_size}, point.device_status())
         point.check_status("ptv3_block_fwd")
@@ -601,6 +620,8 @@ class PointTransformerV3(PointModule):
         self.num_stages = len(enc_depths)
         self.order = [order] if isinstance(order, str) else order
         self.cls_mode = cls_mode
+        # how many stages ahead of the features the pooling plans are made (see forward)
+        self.plan_ahead = 2
         self.shuffle_orders = shuffle_orders
         assert self.num_stages == len(stride) + 1
         assert self.num_stages == len(enc_depths)
@@ -771,7 +792,7 @@ class PointTransformerV3(PointModule):
                 if i == 0:
                     plan_upto(1)
                 point = stage(point)
-            plan_upto(i + 2)
+            plan_upto(i + self.plan_ahead)
         if not self.cls_mode:
             point = self.dec(point)
         point["_defer_status"] = False
