@@ -204,9 +204,10 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_mma_kernel(
     const uint32_t* __restrict__ cells, uint32_t* __restrict__ status)
 {
     constexpr int COUT = 8 * NT;
+    constexpr int WROW = COUT * 2 + 16;   // weight row pitch: 16 bytes of padding keep ldmatrix conflict-free
     extern __shared__ __align__(16) unsigned char smem[];
     unsigned char* x_s = smem;                                   // [CDM_CH][128] rows of 8 channels (16 B)
-    unsigned char* w_s = smem + CDM_CH * CD_TM * 16;             // [CDM_CH * 8][COUT] of this round
+    unsigned char* w_s = smem + CDM_CH * CD_TM * 16;             // [CDM_CH * 8][COUT (+ padding)] of this round
     __shared__ int4 coord_s[CD_TM];
     __shared__ int row_s[CD_TM];
     __shared__ uint32_t block_s[8][CD_TM];
@@ -252,7 +253,7 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_mma_kernel(
     for (int o0 = 0; o0 < kvol_pad; o0 += CDM_CH) {
         // this round's weights: CDM_CH * 8 rows of COUT
         for (int idx = tid; idx < CDM_CH * COUT; idx += CD_THREADS)
-            cp_async16(ws_base + idx * 16, wt + ((size_t)o0 * 8 * COUT + (size_t)idx * 8));
+            cp_async16(ws_base + (idx / NT) * WROW + (idx % NT) * 16, wt + ((size_t)o0 * 8 * COUT + (size_t)idx * 8));
         cp_async_commit();
         // neighbour rows from the cell tables, then their features; all independent
         uint32_t j[CDM_CH * CD_TM / CD_THREADS];
@@ -311,7 +312,7 @@ __global__ void __launch_bounds__(CD_THREADS) conv_direct_mma_kernel(
                 uint32_t b[4];
                 const int mi = lane >> 3, rr = lane & 7;
                 const int kk = 16 * ks + (mi & 1) * 8 + rr, n0 = np * 16 + (mi >> 1) * 8;
-                ldmatrix_x4_trans(b, ws_base + (kk * COUT + n0) * 2);
+                ldmatrix_x4_trans(b, ws_base + kk * WROW + n0 * 2);
                 mma_bf16(acc[2 * np], a, b[0], b[1]);
                 mma_bf16(acc[2 * np + 1], a, b[2], b[3]);
             }
@@ -359,7 +360,7 @@ static int launch_conv_direct_mma(const void* feat, const int32_t* indices, cons
     const int kvol_pad = (kvol + CDM_CH - 1) / CDM_CH * CDM_CH;
     conv_direct_transpose_pad_kernel<<<(kvol_pad * 8 * cout + 255) / 256, 256, 0, stream>>>(
         (const __nv_bfloat16*)weight, (__nv_bfloat16*)wt, cout, kvol, cin, kvol_pad);
-    const size_t smem = (size_t)CDM_CH * CD_TM * 16 + (size_t)CDM_CH * 8 * cout * 2;
+    const size_t smem = (size_t)CDM_CH * CD_TM * 16 + (size_t)CDM_CH * 8 * (cout * 2 + 16);
     const unsigned blocks = (unsigned)((n + CD_TM - 1) / CD_TM);
 #define CDM_LAUNCH(NT)                                                                                      \
     do {                                                                                                    \
