@@ -355,14 +355,16 @@ def run_operator_case(args):
         order, _ = ops.argsort_inverse(codes, 28)
         qkv = torch.randn(n, 3 * C, generator=g).bfloat16().to(dev)
         pad, unpad, cu = ops.pad_plan(torch.tensor([n], device=dev), [n], K)
-        t = _time_device(lambda: ops.attention(qkv, order[0], pad, unpad, cu, H, K, 0.25), args.steps,
-                         args.warmup, flush)
+        st = ops.new_status(dev)
+        t = _time_device(lambda: ops.attention(qkv, order[0], pad, unpad, cu, H, K, 0.25, algo=args.algo, status=st),
+                         args.steps, args.warmup, flush)
         flops = 4.0 * pad.numel() * K * C
         out.update(config={"workload": "patch attention core, bf16, C=64, 4 heads, patch 1024", "points": n,
-                           "patches": cu.numel() - 1},
+                           "patches": cu.numel() - 1, "algo": args.algo},
                    metric="attention_points_per_sec", unit="points/s", value=n / (t * 1e-3), ms=t,
                    exps_per_sec=pad.numel() * K * H / (t * 1e-3),
-                   roofline={"kernel": "attn_mma_d16_kernel", "bound": "tensor", "achieved": flops / t / 1e9,
+                   roofline={"kernel": "attn_tc05_d16_kernel" if args.algo == 4 else "attn_mma_d16_kernel",
+                             "bound": "tensor", "achieved": flops / t / 1e9,
                              "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e9 / tf, "traffic": None})
     elif args.case == "conv":
         c = 128
@@ -391,6 +393,27 @@ def run_operator_case(args):
                    roofline_kmap={"kernel": "km_insert + km_probe", "bound": "hbm",
                                   "achieved": 124.0 * n / t_map / 1e6, "peak": hbm, "unit": "GB/s",
                                   "frac": 124.0 * n / t_map / 1e6 / hbm, "traffic": None})
+    elif args.case == "stem":
+        # the 5x5x5 stem convolution (6 -> 32 channels) on the forward benchmark's batch
+        data = synthetic.indoor_batch(4, target_voxels=(args.points or 400_000) // 4, grid_size=GRID,
+                                      dtype=torch.bfloat16)
+        n = int(data["offset"][-1])
+        off = [0] + data["offset"].tolist()
+        batch = torch.cat([torch.full((off[i + 1] - off[i],), i, dtype=torch.int32) for i in range(4)])
+        ind = torch.cat([batch[:, None], data["grid_coord"]], 1).contiguous().to(dev)
+        codes = ops.encode(data["grid_coord"].to(dev), batch.long().to(dev), 9, ["z"])
+        order, _ = ops.argsort_inverse(codes, 30)
+        feat = data["feat"].to(dev)
+        w = (torch.randn(32, 5, 5, 5, 6, generator=torch.Generator().manual_seed(0)) / 27.0).bfloat16().to(dev)
+        t = _time_device(lambda: ops.subm_conv_direct(feat, ind, w, None, None, None, False, order[0]), args.steps,
+                         args.warmup, flush)
+        byts = n * (6 * 2 + 16 + 32 * 2)      # features and indices in, output rows out
+        out.update(config={"workload": "stem SubMConv3d 5x5x5, 6 -> 32 channels, bf16, 4 indoor scenes",
+                           "voxels": n},
+                   metric="stem_voxels_per_sec", unit="voxels/s", value=n / (t * 1e-3), ms=t,
+                   roofline={"kernel": "conv_direct_mma_kernel (+ voxel index build)", "bound": "hbm",
+                             "achieved": byts / t / 1e6, "peak": hbm, "unit": "GB/s",
+                             "frac": byts / t / 1e6 / hbm, "traffic": None})
     elif args.case == "pooling":
         # stride-2 pooling of a 4-scene indoor batch: plan (clusters, pooled orders) and feature side
         data = synthetic.indoor_batch(4, target_voxels=(args.points or 400_000) // 4, grid_size=GRID)
@@ -454,9 +477,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--gather-outputs", action="store_true",
                     help="N > 1: all-gather the output features over NCCL inside every step")
-    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv", "mlp", "pooling"],
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv", "stem", "mlp", "pooling"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
+    ap.add_argument("--algo", type=int, default=0, help="--case attention: algo of ptv3_attention_fwd (4 = tcgen05)")
     args = ap.parse_args()
     if args.case != "forward":
         run_operator_case(args)
