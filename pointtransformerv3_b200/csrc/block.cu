@@ -103,10 +103,19 @@ static int gemm_bias_bf16(const void* x, const void* w, const void* bias, void* 
     GemmCache& gc = gemm_cache();
     int dev = 0;
     cudaGetDevice(&dev);
-    GemmPlan plan;
     {
         std::lock_guard<std::mutex> lock(gc.mu);
         if (!gc.handle) PTV3_LT(cublasLtCreate(&gc.handle));
+        // row counts change with every batch in service: keep the table bounded
+        if (gc.plans.size() >= 2048) {
+            for (auto& kv : gc.plans) {
+                if (kv.second.op) cublasLtMatmulDescDestroy(kv.second.op);
+                if (kv.second.a) cublasLtMatrixLayoutDestroy(kv.second.a);
+                if (kv.second.b) cublasLtMatrixLayoutDestroy(kv.second.b);
+                if (kv.second.c) cublasLtMatrixLayoutDestroy(kv.second.c);
+            }
+            gc.plans.clear();
+        }
         GemmPlan& p = gc.plans[std::make_tuple(dev, n, k, n_out, ws_bytes)];
         if (!p.ok) {
             const int rc = build_plan(gc.handle, n, k, n_out, ws_bytes, &p);

@@ -160,13 +160,25 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
             for (int kb = 0; kb < KB; ++kb)
                 tma_load_2d(xs0 + b * X_BYTES + kb * X_BLOCK, &map_x, kb * KCOLS, (int)(tile * 128), xbar0 + 8 * b);
         };
+        // The residual rows are read with plain loads in the middle of the epilogue; asking for
+        // them a tile ahead (L2 prefetch, no registers held) takes the DRAM latency out of the
+        // tile's serial chain.
+        auto prefetch_residual = [&](int64_t tile) {
+            const int64_t r = tile * 128 + t;
+            if (a.residual_mode && tile < ntiles && r < a.n) {
+                const char* p = reinterpret_cast<const char*>(a.residual + r * n_out);
+                for (int b = 0; b < n_out * 2; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + b));
+            }
+        };
         if (t == 0 && tile0 < ntiles) load_x(tile0, 0);
+        prefetch_residual(tile0);
         int buf = 0;
         for (int64_t tile = tile0; tile < ntiles; tile += tile_step, buf ^= 1) {
             const int64_t row0 = tile * 128;
             const uint32_t xs = xs0 + buf * X_BYTES;
             ok &= mbar_wait(xbar0 + 8 * buf, xph[buf], abort);
             xph[buf] ^= 1;
+            prefetch_residual(tile + tile_step);
             if (t == 0) {
                 // the other buffer was consumed by the previous tile's MMAs, which have completed:
                 // fetch the next tile into it while this tile is multiplied and written out
