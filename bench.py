@@ -414,6 +414,31 @@ def run_operator_case(args):
                    roofline={"kernel": "conv_direct_mma_kernel (+ voxel index build)", "bound": "hbm",
                              "achieved": byts / t / 1e6, "peak": hbm, "unit": "GB/s",
                              "frac": byts / t / 1e6 / hbm, "traffic": None})
+    elif args.case == "voxelize":
+        # raw points (about 6 per occupied voxel, as a sensor delivers them) -> one point per voxel
+        n = args.points or 2_400_000
+        g = torch.Generator().manual_seed(0)
+        coord = torch.rand(n, 3, generator=g) * torch.tensor([10.0, 10.0, 0.06])
+        offset = torch.tensor([n // 4, n // 2, 3 * n // 4, n])
+        batch = torch.repeat_interleave(torch.arange(4), torch.tensor([n // 4, n // 4, n // 4, n - 3 * (n // 4)]))
+        coord, offset, batch = coord.to(dev), offset.to(dev), batch.to(dev)
+        t_grid = _time_device(lambda: ops.grid_coord(coord, GRID), args.steps, args.warmup, flush)
+        grid, _ = ops.grid_coord(coord, GRID)
+        ind = torch.cat([batch.unsqueeze(-1).int(), grid], 1).contiguous()
+        t_dedup = _time_device(lambda: ops.voxel_dedup(ind, offset), args.steps, args.warmup, flush)
+        m = ops.voxel_dedup(ind, offset)["m"]
+        grid_b = n * (12 + 12 + 12.0)           # coordinates read twice (minimum, then quantisation), grid written
+        dedup_b = n * (16 + 8 + 8.0)            # indices read, keep and point-to-voxel rows written
+        out.update(config={"workload": "grid coordinates + first point per voxel, 4 scenes, grid 0.02", "points": n,
+                           "voxels": m},
+                   metric="voxelize_points_per_sec", unit="points/s", value=n / ((t_grid + t_dedup) * 1e-3),
+                   grid_coord_ms=t_grid, voxel_dedup_ms=t_dedup,
+                   roofline={"kernel": "vox_min_kernel + vox_grid_kernel", "bound": "hbm",
+                             "achieved": grid_b / t_grid / 1e6, "peak": hbm, "unit": "GB/s",
+                             "frac": grid_b / t_grid / 1e6 / hbm, "traffic": None},
+                   roofline_dedup={"kernel": "km_insert + vox_first + flag scan + vox_inverse (one host read)",
+                                   "bound": "hbm", "achieved": dedup_b / t_dedup / 1e6, "peak": hbm, "unit": "GB/s",
+                                   "frac": dedup_b / t_dedup / 1e6 / hbm})
     elif args.case == "pooling":
         # stride-2 pooling of a 4-scene indoor batch: plan (clusters, pooled orders) and feature side
         data = synthetic.indoor_batch(4, target_voxels=(args.points or 400_000) // 4, grid_size=GRID)
@@ -477,7 +502,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--gather-outputs", action="store_true",
                     help="N > 1: all-gather the output features over NCCL inside every step")
-    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "attention", "conv", "stem", "mlp", "pooling"],
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "pooling"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
     ap.add_argument("--algo", type=int, default=0, help="--case attention: algo of ptv3_attention_fwd (4 = tcgen05)")

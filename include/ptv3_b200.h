@@ -390,6 +390,32 @@ int ptv3_block_supported(int channels, int heads, int hidden, int dtype);
 size_t ptv3_block_workspace_bytes(const ptv3_block_args* args);
 int ptv3_block_fwd(const ptv3_block_args* args, void* stream);
 
+/*
+ * Voxelisation front end (the step before the backbone).
+ *
+ * ptv3_grid_coord: grid_coord = trunc((coord - min over all n points) / grid_size),
+ * the derivation of model.py:88-96 / 156-158 (batch-global minimum, fp32
+ * arithmetic, truncation toward zero).
+ *   coord       n x 3 float32       origin   3 float32 (out: the minimum)
+ *   grid_coord  n x 3 int32 (out)
+ *
+ * ptv3_voxel_dedup: keeps the first point (lowest row) of every occupied voxel
+ * of every scene; kept rows stay in input order.  The reference leaves this to
+ * its data pipeline (grid sampling); its submanifold convolutions assume it.
+ *   indices      n x 4 int32 rows (scene, x, y, z), 16-byte aligned; scenes contiguous
+ *   offset       n_scenes int64 cumulative point counts (may be NULL with n_scenes 0)
+ *   keep         n int64 (out): rows kept, ascending; the first *count are valid
+ *   point2voxel  n int64 (out): position in `keep` of the point's voxel
+ *   new_offset   n_scenes int64 (out, optional): cumulative kept counts
+ *   count        1 int64 (out): number of voxels
+ */
+int ptv3_grid_coord(const float* coord, int64_t n, float grid_size, float* origin, int32_t* grid_coord,
+                    void* stream);
+size_t ptv3_voxel_dedup_workspace_bytes(int64_t n);
+int ptv3_voxel_dedup(const int32_t* indices, int64_t n, const int64_t* offset, int n_scenes, int64_t* keep,
+                     int64_t* point2voxel, int64_t* new_offset, int64_t* count, uint32_t* status,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -37,6 +37,32 @@ def batch_to_offset(batch):
 # --------------------------------------------------------------------------- #
 # model.py:81-136  Point.serialization
 # --------------------------------------------------------------------------- #
+def grid_coord_from_coord(coord, grid_size):
+    """model.py:94-96 (and 156-158): grid_coord = trunc((coord - coord.min(0)) / grid_size).int(),
+    the minimum taken over the whole batch."""
+    coord = coord.to(torch.float32)
+    return torch.div(coord - coord.min(0)[0], grid_size, rounding_mode="trunc").int()
+
+
+def voxel_dedup(batch, grid_coord, offset=None):
+    """First point of every occupied (scene, voxel), kept in input order; returns
+    (keep (M,), point2voxel (N,), new_offset or None).  The reference leaves this step to
+    its data pipeline; this is the definition the CUDA front end is held to."""
+    import numpy as np
+    b = batch.numpy().astype(np.int64)
+    g = grid_coord.numpy().astype(np.int64)
+    key = (b << 48) | (g[:, 0] << 32) | (g[:, 1] << 16) | g[:, 2]
+    _, first, inverse = np.unique(key, return_index=True, return_inverse=True)
+    keep = np.sort(first)
+    rank = np.empty(key.shape[0], dtype=np.int64)
+    rank[keep] = np.arange(keep.shape[0])
+    point2voxel = rank[first[inverse.reshape(-1)]]
+    new_offset = None
+    if offset is not None:
+        new_offset = torch.from_numpy(np.searchsorted(keep, offset.numpy(), side="left").astype(np.int64))
+    return torch.from_numpy(keep), torch.from_numpy(point2voxel), new_offset
+
+
 def adaptive_depth(grid_coord):
     """model.py:98-101."""
     return int(grid_coord.max()).bit_length()

@@ -515,3 +515,49 @@ def block(args, conv_in, feat, geometry, attention, status):
     with timed("block", 2.0 * n * (27 * C * C + 4 * C * C + 2 * C * H)):
         _lib.check(lib.ptv3_block_fwd(ctypes.byref(args), _lib.stream()), "ptv3_block_fwd")
     return out
+
+
+def grid_coord(coord, grid_size):
+    """coord (N, 3) float32 -> (grid_coord (N, 3) int32, origin (3,) float32):
+    trunc((coord - coord.min(0)) / grid_size), model.py:94-96."""
+    _lib.require_cuda(coord)
+    lib = _lib.load()
+    coord = coord.to(torch.float32).contiguous()
+    n = coord.shape[0]
+    grid = torch.empty((n, 3), dtype=torch.int32, device=coord.device)
+    origin = torch.empty(3, dtype=torch.float32, device=coord.device)
+    with timed("grid_coord", 36.0 * n):
+        _lib.check(lib.ptv3_grid_coord(_lib.ptr(coord), n, float(grid_size), _lib.ptr(origin), _lib.ptr(grid),
+                                       _lib.stream()), "ptv3_grid_coord")
+    return grid, origin
+
+
+def voxel_dedup(indices, offset=None, status=None):
+    """indices (N, 4) int32 rows (scene, x, y, z) -> dict(keep (M,), point2voxel (N,),
+    offset (scenes,) or None, m): the first point of every occupied voxel.  One host
+    read (the number of voxels)."""
+    _lib.require_cuda(indices, offset)
+    lib = _lib.load()
+    indices = indices.to(torch.int32).contiguous()
+    n = indices.shape[0]
+    dev = indices.device
+    keep = torch.empty(n, dtype=torch.int64, device=dev)
+    p2v = torch.empty(n, dtype=torch.int64, device=dev)
+    n_scenes = 0 if offset is None else offset.numel()
+    off_in = None if offset is None else offset.to(torch.int64).contiguous()
+    new_offset = None if offset is None else torch.empty(n_scenes, dtype=torch.int64, device=dev)
+    count = torch.zeros(1, dtype=torch.int64, device=dev)
+    own = status is None
+    if own:
+        status = new_status(dev)
+    nbytes = lib.ptv3_voxel_dedup_workspace_bytes(n)
+    ws = _lib.workspace(nbytes, dev)
+    with timed("voxel_dedup", 48.0 * n):
+        _lib.check(lib.ptv3_voxel_dedup(_lib.ptr(indices), n, _lib.ptr(off_in), n_scenes, _lib.ptr(keep),
+                                        _lib.ptr(p2v), _lib.ptr(new_offset), _lib.ptr(count), _lib.ptr(status),
+                                        _lib.ptr(ws), nbytes, _lib.stream()), "ptv3_voxel_dedup")
+    host = torch.cat([count, status.to(torch.int64)]).tolist()      # the one sync
+    if own and host[1]:
+        raise _lib.Ptv3Error("ptv3_voxel_dedup: device status 0x%x" % host[1])
+    m = host[0]
+    return dict(keep=keep[:m], point2voxel=p2v, offset=new_offset, m=m)

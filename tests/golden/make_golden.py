@@ -2,7 +2,7 @@
 (serialization package imported directly; model.py imported through the
 stand-in packages of oracle/refshim).  Run where the reference tree exists:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [serialization attention pooling backbone voxelize]
 
 Inputs come from seeded generators (tests/helpers.py) and parameters from the
 name-keyed fill of oracle/weights.py, so only outputs are stored."""
@@ -147,14 +147,39 @@ def gen_backbone(model):
     np.savez_compressed(os.path.join(HERE, "backbone.npz"), **out)
 
 
+def voxelize_inputs():
+    """Seeded coordinates of two scenes (some negative, some sharing a voxel)."""
+    rng = np.random.default_rng(51)
+    coord = (rng.random((4000, 3)) * np.array([6.0, 5.0, 2.5]) - np.array([1.5, 0.0, 0.7])).astype(np.float32)
+    coord[100:200] = coord[0:100] + np.float32(1e-4)           # near-duplicates: same voxel mostly
+    offset = np.array([2600, 4000], dtype=np.int64)
+    return coord, offset, 0.05
+
+
+def gen_voxelize(model):
+    # grid coordinates as Point derives them when only `coord` and `grid_size` are given (model.py:88-96)
+    coord, offset, grid_size = voxelize_inputs()
+    pt = model.Point({"coord": torch.from_numpy(coord), "offset": torch.from_numpy(offset),
+                      "grid_size": grid_size, "feat": torch.zeros(coord.shape[0], 1)})
+    pt.serialization(order=["z"])
+    np.savez_compressed(os.path.join(HERE, "voxelize.npz"), grid_coord=pt.grid_coord.numpy().astype(np.int32))
+
+
 def main():
     ser = refload.load_serialization()
     model = refload.load_model()
     assert ser is not None and model is not None, "the reference tree is required"
-    gen_serialization(ser, model)
-    gen_attention(model)
-    gen_pooling(model)
-    gen_backbone(model)
+    only = set(sys.argv[1:])
+    if not only or "serialization" in only:
+        gen_serialization(ser, model)
+    if not only or "attention" in only:
+        gen_attention(model)
+    if not only or "pooling" in only:
+        gen_pooling(model)
+    if not only or "backbone" in only:
+        gen_backbone(model)
+    if not only or "voxelize" in only:
+        gen_voxelize(model)
     for f in sorted(os.listdir(HERE)):
         if f.endswith(".npz"):
             print(f, os.path.getsize(os.path.join(HERE, f)) // 1024, "KiB")

@@ -215,3 +215,28 @@ def test_backbone_vs_reference_live():
         torch.manual_seed(3)
         got = O.ptv3_forward(sd, data, SMALL_CFG)
     assert (ref - got).abs().max() < 1e-5
+
+
+def _voxelize_inputs():
+    """The seeded input generator stored beside the fixture (tests/golden/make_golden.py)."""
+    src = open(os.path.join(GOLDEN, "make_golden.py")).read()
+    ns = {}
+    exec("import numpy as np\n" + src[src.index("def voxelize_inputs():"):src.index("def gen_voxelize(model):")], ns)
+    return ns["voxelize_inputs"]()
+
+
+def test_grid_coord_golden():
+    """grid_coord derivation (model.py:94-96) against the reference's own Point."""
+    coord, offset, grid_size = _voxelize_inputs()
+    got = O.grid_coord_from_coord(torch.from_numpy(coord), grid_size)
+    assert np.array_equal(got.numpy(), load("voxelize.npz")["grid_coord"])
+
+
+def test_voxel_dedup_definition():
+    """The oracle's dedup keeps exactly one point per (scene, voxel), the first one, in order."""
+    g = torch.tensor([[0, 0, 0], [1, 0, 0], [0, 0, 0], [1, 0, 0], [0, 0, 0], [2, 2, 2]], dtype=torch.int32)
+    b = torch.tensor([0, 0, 0, 1, 1, 1])
+    keep, p2v, off = O.voxel_dedup(b, g, torch.tensor([3, 6]))
+    assert keep.tolist() == [0, 1, 3, 4, 5]
+    assert p2v.tolist() == [0, 1, 0, 2, 3, 4]
+    assert off.tolist() == [2, 5]

@@ -5,6 +5,7 @@ import pytest
 import torch
 
 from oracle import cenc
+from oracle import ptv3_oracle as O
 from pointtransformerv3_b200 import ops, synthetic
 
 pytestmark = pytest.mark.gpu
@@ -95,3 +96,60 @@ def test_decode_inverts_encode(depth):
         assert (grid.cpu().numpy() == g).all() and (batch.cpu().numpy() == b).all()
         og, ob = cenc.decode(code.cpu().numpy(), depth, name)
         assert (grid.cpu().numpy() == og).all() and (batch.cpu().numpy() == ob).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("n,scenes", [(1, 1), (5000, 1), (40_000, 3), (300_000, 4)])
+def test_grid_coord_and_voxel_dedup_match_oracle(n, scenes):
+    """Bit-exact: grid coordinates (model.py:94-96) and first-point-per-voxel selection."""
+    from pointtransformerv3_b200 import ops
+    g = torch.Generator().manual_seed(n)
+    coord = (torch.rand(n, 3, generator=g) * torch.tensor([8.0, 6.0, 3.0]) - torch.tensor([2.0, 0.5, 1.0]))
+    if n > 100:
+        coord[50:100] = coord[0:50]                      # exact duplicates
+    cuts = sorted(torch.randint(0, n + 1, (scenes - 1,), generator=g).tolist()) + [n]
+    offset = torch.tensor(cuts, dtype=torch.int64)       # ragged, possibly empty scenes
+    grid_size = 0.04
+    ref_grid = O.grid_coord_from_coord(coord, grid_size)
+    grid, origin = ops.grid_coord(coord.cuda(), grid_size)
+    assert torch.equal(grid.cpu(), ref_grid)
+    assert torch.equal(origin.cpu(), coord.min(0)[0])
+    batch = O.offset_to_batch(offset)
+    ind = torch.cat([batch.unsqueeze(-1).int(), ref_grid], 1).contiguous()
+    d = ops.voxel_dedup(ind.cuda(), offset.cuda())
+    keep, p2v, off = O.voxel_dedup(batch, ref_grid, offset)
+    assert d["m"] == keep.numel()
+    assert torch.equal(d["keep"].cpu(), keep)
+    assert torch.equal(d["point2voxel"].cpu(), p2v)
+    assert torch.equal(d["offset"].cpu(), off)
+    # idempotence: the kept points are already one per voxel
+    d2 = ops.voxel_dedup(ind.cuda().index_select(0, d["keep"]), d["offset"])
+    assert d2["m"] == d["m"] and torch.equal(d2["keep"].cpu(), torch.arange(d["m"]))
+
+
+@pytest.mark.gpu
+def test_voxelize_feeds_the_backbone():
+    """Raw points -> voxelize -> backbone: same features as the backbone run on the
+    oracle's selection of points."""
+    import pointtransformerv3_b200 as P
+    g = torch.Generator().manual_seed(3)
+    n = 30_000
+    coord = torch.rand(n, 3, generator=g) * torch.tensor([3.0, 3.0, 1.0])
+    feat = torch.cat([coord, torch.rand(n, 3, generator=g)], 1)
+    offset = torch.tensor([17_000, n])
+    data, p2v = P.voxelize(coord.cuda(), feat.cuda(), offset.cuda(), 0.02)
+    ref_grid = O.grid_coord_from_coord(coord, 0.02)
+    keep, ref_p2v, ref_off = O.voxel_dedup(O.offset_to_batch(offset), ref_grid, offset)
+    assert torch.equal(data["grid_coord"].cpu(), ref_grid[keep]) and torch.equal(data["offset"].cpu(), ref_off)
+    assert torch.equal(p2v.cpu(), ref_p2v)
+    torch.manual_seed(0)
+    net = P.PointTransformerV3(in_channels=6, enc_depths=(1, 1, 1, 1, 1), dec_depths=(1, 1, 1, 1)).eval().cuda()
+    with torch.inference_mode():
+        torch.manual_seed(1)
+        a = net(dict(data)).feat
+        torch.manual_seed(1)
+        b = net({"coord": coord[keep].cuda(), "grid_coord": ref_grid[keep].cuda(), "feat": feat[keep].cuda(),
+                 "offset": ref_off.cuda(), "grid_size": 0.02}).feat
+    assert torch.equal(a, b)
+    # per-point results: scatter the voxel features back
+    assert a[p2v].shape == (n, a.shape[1])
