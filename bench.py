@@ -439,6 +439,20 @@ def run_operator_case(args):
                    roofline_dedup={"kernel": "km_insert + vox_first + flag scan + vox_inverse (one host read)",
                                    "bound": "hbm", "achieved": dedup_b / t_dedup / 1e6, "peak": hbm, "unit": "GB/s",
                                    "frac": dedup_b / t_dedup / 1e6 / hbm})
+    elif args.case == "seghead":
+        n, c, k = args.points or 407_000, 64, 20
+        g = torch.Generator().manual_seed(0)
+        feat = torch.randn(n, c, generator=g).bfloat16().to(dev)
+        w = (torch.randn(k, c, generator=g) / 8).bfloat16().to(dev)
+        b = torch.zeros(k).bfloat16().to(dev)
+        t = _time_device(lambda: ops.seg_head(feat, w, b, want_logits=False), args.steps, args.warmup, flush)
+        t_full = _time_device(lambda: ops.seg_head(feat, w, b), args.steps, args.warmup, flush)
+        byts = n * (c * 2 + 8.0)                # feature rows read, labels written
+        out.update(config={"workload": "segmentation head, 64 -> 20 classes + arg max, bf16", "points": n},
+                   metric="seg_head_points_per_sec", unit="points/s", value=n / (t * 1e-3), ms=t,
+                   with_logits_ms=t_full,
+                   roofline={"kernel": "seg_head_kernel (labels only)", "bound": "hbm", "achieved": byts / t / 1e6,
+                             "peak": hbm, "unit": "GB/s", "frac": byts / t / 1e6 / hbm, "traffic": None})
     elif args.case == "pooling":
         # stride-2 pooling of a 4-scene indoor batch: plan (clusters, pooled orders) and feature side
         data = synthetic.indoor_batch(4, target_voxels=(args.points or 400_000) // 4, grid_size=GRID)
@@ -502,7 +516,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--gather-outputs", action="store_true",
                     help="N > 1: all-gather the output features over NCCL inside every step")
-    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "pooling"],
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "pooling", "seghead"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
     ap.add_argument("--algo", type=int, default=0, help="--case attention: algo of ptv3_attention_fwd (4 = tcgen05)")

@@ -416,6 +416,18 @@ int ptv3_voxel_dedup(const int32_t* indices, int64_t n, const int64_t* offset, i
                      int64_t* point2voxel, int64_t* new_offset, int64_t* count, uint32_t* status,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * Segmentation head (the step after the backbone; the reference file ends with the
+ * backbone, model.py:966-982, and the head is the segmentor's Linear on
+ * dec_channels[0]): logits = feat W^T + b and/or the per-point arg max in one pass.
+ *   feat     n x channels (16-byte aligned rows)     weight  classes x channels, bias classes or NULL
+ *   logits   n x classes in the feature dtype, or NULL
+ *   labels   n int64 arg max of the (rounded) logits, lowest index on ties, or NULL
+ * classes <= 64; channels a multiple of 4 (fp32) / 8 (bf16), up to 512.
+ */
+int ptv3_seg_head_fwd(const void* feat, const void* weight, const void* bias, void* logits, int64_t* labels,
+                      int64_t n, int channels, int classes, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -4,9 +4,9 @@ from .point import Point, batch2offset, offset2batch, offset2bincount
 from .sparse import SparseConvTensor, SubMConv3d
 from .voxelize import voxelize
 from .model import (Block, Embedding, GridPooling, GridUnpooling, MLP, PDNorm, PointModule, PointSequential, RPE,
-                    PointTransformerV3, SerializedAttention, SerializedPooling, SerializedUnpooling)
+                    PointTransformerV3, SegHead, SerializedAttention, SerializedPooling, SerializedUnpooling)
 
 __all__ = ["serialization", "Point", "batch2offset", "offset2batch", "offset2bincount", "SparseConvTensor",
            "SubMConv3d", "Block", "Embedding", "GridPooling", "GridUnpooling", "MLP", "PDNorm", "PointModule", "RPE",
            "PointSequential", "PointTransformerV3", "SerializedAttention", "SerializedPooling",
-           "SerializedUnpooling", "voxelize"]
+           "SerializedUnpooling", "SegHead", "voxelize"]

@@ -800,6 +800,35 @@ class PointTransformerV3(PointModule):
         return point
 
 
+class SegHead(PointModule):
+    """Per-point classifier on the backbone's output: ``Linear(in_channels,
+    num_classes)`` (state_dict keys ``weight`` / ``bias`` like the ``seg_head`` of a
+    segmentor around the reference backbone) with the arg max taken in the same pass.
+    ``forward(point)`` stores ``seg_logits`` (unless ``logits=False``) and ``seg_pred``."""
+
+    def __init__(self, in_channels, num_classes, logits=True):
+        super().__init__()
+        self.linear = nn.Linear(in_channels, num_classes)
+        self.logits = logits
+
+    def _load_from_state_dict(self, state_dict, prefix, *args, **kwargs):
+        # accept the flat keys of a plain nn.Linear head
+        for k in ("weight", "bias"):
+            if prefix + k in state_dict and prefix + "linear." + k not in state_dict:
+                state_dict[prefix + "linear." + k] = state_dict.pop(prefix + k)
+        super()._load_from_state_dict(state_dict, prefix, *args, **kwargs)
+
+    def forward(self, point):
+        feat = point.feat if isinstance(point, Point) else point
+        logits, labels = ops.seg_head(feat, self.linear.weight, self.linear.bias, want_logits=self.logits)
+        if not isinstance(point, Point):
+            return logits, labels
+        if logits is not None:
+            point["seg_logits"] = logits
+        point["seg_pred"] = labels
+        return point
+
+
 def _record_stream(obj, stream):
     """tensor.record_stream(stream) for every CUDA tensor reachable through dicts,
     lists and tuples of ``obj``."""

@@ -561,3 +561,20 @@ def voxel_dedup(indices, offset=None, status=None):
         raise _lib.Ptv3Error("ptv3_voxel_dedup: device status 0x%x" % host[1])
     m = host[0]
     return dict(keep=keep[:m], point2voxel=p2v, offset=new_offset, m=m)
+
+
+def seg_head(feat, weight, bias=None, want_logits=True, want_labels=True):
+    """feat (N, C), weight (K, C) -> (logits (N, K) or None, labels (N,) int64 or None)."""
+    _lib.require_cuda(feat, weight, bias)
+    lib = _lib.load()
+    feat = feat.contiguous()
+    n, C = feat.shape
+    K = weight.shape[0]
+    logits = torch.empty((n, K), dtype=feat.dtype, device=feat.device) if want_logits else None
+    labels = torch.empty(n, dtype=torch.int64, device=feat.device) if want_labels else None
+    with timed("seg_head", 2.0 * n * C * K):
+        _lib.check(lib.ptv3_seg_head_fwd(_lib.ptr(feat), _lib.ptr(weight.to(feat.dtype).contiguous()),
+                                         _lib.ptr(None if bias is None else bias.to(feat.dtype).contiguous()),
+                                         _lib.ptr(logits), _lib.ptr(labels), n, C, K, _lib.dtype_id(feat),
+                                         _lib.stream()), "ptv3_seg_head_fwd")
+    return logits, labels

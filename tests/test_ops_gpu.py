@@ -449,3 +449,25 @@ def test_pool_reduce_modes(reduce):
     ref = O.segment_reduce(x[plan["indices"]], plan["idx_ptr"], reduce)
     got, _ = ops.pool(x.cuda(), None, order[0].cuda(), plan["idx_ptr"].cuda(), None, None, reduce)
     assert_close(got, ref, atol=1e-5, rtol=1e-5, what="pool " + reduce)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,C,K", [(1, 64, 13), (5000, 64, 20), (70_000, 64, 13), (3000, 32, 40), (2000, 128, 64)])
+def test_seg_head_matches_torch(n, C, K, dtype):
+    """Linear + arg max in one pass against F.linear / argmax (fp32 accumulation on both
+    sides; labels must agree wherever the two best logits are not within rounding)."""
+    g = torch.Generator().manual_seed(n + K)
+    feat = torch.randn(n, C, generator=g).to(dtype)
+    w = (torch.randn(K, C, generator=g) / C ** 0.5).to(dtype)
+    b = (torch.randn(K, generator=g) * 0.1).to(dtype)
+    ref = F.linear(feat.float(), w.float(), b.float())
+    logits, labels = ops.seg_head(feat.cuda(), w.cuda(), b.cuda())
+    assert logits.dtype == dtype and labels.dtype == torch.int64
+    assert_close(logits, ref.to(dtype), what="seg head logits", **TOL[dtype])
+    # arg max of exactly what was returned, lowest index on ties
+    assert torch.equal(labels.cpu(), logits.float().cpu().argmax(1))
+    top2 = ref.topk(2, dim=1).values
+    clear = (top2[:, 0] - top2[:, 1]) > (1e-4 if dtype == torch.float32 else 5e-2)
+    assert torch.equal(labels.cpu()[clear], ref.argmax(1)[clear])
+    only_labels = ops.seg_head(feat.cuda(), w.cuda(), b.cuda(), want_logits=False)
+    assert only_labels[0] is None and torch.equal(only_labels[1], labels)
