@@ -622,6 +622,8 @@ class PointTransformerV3(PointModule):
         self.cls_mode = cls_mode
         # how many stages ahead of the features the pooling plans are made (see forward)
         self.plan_ahead = 2
+        # True: forward() leaves the device status word unread (see forward)
+        self.defer_status_check = False
         self.shuffle_orders = shuffle_orders
         assert self.num_stages == len(stride) + 1
         assert self.num_stages == len(enc_depths)
@@ -704,11 +706,23 @@ class PointTransformerV3(PointModule):
         """data_dict: ``feat``, ``grid_coord`` (or ``coord`` + ``grid_size``) and
         ``offset`` or ``batch``; returns the Point of the finest level.
 
-        Extension: an optional ``serialization_depth`` entry fixes the depth of
-        the codes instead of deriving it from this batch's largest coordinate
-        (needed when one logical batch is split over several processes)."""
+        Extensions, all optional.  ``serialization_depth`` fixes the depth of the
+        codes instead of deriving it from this batch's largest coordinate (needed
+        when one logical batch is split over several processes).  ``offset_host``
+        (the cumulative scene sizes as a Python list or CPU tensor) together with
+        ``sparse_shape`` and ``serialization_depth`` lets a caller that knows these
+        on the host skip the one device read at the start of the pass.  With
+        ``self.defer_status_check = True`` the device status word is not read at
+        the end either; the caller checks ``point.check_status(force=True)`` when
+        it next needs the host to wait.  (On the benchmark batch neither changes
+        the throughput of back-to-back passes: measured 9.8 ms per step against
+        9.5-9.7 with the two host waits in place.)"""
         point = Point(data_dict)
         depth = point.pop("serialization_depth", None)
+        host_offset = point.pop("offset_host", None)
+        if host_offset is not None and "_counts" not in point.keys():
+            off = [0] + [int(v) for v in (host_offset.tolist() if hasattr(host_offset, "tolist") else host_offset)]
+            point["_counts"] = [off[i + 1] - off[i] for i in range(len(off) - 1)]
         status = point.device_status()
         point["_defer_status"] = True
         # -- planning phase: everything whose size depends on the data, so that all
@@ -796,7 +810,8 @@ class PointTransformerV3(PointModule):
         if not self.cls_mode:
             point = self.dec(point)
         point["_defer_status"] = False
-        _lib.raise_on_status(status, "PointTransformerV3.forward")
+        if not self.defer_status_check:
+            _lib.raise_on_status(status, "PointTransformerV3.forward")
         return point
 
 

@@ -385,3 +385,26 @@ def test_block_single_call_matches_per_operator_path(channels, heads, n_per_scen
     a, b = run(True), run(False)
     assert bool(torch.isfinite(b.float()).all())
     assert rel_l2(b, a) < 4e-3, rel_l2(b, a)
+
+
+@pytest.mark.gpu
+def test_forward_with_host_metadata_and_deferred_status():
+    """The optional entries that let a caller skip the host waits of a pass (scene sizes,
+    code depth and sparse shape known on the host; status word read later) do not change
+    the result."""
+    data = small_batch([3000, 1800], 33)
+    torch.manual_seed(0)
+    net = P.PointTransformerV3(in_channels=6, enc_depths=(1, 1, 1, 1, 1), dec_depths=(1, 1, 1, 1)).eval().cuda()
+    dev = {k: v.cuda() for k, v in data.items()}
+    with torch.inference_mode():
+        torch.manual_seed(1)
+        ref = net(dict(dev)).feat
+        mx = data["grid_coord"].max(0).values.tolist()
+        meta = {"offset_host": data["offset"].tolist(), "serialization_depth": max(mx).bit_length(),
+                "sparse_shape": [v + 96 for v in mx]}
+        net.defer_status_check = True
+        torch.manual_seed(1)
+        point = net(dict(dev, **meta))
+        point.check_status("deferred", force=True)
+        net.defer_status_check = False
+    assert torch.equal(point.feat, ref)
