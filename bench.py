@@ -151,6 +151,16 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+        # One launching thread per rank: give every rank its own slice of the host cores, so that
+        # the ranks' Python threads and the driver's helper threads do not migrate onto each other
+        # (the path is host-paced on its coarse levels, and 8 ranks share one host).
+        try:
+            cores = sorted(os.sched_getaffinity(0))
+            per = len(cores) // world
+            if per >= 1:
+                os.sched_setaffinity(0, set(cores[local * per:(local + 1) * per]))
+        except (AttributeError, OSError):
+            pass
     lib = _lib.load()
     gather = world > 1 and args.gather_outputs
 
