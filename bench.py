@@ -300,14 +300,16 @@ def run_ours(args):
         att = timers.get("attention", {"calls": 0, "ms": 0.0, "work": 0.0})
         tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
         achieved = att["work"] / (att["ms"] * 1e-3) / 1e12 if att["ms"] else 0.0
-        # DRAM bytes per launch: the ncu capture of one launch on the C = 64, 120 832-row case reads and
-        # writes 56.1 MB, i.e. 7.25 B per padded row and channel; traffic grows in proportion to
-        # rows x channels, which is the work figure / (4 x patch)
-        traffic = 7.25 * att["work"] / (4.0 * 1024.0) / max(att["calls"], 1)
+        # DRAM bytes per launch: the ncu capture of one launch on 240 640 padded rows x 64 channels
+        # (qkv of 92 MB gathered through a random permutation, the least local case) reads 322 MB and
+        # writes 26 MB, i.e. 22.6 B per padded row and channel against 8 B algorithmic (qkv read once,
+        # output written once): a row's 32-byte pieces are fetched again by every head group and query
+        # slice that gathers them.  Traffic grows in proportion to rows x channels = work / (4 x patch).
+        traffic = 22.6 * att["work"] / (4.0 * 1024.0) / max(att["calls"], 1)
         roofline = {"kernel": "attention core (all patch-attention launches of the timed steps)",
                     "bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
                     "frac": achieved / tf_peak, "traffic": traffic,
-                    "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch",
+                    "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch (profiles/attention_tc05_240k_points.md)",
                     "peak_source": "measured (sustained)" if peaks else "fallback",
                     "launches": att["calls"], "avg_launch_ms": att["ms"] / max(att["calls"], 1)}
         breakdown = {k: {"calls": v["calls"], "ms_per_step": v["ms"] / args.steps} for k, v in all_timers.items()}
