@@ -53,7 +53,9 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     unsigned char* Ks = smem;
     unsigned char* Vs = smem + (size_t)lpad_max * 32;
 
-    const int seq = blockIdx.x, h = blockIdx.y;
+    // heads vary fastest over the grid: the CTAs of one patch run together, so the rows they all
+    // gather from (a row holds every head's q, k and v side by side) are fetched from DRAM once
+    const int seq = blockIdx.y, h = blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t start = cu_seqlens[seq];
     const int L = (int)(cu_seqlens[seq + 1] - start);
@@ -248,7 +250,7 @@ int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, c
     const int tiles = (max_seqlen + 15) / 16;
     // three CTAs fit on an SM; aim at several waves so that the last one costs little
     while (pairs * qsplit < 4 * 3 * 148 && qsplit * 2 * AM_WARPS <= tiles) qsplit *= 2;
-    const dim3 grid(n_seq, H, qsplit);
+    const dim3 grid(H, n_seq, qsplit);
     kern<<<grid, AM_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad);
     count_launches(1);

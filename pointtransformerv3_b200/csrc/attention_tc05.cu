@@ -126,7 +126,9 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
     const AtLayout lay(lpad_max);
     const uint32_t sbase = smem_u32_generic(smem);
 
-    const int seq = blockIdx.x, h = blockIdx.y;
+    // heads vary fastest over the grid: the CTAs of one patch run together, so the rows they all
+    // gather from (a row holds every head's q, k and v side by side) are fetched from DRAM once
+    const int seq = blockIdx.y, h = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
     const int start = cu_seqlens[seq];
     const int L = cu_seqlens[seq + 1] - start;
@@ -454,7 +456,7 @@ int launch_attn_tc05(const void* qkv, const int64_t* order, const int64_t* pad, 
             qsplit = q;
         }
     }
-    const dim3 grid(n_seq, H, qsplit);
+    const dim3 grid(H, n_seq, qsplit);
     attn_tc05_d16_kernel<<<grid, AT_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad, status);
     count_launches(1);
