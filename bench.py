@@ -301,11 +301,10 @@ def run_ours(args):
         tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
         achieved = att["work"] / (att["ms"] * 1e-3) / 1e12 if att["ms"] else 0.0
         # DRAM bytes per launch: the ncu capture of one launch on 240 640 padded rows x 64 channels
-        # (qkv of 92 MB gathered through a random permutation, the least local case) reads 322 MB and
-        # writes 26 MB, i.e. 22.6 B per padded row and channel against 8 B algorithmic (qkv read once,
-        # output written once): a row's 32-byte pieces are fetched again by every head group and query
-        # slice that gathers them.  Traffic grows in proportion to rows x channels = work / (4 x patch).
-        traffic = 22.6 * att["work"] / (4.0 * 1024.0) / max(att["calls"], 1)
+        # (qkv of 92 MB gathered through a random permutation, the least local case) reads 147.5 MB and
+        # writes 17.9 MB, i.e. 10.7 B per padded row and channel against 8 B algorithmic (qkv read once,
+        # output written once).  Traffic grows in proportion to rows x channels = work / (4 x patch).
+        traffic = 10.74 * att["work"] / (4.0 * 1024.0) / max(att["calls"], 1)
         roofline = {"kernel": "attention core (all patch-attention launches of the timed steps)",
                     "bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
                     "frac": achieved / tf_peak, "traffic": traffic,
