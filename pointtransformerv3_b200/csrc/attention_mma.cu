@@ -53,17 +53,20 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     unsigned char* Ks = smem;
     unsigned char* Vs = smem + (size_t)lpad_max * 32;
 
-    // heads vary fastest over the grid: the CTAs of one patch run together, so the rows they all
-    // gather from (a row holds every head's q, k and v side by side) are fetched from DRAM once
-    const int seq = blockIdx.y, h = blockIdx.x;
+    // heads and query slices vary fastest over the grid (blockIdx.x = slice * heads + head): the
+    // CTAs of one patch run together, so the rows they all gather from (a row holds every head's
+    // q, k and v side by side) are fetched from DRAM once
+    const int n_heads = C / 16;
+    const int seq = blockIdx.y, h = blockIdx.x % n_heads;
+    const int slice = blockIdx.x / n_heads, n_slices = gridDim.x / n_heads;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t start = cu_seqlens[seq];
     const int L = (int)(cu_seqlens[seq + 1] - start);
     if (L <= 0) return;
     const int Lp = (L + AM_KC - 1) / AM_KC * AM_KC;   // <= lpad_max
     const int ntiles = (L + 15) / 16;
-    const int tiles_per_slice = (ntiles + gridDim.z - 1) / gridDim.z;
-    const int tile_lo = blockIdx.z * tiles_per_slice;
+    const int tiles_per_slice = (ntiles + n_slices - 1) / n_slices;
+    const int tile_lo = slice * tiles_per_slice;
     const int tile_hi = min(ntiles, tile_lo + tiles_per_slice);
     if (tile_lo >= tile_hi) return;
     const int64_t row_stride = 3 * (int64_t)C;
@@ -250,7 +253,7 @@ int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, c
     const int tiles = (max_seqlen + 15) / 16;
     // three CTAs fit on an SM; aim at several waves so that the last one costs little
     while (pairs * qsplit < 4 * 3 * 148 && qsplit * 2 * AM_WARPS <= tiles) qsplit *= 2;
-    const dim3 grid(H, n_seq, qsplit);
+    const dim3 grid(H * qsplit, n_seq);
     kern<<<grid, AM_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad);
     count_launches(1);

@@ -126,9 +126,12 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
     const AtLayout lay(lpad_max);
     const uint32_t sbase = smem_u32_generic(smem);
 
-    // heads vary fastest over the grid: the CTAs of one patch run together, so the rows they all
-    // gather from (a row holds every head's q, k and v side by side) are fetched from DRAM once
-    const int seq = blockIdx.y, h = blockIdx.x;
+    // heads and query slices vary fastest over the grid (blockIdx.x = slice * heads + head): the
+    // CTAs of one patch run together, so the rows they all gather from (a row holds every head's
+    // q, k and v side by side) are fetched from DRAM once
+    const int n_heads = C / 16;
+    const int seq = blockIdx.y, h = blockIdx.x % n_heads;
+    const int slice = blockIdx.x / n_heads, n_slices = gridDim.x / n_heads;
     const int tid = threadIdx.x, warp = tid >> 5;
     const int start = cu_seqlens[seq];
     const int L = cu_seqlens[seq + 1] - start;
@@ -141,8 +144,8 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
     const int ntiles = (L + AT_BM - 1) / AT_BM;      // query tiles
     const int nb = (L + AT_BK - 1) / AT_BK;          // key blocks
     const int Lp = ntiles * AT_BM;                   // rows of the zero-padded K / V planes
-    const int tiles_per_slice = (ntiles + gridDim.z - 1) / gridDim.z;
-    const int tile_lo = blockIdx.z * tiles_per_slice;
+    const int tiles_per_slice = (ntiles + n_slices - 1) / n_slices;
+    const int tile_lo = slice * tiles_per_slice;
     const int tile_hi = min(ntiles, tile_lo + tiles_per_slice);
     if (tile_lo >= tile_hi) return;
     const int64_t row_stride = 3 * (int64_t)C;
@@ -456,7 +459,7 @@ int launch_attn_tc05(const void* qkv, const int64_t* order, const int64_t* pad, 
             qsplit = q;
         }
     }
-    const dim3 grid(H, n_seq, qsplit);
+    const dim3 grid(H * qsplit, n_seq);
     attn_tc05_d16_kernel<<<grid, AT_THREADS, smem, stream>>>(
         (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad, status);
     count_launches(1);
