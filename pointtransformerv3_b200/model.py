@@ -746,12 +746,22 @@ class PointTransformerV3(PointModule):
         #    level s + 2 while stage s runs), so that their host reads never wait behind, and
         #    never hold up, the feature kernels.
         main = torch.cuda.current_stream()
+        point["_sparse_indices"] = point._sparse_indices()
         serialized = torch.cuda.Event()
         serialized.record(main)
         side = self._side_stream(main.device)
         side.wait_event(serialized)
+        # the finest level's 3x3x3 kernel map is first needed after the stem: build it on the
+        # second stream while the stem (which probes its own voxel index) runs on the first
+        with torch.cuda.stream(side):
+            kmaps0 = spconv.prebuild_kernel_map(
+                point["_sparse_indices"], point.serialized_order[0], 3, status,
+                with_pairs=point.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
+        _record_stream(kmaps0, main)
+        point["_prebuilt_kmaps"] = kmaps0
+        events = {0: torch.cuda.Event()}
+        events[0].record(side)
         stages = list(self.enc._modules.values())
-        events = {}
         plan_state = {"cursor": point, "next": 0}
 
         def plan_upto(last):
