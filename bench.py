@@ -488,6 +488,29 @@ def run_operator_case(args):
                    roofline_dedup={"kernel": "km_insert + vox_first + flag scan + vox_inverse (one host read)",
                                    "bound": "hbm", "achieved": dedup_b / t_dedup / 1e6, "peak": hbm, "unit": "GB/s",
                                    "frac": dedup_b / t_dedup / 1e6 / hbm})
+    elif args.case == "linear":
+        # the two Linear forms of a block on the tcgen05 kernels: qkv projection, and
+        # Linear + LayerNorm + residual + LayerNorm (cpe.1 / cpe.2 / shortcut / norm1)
+        n, c = args.points or 407_000, 64
+        g = torch.Generator().manual_seed(0)
+        mk = lambda *shape: torch.randn(*shape, generator=g).bfloat16().to(dev)
+        x, res = mk(n, c), mk(n, c)
+        w, b, wq, bq = mk(c, c), mk(c), mk(3 * c, c), mk(3 * c)
+        ln1 = torch.nn.LayerNorm(c).to(dev).bfloat16()
+        ln2 = torch.nn.LayerNorm(c).to(dev).bfloat16()
+        st = ops.new_status(dev)
+        t_ln = _time_device(lambda: ops.linear_ln(x, w, b, res, ln1, ln2, st), args.steps, args.warmup, flush)
+        t_qkv = _time_device(lambda: ops.linear(x, wq, bq, st), args.steps, args.warmup, flush)
+        ln_b, qkv_b = 4.0 * n * c * 2, 4.0 * n * c * 2     # x + residual in, two outputs; x in, 3C out
+        out.update(config={"workload": "Linear + LN + residual + LN and the qkv Linear, C=64, bf16", "rows": n},
+                   metric="linear_rows_per_sec", unit="rows/s", value=n / ((t_ln + t_qkv) * 1e-3),
+                   linear_ln_ms=t_ln, linear_qkv_ms=t_qkv,
+                   roofline={"kernel": "linear_tc05_kernel<64> (residual mode)", "bound": "hbm",
+                             "achieved": ln_b / t_ln / 1e6, "peak": hbm, "unit": "GB/s",
+                             "frac": ln_b / t_ln / 1e6 / hbm, "traffic": None},
+                   roofline_qkv={"kernel": "linear_tc05_kernel<64> (plain mode)", "bound": "hbm",
+                                 "achieved": qkv_b / t_qkv / 1e6, "peak": hbm, "unit": "GB/s",
+                                 "frac": qkv_b / t_qkv / 1e6 / hbm})
     elif args.case == "seghead":
         n, c, k = args.points or 407_000, 64, 20
         g = torch.Generator().manual_seed(0)
@@ -565,7 +588,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--gather-outputs", action="store_true",
                     help="N > 1: all-gather the output features over NCCL inside every step")
-    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "pooling", "seghead"],
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "linear", "pooling", "seghead"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
     ap.add_argument("--algo", type=int, default=0, help="--case attention: algo of ptv3_attention_fwd (4 = tcgen05)")
