@@ -408,3 +408,34 @@ def test_forward_with_host_metadata_and_deferred_status():
         point.check_status("deferred", force=True)
         net.defer_status_check = False
     assert torch.equal(point.feat, ref)
+
+
+@pytest.mark.gpu
+def test_repeated_passes_over_changing_batches_are_bit_identical():
+    """Batches of different shapes interleaved and repeated: with the atomic pair-list
+    convolution switched off every kernel is deterministic, so any difference between
+    repeats would be a hazard between the planning stream, the feature stream and the
+    allocator (plans are made two stages ahead on a second stream)."""
+    from pointtransformerv3_b200 import sparse
+    torch.manual_seed(0)
+    net = P.PointTransformerV3(in_channels=6).eval().cuda().bfloat16()
+    batches = []
+    for i, sizes in enumerate(([900], [4000, 2500, 700], [12000, 300], [150, 150, 150, 150, 9000])):
+        d = small_batch(sizes, 50 + i)
+        d["feat"] = d["feat"].bfloat16()
+        batches.append({k: v.cuda() for k, v in d.items()})
+
+    def run(d):
+        with torch.inference_mode():
+            torch.manual_seed(1)
+            return net(dict(d)).feat
+
+    keep = sparse.PAIR_PATH_MAX_VOXELS
+    sparse.PAIR_PATH_MAX_VOXELS = 0
+    try:
+        first = [run(d).clone() for d in batches]
+        for order in ([3, 0, 2, 1], [1, 1, 3, 0], [2, 3, 0, 2]):
+            for i in order:
+                assert torch.equal(run(batches[i]), first[i]), "batch %d differs between repeats" % i
+    finally:
+        sparse.PAIR_PATH_MAX_VOXELS = keep
