@@ -256,7 +256,10 @@ int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indices, const vo
  *               values (= pooling_inverse)
  *   idx_ptr     n + 1 int64 (m + 1 used): run starts of the clusters in order[0]
  *   head        n int64 (m used): one member point of every cluster
- *   pooled_*    outputs sized for m = n, row stride n for the k-row tensors
+ *   pooled_*    outputs sized for m = n; the k-row tensors (code, order, inverse)
+ *               are written packed, k x m with row stride m, at the start of
+ *               their k x n buffers, so that a view of the first k * m
+ *               elements is the contiguous result
  *   meta        1 + n_scenes int64: m, then the number of clusters per scene
  */
 size_t ptv3_pool_plan_workspace_bytes(int k, int64_t n, int n_scenes);

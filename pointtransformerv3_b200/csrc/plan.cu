@@ -94,10 +94,10 @@ struct ClusterSink {
     int64_t* cluster;       // n
     int64_t* idx_ptr;       // cap + 1
     int64_t* head;          // cap
-    int64_t* pcode;         // k x cap (row stride cap)
+    int64_t* pcode;         // k x m, packed: the row stride is the cluster count, read from `total`
     int32_t* pgrid;         // cap x 3
     int64_t* pbatch;        // cap
-    int64_t cap;
+    const uint32_t* total;  // number of clusters (written by the scan of the tile sums)
     unsigned long long* scene_count;  // B
     __device__ void operator()(int, int64_t j, uint32_t pos, bool f) const
     {
@@ -108,7 +108,7 @@ struct ClusterSink {
             idx_ptr[cid] = j;
             head[cid] = p;
             for (int r = 0; r < k; ++r)
-                pcode[(int64_t)r * cap + cid] = code[(int64_t)perm.src[r] * n + p] >> shift;
+                pcode[(int64_t)r * (int64_t)*total + cid] = code[(int64_t)perm.src[r] * n + p] >> shift;
             pgrid[3 * cid + 0] = grid[3 * p + 0] >> pooling_depth;
             pgrid[3 * cid + 1] = grid[3 * p + 1] >> pooling_depth;
             pgrid[3 * cid + 2] = grid[3 * p + 2] >> pooling_depth;
@@ -136,16 +136,18 @@ struct OrderFlag {
 struct OrderSink {
     const int64_t* order;
     const int64_t* cluster;
-    int64_t n, cap;
+    int64_t n;
+    const uint32_t* total;   // number of clusters = row stride of the packed outputs
     RowPerm perm;
-    int64_t* porder;    // k x cap
-    int64_t* pinverse;  // k x cap
+    int64_t* porder;    // k x m, packed
+    int64_t* pinverse;  // k x m, packed
     __device__ void operator()(int r, int64_t j, uint32_t pos, bool f) const
     {
         if (!f) return;
         const int64_t c = cluster[order[(int64_t)perm.src[r] * n + j]];
-        porder[(int64_t)r * cap + pos] = c;
-        pinverse[(int64_t)r * cap + c] = pos;
+        const int64_t m = (int64_t)*total;
+        porder[(int64_t)r * m + pos] = c;
+        pinverse[(int64_t)r * m + c] = pos;
     }
 };
 
@@ -246,14 +248,14 @@ extern "C" int ptv3_pool_plan(const int64_t* code, const int64_t* order, const i
     // clusters along row 0 of the caller's (already shuffled) rows
     ClusterFlag cf{code, order, shift};
     ClusterSink cs{code, order, grid_coord, batch, n, k, shift, pooling_depth, perm, cluster, idx_ptr,
-                   head, pooled_code, pooled_grid_coord, pooled_batch, n, scene_count};
+                   head, pooled_code, pooled_grid_coord, pooled_batch, totals, scene_count};
     scan_tile_sums_kernel<<<dim3(w.ntiles, 1), SC_THREADS, 0, stream>>>(cf, n, w.ntiles, tile_sums);
     scan_sums_kernel<<<1, SC_THREADS, 0, stream>>>(tile_sums, w.ntiles, totals);
     scan_apply_kernel<<<dim3(w.ntiles, 1), SC_THREADS, 0, stream>>>(cf, cs, n, w.ntiles, tile_sums);
     // pooled orders of the k (permuted) rows
     uint32_t* ts2 = tile_sums + w.ntiles;
     OrderFlag of{order, cluster, n, perm};
-    OrderSink os{order, cluster, n, n, perm, pooled_order, pooled_inverse};
+    OrderSink os{order, cluster, n, totals, perm, pooled_order, pooled_inverse};
     scan_tile_sums_kernel<<<dim3(w.ntiles, k), SC_THREADS, 0, stream>>>(of, n, w.ntiles, ts2);
     scan_sums_kernel<<<k, SC_THREADS, 0, stream>>>(ts2, w.ntiles, totals + 1);
     scan_apply_kernel<<<dim3(w.ntiles, k), SC_THREADS, 0, stream>>>(of, os, n, w.ntiles, ts2);

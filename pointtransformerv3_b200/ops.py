@@ -258,14 +258,36 @@ def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=
                                   _lib.ptr(pinv), _lib.ptr(pgrid), _lib.ptr(pbatch), _lib.ptr(meta),
                                   _lib.ptr(status), _lib.ptr(ws), nbytes, _lib.stream()),
                "ptv3_pool_plan")
-    host = torch.cat([meta, status.to(torch.int64)]).tolist()     # the one sync
-    if host[-1]:
-        raise _lib.Ptv3Error("ptv3_pool_plan: device status 0x%x" % host[-1])
+    # the one sync: the cluster counts and the status word through pinned staging buffers
+    meta_host, status_host = _pinned(1 + n_scenes, torch.int64, "pool_plan.meta"), _pinned(1, torch.int32,
+                                                                                           "pool_plan.status")
+    meta_host.copy_(meta, non_blocking=True)
+    status_host.copy_(status, non_blocking=True)
+    torch.cuda.current_stream().synchronize()
+    host = meta_host.tolist()
+    if int(status_host[0]):
+        raise _lib.Ptv3Error("ptv3_pool_plan: device status 0x%x" % int(status_host[0]))
     m = host[0]
+    # the k-row outputs are written packed (row stride m): views, no copies
+    packed = lambda t: t.view(-1)[: k * m].view(k, m)
     return dict(cluster=cluster, idx_ptr=idx_ptr[: m + 1], head=head[:m],
-                code=pcode[:, :m].contiguous(), order=porder[:, :m].contiguous(),
-                inverse=pinv[:, :m].contiguous(), grid_coord=pgrid[:m], batch=pbatch[:m],
-                counts=host[1:-1], m=m, offset=torch.cumsum(meta[1:], 0))
+                code=packed(pcode), order=packed(porder), inverse=packed(pinv), grid_coord=pgrid[:m],
+                batch=pbatch[:m], counts=host[1:], m=m, offset=torch.cumsum(meta[1:], 0))
+
+
+_PINNED = {}
+
+
+def _pinned(numel, dtype, tag):
+    """A cached pinned host buffer (the callers synchronise before reading it and do not
+    overlap, so one per call site is enough)."""
+    key = (tag, numel, dtype)
+    buf = _PINNED.get(key)
+    if buf is None:
+        with torch.inference_mode(False):      # a plain tensor: it is written in and out of inference mode
+            buf = torch.empty(numel, dtype=dtype).pin_memory()
+        _PINNED[key] = buf
+    return buf
 
 
 REDUCE_IDS = {"max": 0, "min": 1, "sum": 2, "mean": 3}
