@@ -114,7 +114,11 @@ struct ClusterSink {
             pgrid[3 * cid + 2] = grid[3 * p + 2] >> pooling_depth;
             const int64_t b = batch[p];
             pbatch[cid] = b;
-            atomicAdd(&scene_count[b], 1ull);
+            // one atomic per scene and warp instead of one per cluster: the lanes that reached
+            // this point with the same scene elect a leader (clusters of a warp mostly share it)
+            const unsigned peers = __match_any_sync(__activemask(), (unsigned long long)b);
+            if ((int)(threadIdx.x & 31) == __ffs(peers) - 1)
+                atomicAdd(&scene_count[b], (unsigned long long)__popc(peers));
         }
     }
 };
