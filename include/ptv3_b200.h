@@ -431,6 +431,27 @@ int ptv3_voxel_dedup(const int32_t* indices, int64_t n, const int64_t* offset, i
 int ptv3_seg_head_fwd(const void* feat, const void* weight, const void* bias, void* logits, int64_t* labels,
                       int64_t n, int channels, int classes, int dtype, void* stream);
 
+/*
+ * Stage transitions in one call each (bf16): the Linear projection(s) by cuBLASLt,
+ * then the kernel of ptv3_pool_fwd / ptv3_unpool_fwd with the same arguments.
+ *   ptv3_pool_stage_fwd     SerializedPooling: proj + segment reduction + BN + GELU
+ *                           (model.py:684-689, 707-710); x is n x c_in, out m x c_out
+ *   ptv3_unpool_stage_fwd   SerializedUnpooling: proj and proj_skip + BN + GELU + gather-add
+ *                           (model.py:726-735, 744-746); skip_feat n x c_skip, child_feat m x c_child
+ * Weights in nn.Linear layout (c_out x c_in), biases required.
+ */
+size_t ptv3_pool_stage_workspace_bytes(int64_t n, int c_out);
+int ptv3_pool_stage_fwd(const void* x, const void* weight, const void* bias, const float* coord,
+                        const int64_t* indices, const int64_t* idx_ptr, int64_t n, int64_t m, int c_in, int c_out,
+                        const float* bn_scale, const float* bn_shift, void* out, float* coord_out, int reduce,
+                        int dtype, void* workspace, size_t workspace_bytes, void* stream);
+size_t ptv3_unpool_stage_workspace_bytes(int64_t n, int64_t m, int c_out);
+int ptv3_unpool_stage_fwd(const void* skip_feat, const void* child_feat, const void* w_skip, const void* b_skip,
+                          const void* w_child, const void* b_child, const int64_t* cluster, int64_t n, int64_t m,
+                          int c_skip, int c_child, int c_out, const float* skip_scale, const float* skip_shift,
+                          const float* child_scale, const float* child_shift, void* out, void* skip_act, int dtype,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

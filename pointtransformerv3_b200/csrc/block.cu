@@ -269,3 +269,74 @@ extern "C" int ptv3_block_fwd(const ptv3_block_args* a, void* stream_)
 #undef STEP
     return PTV3_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Stage transitions in one call each: the projection(s) by cuBLASLt followed by the
+// pooling / unpooling kernel (model.py:684-689, 707-710 and model.py:726-735, 744-746).
+// ---------------------------------------------------------------------------
+extern "C" size_t ptv3_pool_stage_workspace_bytes(int64_t n, int c_out)
+{
+    if (n <= 0 || c_out <= 0) return 0;
+    return align_up((size_t)n * c_out * 2, 256) + BLOCK_LT_WORKSPACE;
+}
+
+extern "C" int ptv3_pool_stage_fwd(const void* x, const void* weight, const void* bias, const float* coord,
+                                   const int64_t* indices, const int64_t* idx_ptr, int64_t n, int64_t m, int c_in,
+                                   int c_out, const float* bn_scale, const float* bn_shift, void* out,
+                                   float* coord_out, int reduce, int dtype, void* workspace, size_t workspace_bytes,
+                                   void* stream)
+{
+    PTV3_REQUIRE(dtype == PTV3_DTYPE_BF16 && c_in % 8 == 0 && c_out % 8 == 0 && c_in > 0 && c_out > 0,
+                 PTV3_ERR_UNSUPPORTED, "ptv3_pool_stage_fwd: bf16 only, channel counts multiples of 8");
+    PTV3_REQUIRE(n >= 0 && m >= 0, PTV3_ERR_INVALID_ARGUMENT, "ptv3_pool_stage_fwd: bad sizes");
+    if (n == 0 || m == 0) return PTV3_OK;
+    PTV3_REQUIRE(x && weight && bias && indices && idx_ptr && out && workspace, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_pool_stage_fwd: null pointer");
+    PTV3_REQUIRE(workspace_bytes >= ptv3_pool_stage_workspace_bytes(n, c_out), PTV3_ERR_WORKSPACE,
+                 "ptv3_pool_stage_fwd: workspace too small");
+    Carver cv(workspace);
+    char* proj = cv.take<char>((size_t)n * c_out * 2);
+    char* lt = cv.take<char>(BLOCK_LT_WORKSPACE);
+    int rc = gemm_bias_bf16(x, weight, bias, proj, n, c_in, c_out, lt, BLOCK_LT_WORKSPACE, (cudaStream_t)stream);
+    if (rc != PTV3_OK) return rc;
+    return ptv3_pool_fwd(proj, coord, indices, idx_ptr, m, c_out, bn_scale, bn_shift, out, coord_out, reduce, dtype,
+                         stream);
+}
+
+extern "C" size_t ptv3_unpool_stage_workspace_bytes(int64_t n, int64_t m, int c_out)
+{
+    if (n <= 0 || m <= 0 || c_out <= 0) return 0;
+    return align_up((size_t)n * c_out * 2, 256) + align_up((size_t)m * c_out * 2, 256) + BLOCK_LT_WORKSPACE;
+}
+
+extern "C" int ptv3_unpool_stage_fwd(const void* skip_feat, const void* child_feat, const void* w_skip,
+                                     const void* b_skip, const void* w_child, const void* b_child,
+                                     const int64_t* cluster, int64_t n, int64_t m, int c_skip, int c_child,
+                                     int c_out, const float* skip_scale, const float* skip_shift,
+                                     const float* child_scale, const float* child_shift, void* out,
+                                     void* skip_act, int dtype, void* workspace, size_t workspace_bytes,
+                                     void* stream)
+{
+    PTV3_REQUIRE(dtype == PTV3_DTYPE_BF16 && c_skip % 8 == 0 && c_child % 8 == 0 && c_out % 8 == 0 && c_skip > 0 &&
+                     c_child > 0 && c_out > 0,
+                 PTV3_ERR_UNSUPPORTED, "ptv3_unpool_stage_fwd: bf16 only, channel counts multiples of 8");
+    PTV3_REQUIRE(n >= 0 && m >= 0, PTV3_ERR_INVALID_ARGUMENT, "ptv3_unpool_stage_fwd: bad sizes");
+    if (n == 0) return PTV3_OK;
+    PTV3_REQUIRE(m > 0 && skip_feat && child_feat && w_skip && b_skip && w_child && b_child && cluster && out &&
+                     workspace,
+                 PTV3_ERR_INVALID_ARGUMENT, "ptv3_unpool_stage_fwd: null pointer or empty coarse level");
+    PTV3_REQUIRE(workspace_bytes >= ptv3_unpool_stage_workspace_bytes(n, m, c_out), PTV3_ERR_WORKSPACE,
+                 "ptv3_unpool_stage_fwd: workspace too small");
+    Carver cv(workspace);
+    char* skip_lin = cv.take<char>((size_t)n * c_out * 2);
+    char* child_lin = cv.take<char>((size_t)m * c_out * 2);
+    char* lt = cv.take<char>(BLOCK_LT_WORKSPACE);
+    int rc = gemm_bias_bf16(child_feat, w_child, b_child, child_lin, m, c_child, c_out, lt, BLOCK_LT_WORKSPACE,
+                            (cudaStream_t)stream);
+    if (rc != PTV3_OK) return rc;
+    rc = gemm_bias_bf16(skip_feat, w_skip, b_skip, skip_lin, n, c_skip, c_out, lt, BLOCK_LT_WORKSPACE,
+                        (cudaStream_t)stream);
+    if (rc != PTV3_OK) return rc;
+    return ptv3_unpool_fwd(skip_lin, child_lin, cluster, n, c_out, skip_scale, skip_shift, child_scale, child_shift,
+                           out, skip_act, dtype, stream);
+}

@@ -496,8 +496,15 @@ class SerializedPooling(PointModule):
         scale = shift = None
         if fused:
             scale, shift = _bn_eval_affine(self.norm[0])
-        feat, coord = ops.pool(self.proj(point.feat), point.coord if "coord" in point.keys() else None,
-                               point.serialized_order[0], child.pop("_idx_ptr"), scale, shift, self.reduce)
+        src_coord = point.coord if "coord" in point.keys() else None
+        if _single_call_ok(point.feat, self.proj):
+            # projection and reduction queued by one C call
+            feat, coord = ops.pool_stage(point.feat, self.proj.weight, self.proj.bias, src_coord,
+                                         point.serialized_order[0], child.pop("_idx_ptr"), scale, shift,
+                                         self.reduce)
+        else:
+            feat, coord = ops.pool(self.proj(point.feat), src_coord, point.serialized_order[0],
+                                   child.pop("_idx_ptr"), scale, shift, self.reduce)
         cluster = child.pop("_cluster")
         child["feat"] = feat
         if coord is not None:
@@ -549,11 +556,19 @@ class SerializedUnpooling(PointModule):
         parent = point.pop("pooling_parent")
         inverse = point.pop("pooling_inverse")
         if self._fusable():
-            child_lin = self.proj[0](point.feat)
-            skip_lin = self.proj_skip[0](parent.feat)
             cs, cb = _bn_eval_affine(self.proj[1])
             ss, sb = _bn_eval_affine(self.proj_skip[1])
-            out, skip_act = ops.unpool(skip_lin, child_lin, inverse, ss, sb, cs, cb)
+            child_lin = None
+            if (not self.traceable and _single_call_ok(point.feat, self.proj[0])
+                    and _single_call_ok(parent.feat, self.proj_skip[0])):
+                # both projections and the gather-add queued by one C call
+                out, skip_act = ops.unpool_stage(parent.feat, point.feat, self.proj_skip[0].weight,
+                                                 self.proj_skip[0].bias, self.proj[0].weight, self.proj[0].bias,
+                                                 inverse, ss, sb, cs, cb)
+            else:
+                child_lin = self.proj[0](point.feat)
+                skip_lin = self.proj_skip[0](parent.feat)
+                out, skip_act = ops.unpool(skip_lin, child_lin, inverse, ss, sb, cs, cb)
             # the parent's sparse tensor keeps the skip branch alone: the reference
             # adds the up-sampled features to `feat` only (model.py:746), and the next
             # block's convolution reads the sparse tensor
@@ -852,6 +867,20 @@ class SegHead(PointModule):
             point["seg_logits"] = logits
         point["seg_pred"] = labels
         return point
+
+
+SINGLE_CALL_MAX_ROWS = 131072
+
+
+def _single_call_ok(feat, linear):
+    """Whether a stage transition can go through its one-call entry point: bf16 features and
+    parameters, a bias, channel counts the library GEMM takes, no per-operator timing."""
+    # (levels with many rows are GPU-bound and keep torch's GEMM call, which picks the faster
+    # library kernel there; the one-call path is for the host-paced coarse levels)
+    return (ops.TIMERS is None and feat.shape[0] <= SINGLE_CALL_MAX_ROWS and feat.dtype == torch.bfloat16
+            and type(linear) is nn.Linear
+            and linear.bias is not None and linear.weight.dtype == torch.bfloat16
+            and linear.weight.is_contiguous() and linear.in_features % 8 == 0 and linear.out_features % 8 == 0)
 
 
 def _record_stream(obj, stream):

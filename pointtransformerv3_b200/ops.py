@@ -600,3 +600,51 @@ def seg_head(feat, weight, bias=None, want_logits=True, want_labels=True):
                                          _lib.ptr(logits), _lib.ptr(labels), n, C, K, _lib.dtype_id(feat),
                                          _lib.stream()), "ptv3_seg_head_fwd")
     return logits, labels
+
+
+def pool_stage(x, weight, bias, coord, indices, idx_ptr, bn_scale=None, bn_shift=None, reduce="max"):
+    """SerializedPooling's feature side in one call (bf16): proj(x), segment reduction,
+    BN + GELU, mean coordinate.  Returns (pooled feat (M, C_out), pooled coord or None)."""
+    _lib.require_cuda(x, weight, bias, indices, idx_ptr)
+    lib = _lib.load()
+    x = x.contiguous()
+    n, cin = x.shape
+    cout = weight.shape[0]
+    m = idx_ptr.numel() - 1
+    out = torch.empty((m, cout), dtype=x.dtype, device=x.device)
+    cout_coord = None
+    if coord is not None:
+        coord = coord.to(torch.float32).contiguous()
+        cout_coord = torch.empty((m, 3), dtype=torch.float32, device=x.device)
+    nbytes = lib.ptv3_pool_stage_workspace_bytes(n, cout)
+    ws = _lib.workspace(nbytes, x.device)
+    with timed("pool_stage", 2.0 * n * cin * cout):
+        _lib.check(lib.ptv3_pool_stage_fwd(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(coord),
+                                           _lib.ptr(indices), _lib.ptr(idx_ptr), n, m, cin, cout,
+                                           _lib.ptr(bn_scale), _lib.ptr(bn_shift), _lib.ptr(out),
+                                           _lib.ptr(cout_coord), REDUCE_IDS[reduce], _lib.dtype_id(x), _lib.ptr(ws),
+                                           nbytes, _lib.stream()), "ptv3_pool_stage_fwd")
+    return out, cout_coord
+
+
+def unpool_stage(skip_feat, child_feat, w_skip, b_skip, w_child, b_child, cluster, skip_scale, skip_shift,
+                 child_scale, child_shift):
+    """SerializedUnpooling in one call (bf16); returns (out, skip_act) as ops.unpool does."""
+    _lib.require_cuda(skip_feat, child_feat, cluster)
+    lib = _lib.load()
+    skip_feat, child_feat = skip_feat.contiguous(), child_feat.contiguous()
+    n, cs = skip_feat.shape
+    m, cc = child_feat.shape
+    cout = w_skip.shape[0]
+    out = torch.empty((n, cout), dtype=skip_feat.dtype, device=skip_feat.device)
+    act = torch.empty_like(out)
+    nbytes = lib.ptv3_unpool_stage_workspace_bytes(n, m, cout)
+    ws = _lib.workspace(nbytes, skip_feat.device)
+    with timed("unpool_stage", 2.0 * cout * (n * cs + m * cc)):
+        _lib.check(lib.ptv3_unpool_stage_fwd(_lib.ptr(skip_feat), _lib.ptr(child_feat), _lib.ptr(w_skip),
+                                             _lib.ptr(b_skip), _lib.ptr(w_child), _lib.ptr(b_child),
+                                             _lib.ptr(cluster), n, m, cs, cc, cout, _lib.ptr(skip_scale),
+                                             _lib.ptr(skip_shift), _lib.ptr(child_scale), _lib.ptr(child_shift),
+                                             _lib.ptr(out), _lib.ptr(act), _lib.dtype_id(skip_feat), _lib.ptr(ws),
+                                             nbytes, _lib.stream()), "ptv3_unpool_stage_fwd")
+    return out, act
