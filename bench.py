@@ -33,6 +33,10 @@ SCENES_PER_GPU = 4
 TARGET_VOXELS = 100_000
 GRID = 0.02
 CPU_SAMPLE_VOXELS = 100_000
+# DRAM read + write bytes per row and channel of one attention launch (ncu, dram__bytes_read.sum +
+# dram__bytes_write.sum of a single launch on 240 640 rows x 64 channels gathered through a random
+# permutation, the least local case)
+ATTENTION_DRAM_BYTES_PER_ROW_CHANNEL = 10.74
 
 
 def workload_config(n_gpus, gather=False):
@@ -83,8 +87,50 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- #
-# CPU arm (oracle port of the reference path)
+# CPU arm: the reference's own forward on the host cores
 # --------------------------------------------------------------------------- #
+def cpu_step_fn(n_scenes):
+    """Returns (callable running one CPU forward, points per forward, description, kind).
+
+    kind "reference": the unmodified reference model file (placed under oracle/_ref by
+    oracle/make_ref.py, or a checkout beside this repository), run on CPU through the
+    stand-ins of oracle/refshim for the four third-party packages it imports (the
+    submanifold convolution among them is this repository's CPU restatement: spconv has
+    no CPU build).  kind "port": the oracle's restatement of that forward, used where the
+    reference's files are not present."""
+    from oracle import ptv3_oracle as O, refload
+    from pointtransformerv3_b200 import synthetic
+    torch.set_num_threads(os.cpu_count() or 1)
+    scenes = [synthetic.indoor_scene(i, CPU_SAMPLE_VOXELS, GRID) for i in range(n_scenes)]
+    data = synthetic.make_batch(scenes, 3, 0, torch.bfloat16)
+    n = int(data["offset"][-1])
+    what = "%d indoor scene%s of the benchmark batch (%d voxels), bf16, enable_flash=False" % (
+        n_scenes, "" if n_scenes == 1 else "s", n)
+    ref = None
+    try:
+        ref = refload.load_model()
+    except Exception:            # a stand-in that does not match this torch build: fall back to the port
+        ref = None
+    if ref is not None:
+        torch.manual_seed(0)
+        net = ref.PointTransformerV3(in_channels=6, enable_flash=False).eval().bfloat16()
+
+        def step():
+            with torch.inference_mode():
+                torch.manual_seed(1)
+                d = {k: v.clone() for k, v in data.items()}
+                d["grid_size"] = GRID
+                return net(d).feat
+        return step, n, "unmodified reference model.py on CPU (stand-ins for addict/timm/torch_scatter/spconv); " + what, "reference"
+    sd = cpu_state_dict(torch.bfloat16)
+
+    def step():
+        with torch.inference_mode():
+            torch.manual_seed(1)
+            return O.ptv3_forward(sd, data)
+    return step, n, "CPU restatement of the reference forward (oracle); " + what, "port"
+
+
 def cpu_state_dict(dtype):
     from pointtransformerv3_b200 import PointTransformerV3
     torch.manual_seed(0)
@@ -92,30 +138,13 @@ def cpu_state_dict(dtype):
     return {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in net.state_dict().items()}
 
 
-def cpu_step_fn():
-    """Returns (callable running one bounded CPU step, points per step, description)."""
-    from oracle import ptv3_oracle as O
-    from pointtransformerv3_b200 import synthetic
-    torch.set_num_threads(os.cpu_count() or 1)
-    data = synthetic.make_batch([synthetic.indoor_scene(0, CPU_SAMPLE_VOXELS, GRID)], 3, 0, torch.bfloat16)
-    sd = cpu_state_dict(torch.bfloat16)
-    n = int(data["offset"][-1])
-
-    def step():
-        with torch.inference_mode():
-            torch.manual_seed(1)
-            return O.ptv3_forward(sd, data)
-    sample = ("CPU restatement of the reference forward (bf16, enable_flash=False) on one indoor scene "
-              "of %d voxels from the same generator; points/s = voxels / time" % n)
-    return step, n, sample
-
-
 def run_reference(args):
+    """The reference arm: the same workload (all scenes of one GPU's batch) per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    step, n, sample = cpu_step_fn()
-    for _ in range(max(args.warmup, 1) if args.warmup else 0):
+    step, n, sample, kind = cpu_step_fn(SCENES_PER_GPU)
+    for _ in range(args.warmup):
         step()
     t = []
     for _ in range(args.steps):
@@ -128,9 +157,9 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": per * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
+        "config": dict(workload_config(args.gpus), points_per_gpu=n),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": sample + "; every step is the whole batch; rank 0 only"},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -297,20 +326,32 @@ def run_ours(args):
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
         except OSError:
             pass
-        att = timers.get("attention", {"calls": 0, "ms": 0.0, "work": 0.0})
+        att = timers.get("attention", {"calls": 0, "ms": 0.0, "work": 0.0, "extra": 0.0})
         tf_peak = peaks.get("bf16_tflops_sustained", 1400.0)
-        achieved = att["work"] / (att["ms"] * 1e-3) / 1e12 if att["ms"] else 0.0
-        # DRAM bytes per launch: the ncu capture of one launch on 240 640 padded rows x 64 channels
-        # (qkv of 92 MB gathered through a random permutation, the least local case) reads 147.5 MB and
-        # writes 17.9 MB, i.e. 10.7 B per padded row and channel against 8 B algorithmic (qkv read once,
-        # output written once).  Traffic grows in proportion to rows x channels = work / (4 x patch).
-        traffic = 10.74 * att["work"] / (4.0 * 1024.0) / max(att["calls"], 1)
+        sec = att["ms"] * 1e-3
+        achieved = att["work"] / sec / 1e12 if sec else 0.0
+        # One exponential per score, head dimension 16: exps = FLOPs / 64.  The exp unit has 16
+        # lanes per SM: 16 x 148 x clock results per second at most.
+        exps = att["work"] / 64.0
+        sm_mhz = (clocks or {}).get("sm_mhz") or 1965.0
+        exp_peak = 16 * 148 * sm_mhz * 1e6
+        # DRAM bytes per launch: bytes per row and channel of a committed ncu capture of one launch
+        # of this kernel (see ATTENTION_DRAM_BYTES_PER_ROW_CHANNEL) x the rows and channels of the
+        # average launch of this run; algorithmic: qkv read once, output written once = 8 B.
+        rows_channels = att["extra"] or None
         roofline = {"kernel": "attention core (all patch-attention launches of the timed steps)",
                     "bound": "tensor", "achieved": achieved, "peak": tf_peak, "unit": "TFLOP/s",
-                    "frac": achieved / tf_peak, "traffic": traffic,
-                    "traffic_note": "bytes per launch, scaled from an ncu capture of a smaller launch (profiles/attention_tc05_240k_points.md)",
+                    "frac": achieved / tf_peak,
+                    "traffic": None if rows_channels is None else
+                    ATTENTION_DRAM_BYTES_PER_ROW_CHANNEL * rows_channels / max(att["calls"], 1),
+                    "traffic_note": "DRAM bytes per launch: %.2f B per row and channel (one ncu capture of a "
+                                    "single launch of this kernel, 8 B algorithmic) x rows x channels of this "
+                                    "run's average launch" % ATTENTION_DRAM_BYTES_PER_ROW_CHANNEL,
                     "peak_source": "measured (sustained)" if peaks else "fallback",
-                    "launches": att["calls"], "avg_launch_ms": att["ms"] / max(att["calls"], 1)}
+                    "launches": att["calls"], "avg_launch_ms": att["ms"] / max(att["calls"], 1),
+                    "limiter": {"unit": "exp (one exponential per 64 tensor FLOPs at head dimension 16)",
+                                "achieved_exps_per_s": exps / sec if sec else 0.0, "peak_exps_per_s": exp_peak,
+                                "frac": exps / sec / exp_peak if sec else 0.0}}
         breakdown = {k: {"calls": v["calls"], "ms_per_step": v["ms"] / args.steps} for k, v in all_timers.items()}
         line = {
             "metric": METRIC, "value": total_points * args.steps / (ms * 1e-3), "unit": UNIT,
@@ -325,15 +366,20 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "roofline": roofline,
             "kernel_ms_per_step": breakdown,
+            "kernel_ms_note": "second pass on the per-operator host path (one event pair per operator); the "
+                              "timed steps queue a whole block per C call and carry no events inside",
         }
         if world == 1 and not args.no_cpu_baseline:
-            step, n, sample = cpu_step_fn()
+            step, n, sample, kind = cpu_step_fn(1)
             step()
-            t = time.perf_counter()
-            step()
-            dt = time.perf_counter() - t
-            line["cpu_baseline"] = {"value": n / dt, "unit": UNIT, "cores": torch.get_num_threads(),
-                                    "kind": "port", "sample": sample}
+            dts = []
+            for _ in range(3):
+                t = time.perf_counter()
+                step()
+                dts.append(time.perf_counter() - t)
+            line["cpu_baseline"] = {"value": n / statistics.median(dts), "unit": UNIT,
+                                    "cores": torch.get_num_threads(), "kind": kind,
+                                    "sample": sample + "; median of 3 after one warm-up"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -126,9 +126,11 @@ int ptv3_pad_plan(const int64_t* offset, int n_scenes, int patch, int64_t n, int
  *               per element is the same; kept for comparison), 4 = tcgen05 /
  *               tensor-memory path (bf16, head_dim 16, max_seqlen <= 1024,
  *               needs `status`; measured 12 % slower than 2 on B200)
- *   status      one uint32 or NULL; path 4 ORs PTV3_STATUS_WAIT_LIMIT into it
- *               when one of its bounded waits ran out (the output is then
- *               undefined); the other paths do not touch it
+ *   status      one uint32 or NULL.  Every path ORs PTV3_STATUS_BAD_INDEX into it
+ *               when cu_seqlens holds a patch longer than max_seqlen (that patch is
+ *               skipped, its output rows stay unwritten; with NULL it is skipped
+ *               silently); path 4 also ORs PTV3_STATUS_WAIT_LIMIT when one of its
+ *               bounded waits ran out (the output is then undefined)
  */
 int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad,
                        const int64_t* unpad, const int32_t* cu_seqlens, void* out, int64_t n,
@@ -173,8 +175,11 @@ int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int32_t* nbr, 
  *     rejected with PTV3_ERR_UNSUPPORTED and the caller should fall back to
  *     ptv3_kmap_build
  *   - nothing is allocated or freed, here or in any library it calls
- *   - the first call on each device resolves the array's device address; make
- *     that first call outside any stream capture
+ *   - the first call on each device resolves the array's device address and caches
+ *     it for the life of the process (the cache is atomic: first calls from several
+ *     host threads are safe); make that first call outside any stream capture, and
+ *     do not call cudaDeviceReset() afterwards, which would leave the cached
+ *     address pointing into a context that no longer exists
  *   - all calls on a device share the one table (it is re-initialised at the
  *     start of each call, in stream order): two calls whose kernels may overlap
  *     on the GPU (different streams or threads) race and must be serialised by

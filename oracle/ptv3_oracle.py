@@ -132,28 +132,71 @@ def rpe_bias(grid_coord_patches, table, pos_bnd):
     return out.permute(0, 3, 1, 2)
 
 
+ATTENTION_CHUNK_BYTES = 1 << 30    # score tensors are built for this many bytes of patches at a time
+
+
+def _patch_attention(q, k, v, scale, upcast_attention, upcast_softmax, bias=None):
+    """softmax((q * scale) k^T [+ bias]) v over (P, H, K, d) tensors, model.py:467-474; patches are
+    walked in groups so that the (P, H, K, K) score tensor stays bounded (same arithmetic)."""
+    P, H, K, d = q.shape
+    step = max(1, ATTENTION_CHUNK_BYTES // max(1, H * K * K * 4))
+    outs = []
+    for a in range(0, P, step):
+        qq, kk, vv = q[a:a + step], k[a:a + step], v[a:a + step]
+        if upcast_attention:
+            qq, kk = qq.float(), kk.float()
+        attn = (qq * scale) @ kk.transpose(-2, -1)              # model.py:467
+        if bias is not None:
+            attn = attn + bias[a:a + step]                      # model.py:468-469
+        if upcast_softmax:
+            attn = attn.float()
+        attn = torch.softmax(attn, dim=-1).to(v.dtype)          # model.py:470-473
+        outs.append(attn @ vv)
+    return torch.cat(outs) if len(outs) > 1 else outs[0]
+
+
 def attention(feat, w_qkv, b_qkv, w_proj, b_proj, order, inverse, offset, num_heads,
-              patch_size_max, scale=None, upcast_attention=False, upcast_softmax=False, rpe=None):
-    """``rpe``: None or (grid_coord (N,3), table (3*num, H), pos_bnd)."""
+              patch_size_max, scale=None, upcast_attention=False, upcast_softmax=False, rpe=None,
+              flash=False):
+    """``rpe``: None or (grid_coord (N,3), table (3*num, H), pos_bnd).
+
+    ``flash=True`` restates the grouping of the flash branch (model.py:475-483) in the
+    feature dtype: the patch is ``patch_size_max`` itself and the sequences are the
+    ``cu_seqlens`` segments, so a scene shorter than the patch is one short sequence.
+    (The reference computes that branch in fp16 on a GPU library; the grouping is what
+    is restated here, the arithmetic is the non-flash branch's.)"""
     N, C = feat.shape
     H = num_heads
     scale = scale or (C // H) ** -0.5
-    K = effective_patch(offset, patch_size_max)
-    pad, unpad, _ = pad_plan(offset, K)
+    K = patch_size_max if flash else effective_patch(offset, patch_size_max)
+    pad, unpad, cu = pad_plan(offset, K)
     src = order[pad]                                            # model.py:452
     dst = unpad[inverse]                                        # model.py:453
     qkv = F.linear(feat, w_qkv, b_qkv)[src]                     # model.py:456
-    q, k, v = qkv.reshape(-1, K, 3, H, C // H).permute(2, 0, 3, 1, 4).unbind(0)
-    if upcast_attention:
-        q, k = q.float(), k.float()
-    attn = (q * scale) @ k.transpose(-2, -1)                    # model.py:467
-    if rpe is not None:                                         # model.py:468-469
-        grid_coord, table, pos_bnd = rpe
-        attn = attn + rpe_bias(grid_coord[src].reshape(-1, K, 3), table, pos_bnd)
-    if upcast_softmax:
-        attn = attn.float()
-    attn = torch.softmax(attn, dim=-1).to(qkv.dtype)            # model.py:470-473
-    out = (attn @ v).transpose(1, 2).reshape(-1, C)             # model.py:474
+    if flash:
+        assert rpe is None
+        out = torch.empty(qkv.shape[0], C, dtype=qkv.dtype)
+        cu = cu.tolist()
+        lens = [cu[i + 1] - cu[i] for i in range(len(cu) - 1)]
+        i = 0
+        while i < len(lens):
+            # runs of equally long sequences (the full patches of a scene) go through one call
+            j = i
+            while j < len(lens) and lens[j] == lens[i]:
+                j += 1
+            L = lens[i]
+            blk = qkv[cu[i]:cu[j]].reshape(j - i, L, 3, H, C // H).permute(2, 0, 3, 1, 4)
+            o = _patch_attention(blk[0], blk[1], blk[2], scale, upcast_attention, upcast_softmax)
+            out[cu[i]:cu[j]] = o.transpose(1, 2).reshape(-1, C)
+            i = j
+    else:
+        q, k, v = qkv.reshape(-1, K, 3, H, C // H).permute(2, 0, 3, 1, 4).unbind(0)
+        bias = None
+        if rpe is not None:                                     # model.py:468-469
+            grid_coord, table, pos_bnd = rpe
+            bias = rpe_bias(grid_coord[src].reshape(-1, K, 3), table, pos_bnd)
+        out = _patch_attention(q, k, v, scale, upcast_attention, upcast_softmax, bias)
+        out = out.transpose(1, 2).reshape(-1, C)                # model.py:474
     out = out[dst]                                              # model.py:484
     return F.linear(out, w_proj, b_proj)                        # model.py:487
 
@@ -275,7 +318,7 @@ class Level:
         self.nbr3 = None
 
 
-def block(sd, p, lv, feat, heads, patch, order_index, conv_in=None):
+def block(sd, p, lv, feat, heads, patch, order_index, conv_in=None, flash=False):
     """model.py:586-606 with pre_norm=True.
 
     ``conv_in``: what the xCPE convolution reads when it is not ``feat``.  The
@@ -292,7 +335,7 @@ def block(sd, p, lv, feat, heads, patch, order_index, conv_in=None):
     x = ln(feat, sd, p + "norm1.0.")
     x = attention(x, sd[p + "attn.qkv.weight"], sd[p + "attn.qkv.bias"], sd[p + "attn.proj.weight"],
                   sd[p + "attn.proj.bias"], lv.order[order_index], lv.inverse[order_index],
-                  lv.offset, heads, patch)
+                  lv.offset, heads, patch, flash=flash)
     feat = feat + x
     x = ln(feat, sd, p + "norm2.0.")
     x = F.linear(x, sd[p + "mlp.0.fc1.weight"], sd[p + "mlp.0.fc1.bias"])
@@ -324,10 +367,14 @@ def unpool(sd, p, lv, feat, skip_feat):
     return b + a[lv.cluster], b
 
 
-def ptv3_forward(sd, data, cfg=None, return_levels=False):
+def ptv3_forward(sd, data, cfg=None, return_levels=False, flash=False, taps=None):
     """Runs the backbone.  ``data``: feat, grid_coord, coord, offset.  Draws the
-    same ``torch.randperm`` sequence as the reference (1 + one per pooling)."""
+    same ``torch.randperm`` sequence as the reference (1 + one per pooling).
+    ``flash``: the patch grouping of ``enable_flash=True`` (see ``attention``).
+    ``taps``: a dict that receives the features after "embedding", every "enc.enc{s}"
+    and every "dec.dec{s}"."""
     cfg = dict(DEFAULT_CFG, **(cfg or {}))
+    tap = (lambda name, f: taps.__setitem__(name, f)) if taps is not None else (lambda name, f: None)
     orders = cfg["order"]
     offset = data["offset"].to(torch.int64)
     batch = offset_to_batch(offset)
@@ -344,6 +391,7 @@ def ptv3_forward(sd, data, cfg=None, return_levels=False):
     nbr5 = kernel_map(sparse_indices(batch, grid), 5)
     feat = subm_conv(feat, nbr5, sd["embedding.stem.conv.weight"], None)
     feat = F.gelu(bn_eval(feat, sd, "embedding.stem.norm."))
+    tap("embedding", feat)
     levels, skips = [], []
     ns = len(cfg["enc_depths"])
     for s in range(ns):
@@ -352,7 +400,8 @@ def ptv3_forward(sd, data, cfg=None, return_levels=False):
             lv, feat = pool(sd, f"enc.enc{s}.down.", lv, feat, cfg["stride"][s - 1], cfg["shuffle_orders"])
         for i in range(cfg["enc_depths"][s]):
             feat = block(sd, f"enc.enc{s}.block{i}.", lv, feat, cfg["enc_num_head"][s],
-                         cfg["enc_patch_size"][s], i % len(orders))
+                         cfg["enc_patch_size"][s], i % len(orders), flash=flash)
+        tap(f"enc.enc{s}", feat)
         levels.append(lv)
     if not cfg["cls_mode"]:
         for s in reversed(range(ns - 1)):
@@ -361,7 +410,8 @@ def ptv3_forward(sd, data, cfg=None, return_levels=False):
             for i in range(cfg["dec_depths"][s]):
                 feat = block(sd, f"dec.dec{s}.block{i}.", lv, feat, cfg["dec_num_head"][s],
                              cfg["dec_patch_size"][s], i % len(orders),
-                             conv_in=stale if i == 0 else None)
+                             conv_in=stale if i == 0 else None, flash=flash)
+            tap(f"dec.dec{s}", feat)
     if return_levels:
         return feat, levels
     return feat

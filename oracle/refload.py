@@ -9,10 +9,15 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 def reference_root():
-    """Directory of the reference checkout: $PTV3_REFERENCE_ROOT, else a `reference`
-    directory next to this repository."""
-    default = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
-    return os.environ.get("PTV3_REFERENCE_ROOT", default)
+    """Directory of the reference's files: $PTV3_REFERENCE_ROOT, else a `reference`
+    directory next to this repository, else the copy `oracle/make_ref.py` placed under
+    `oracle/_ref/reference`."""
+    if "PTV3_REFERENCE_ROOT" in os.environ:
+        return os.environ["PTV3_REFERENCE_ROOT"]
+    sibling = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    if os.path.isfile(os.path.join(sibling, "model.py")):
+        return sibling
+    return os.path.join(_HERE, "_ref", "reference")
 
 
 def load_serialization():

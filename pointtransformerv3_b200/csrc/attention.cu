@@ -35,7 +35,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(AF_QT) attn_fma_kernel(
     const T* __restrict__ qkv, const int64_t* __restrict__ order, const int64_t* __restrict__ pad,
     const int64_t* __restrict__ unpad, const int32_t* __restrict__ cu_seqlens, T* __restrict__ out,
-    int C, float scale, RpeArgs rpe)
+    int C, float scale, RpeArgs rpe, uint32_t* __restrict__ status)
 {
     constexpr int AF_KC = D <= 32 ? 128 : 64;   // keys per staged chunk
     __shared__ float Ks[AF_KC][D];
@@ -50,6 +50,10 @@ __global__ void __launch_bounds__(AF_QT) attn_fma_kernel(
     const int64_t start = cu_seqlens[seq];
     const int L = (int)(cu_seqlens[seq + 1] - start);
     const int q0 = blockIdx.x * AF_QT;
+    // the grid covers max_seqlen queries per sequence: a longer sequence would leave rows of
+    // the output unwritten, so it is reported instead
+    if (blockIdx.x == 0 && tid == 0 && status && L > (int)gridDim.x * AF_QT)
+        atomicOr(status, PTV3_STATUS_BAD_INDEX);
     if (q0 >= L) return;
     const int qi = q0 + tid;
     const bool valid = qi < L;
@@ -142,13 +146,14 @@ __global__ void __launch_bounds__(AF_QT) attn_fma_kernel(
 template <typename T>
 static int launch_attn_fma(const void* qkv, const int64_t* order, const int64_t* pad,
                            const int64_t* unpad, const int32_t* cu, void* out, int n_seq,
-                           int max_seqlen, int C, int H, float scale, RpeArgs rpe, cudaStream_t stream)
+                           int max_seqlen, int C, int H, float scale, RpeArgs rpe, uint32_t* status,
+                           cudaStream_t stream)
 {
     const int D = C / H;
     const dim3 grid((max_seqlen + AF_QT - 1) / AF_QT, n_seq, H);
 #define AF_LAUNCH(DD)                                                                         \
     attn_fma_kernel<T, DD><<<grid, AF_QT, 0, stream>>>((const T*)qkv, order, pad, unpad, cu, \
-                                                       (T*)out, C, scale, rpe)
+                                                       (T*)out, C, scale, rpe, status)
     switch (D) {
         case 8: AF_LAUNCH(8); break;
         case 16: AF_LAUNCH(16); break;
@@ -198,12 +203,12 @@ static int attention_impl(const void* qkv, const int64_t* order, const int64_t* 
                  "16-byte aligned qkv", ATTN_MMA_MAX_SEQLEN);
     if (mma_ok && algo != 1)
         return launch_attn_mma(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen, channels,
-                               heads, scale, algo == 3, (cudaStream_t)stream);
+                               heads, scale, algo == 3, status, (cudaStream_t)stream);
     if (dtype == PTV3_DTYPE_F32)
         return launch_attn_fma<float>(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen,
-                                      channels, heads, scale, rpe, (cudaStream_t)stream);
+                                      channels, heads, scale, rpe, status, (cudaStream_t)stream);
     return launch_attn_fma<__nv_bfloat16>(qkv, order, pad, unpad, cu_seqlens, out, n_seq, max_seqlen,
-                                          channels, heads, scale, rpe, (cudaStream_t)stream);
+                                          channels, heads, scale, rpe, status, (cudaStream_t)stream);
 }
 
 extern "C" int ptv3_attention_fwd(const void* qkv, const int64_t* order, const int64_t* pad,

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     const __nv_bfloat16* __restrict__ qkv, const int64_t* __restrict__ order,
     const int64_t* __restrict__ pad, const int64_t* __restrict__ unpad,
     const int32_t* __restrict__ cu_seqlens, __nv_bfloat16* __restrict__ out, int C, float scale,
-    int lpad_max)
+    int lpad_max, uint32_t* __restrict__ status)
 {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* Ks = smem;
@@ -63,6 +63,12 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     const int64_t start = cu_seqlens[seq];
     const int L = (int)(cu_seqlens[seq + 1] - start);
     if (L <= 0) return;
+    // shared memory was sized from the caller's max_seqlen: a longer sequence (a plan made
+    // for a larger patch) is reported and skipped, uniformly over the CTA, before any write
+    if (L > lpad_max) {
+        if (tid == 0 && status) atomicOr(status, PTV3_STATUS_BAD_INDEX);
+        return;
+    }
     const int Lp = (L + AM_KC - 1) / AM_KC * AM_KC;   // <= lpad_max
     const int ntiles = (L + 15) / 16;
     const int tiles_per_slice = (ntiles + n_slices - 1) / n_slices;
@@ -238,7 +244,7 @@ bool attn_mma_supported(int channels, int heads, int max_seqlen)
 
 int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, const int64_t* unpad,
                     const int32_t* cu, void* out, int n_seq, int max_seqlen, int C, int H, float scale,
-                    bool packed_exp, cudaStream_t stream)
+                    bool packed_exp, uint32_t* status, cudaStream_t stream)
 {
     const int lpad = (max_seqlen + AM_KC - 1) / AM_KC * AM_KC;
     const size_t smem = (size_t)lpad * 64;
@@ -255,7 +261,7 @@ int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, c
     while (pairs * qsplit < 4 * 3 * 148 && qsplit * 2 * AM_WARPS <= tiles) qsplit *= 2;
     const dim3 grid(H * qsplit, n_seq);
     kern<<<grid, AM_THREADS, smem, stream>>>(
-        (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad);
+        (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad, status);
     count_launches(1);
     return check_launch("ptv3_attention_fwd");
 }

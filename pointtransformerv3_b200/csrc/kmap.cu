@@ -7,6 +7,8 @@
 // (5x5x5 stem).  The table is offset-major, nbr[o][i], so that a tile of
 // consecutive voxels reads each offset's neighbour rows coalesced.
 // Offset index o = ((dx+r)*k + (dy+r))*k + (dz+r), r = k/2.
+#include <atomic>
+
 #include "common.cuh"
 #include "kmap.cuh"
 #include "voxel_index.cuh"
@@ -185,8 +187,9 @@ extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int
     Carver cv(workspace);
     unsigned long long* keys = cv.take<unsigned long long>(cap);
     uint32_t* vals = cv.take<uint32_t>(cap);
-    cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
-    cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream);
+    if (cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream) != cudaSuccess ||
+        cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream) != cudaSuccess)
+        return check_launch("ptv3_kmap_build: table reset");
     km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
     km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(
         indices, n, ksize, keys, vals, cap - 1, nbr, status);
@@ -209,8 +212,9 @@ constexpr size_t KM_STATIC_BYTES = KM_STATIC_KEY_BYTES + KM_STATIC_SLOTS * sizeo
 static __device__ __align__(256) unsigned char g_kmap_static_scratch[KM_STATIC_BYTES];
 
 constexpr int KM_MAX_DEVICES = 64;
-// device address of the static table on each device, resolved on first use there
-static void* g_kmap_static_ptr[KM_MAX_DEVICES] = {nullptr};
+// device address of the static table on each device, resolved on first use there; atomic, so
+// that first calls from two host threads do not race (both would store the same address)
+static std::atomic<void*> g_kmap_static_ptr[KM_MAX_DEVICES];
 
 // In host code `g_kmap_static_scratch` is only a handle for the runtime, not an
 // address a kernel could use, so the device address is looked up once per
@@ -224,7 +228,8 @@ static int km_static_table(void** out)
                   e != cudaSuccess ? cudaGetErrorString(e) : "index out of range");
         return PTV3_ERR_CUDA;
     }
-    if (g_kmap_static_ptr[dev] == nullptr) {
+    void* cached = g_kmap_static_ptr[dev].load(std::memory_order_acquire);
+    if (cached == nullptr) {
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_kmap_static_scratch);
         if (e != cudaSuccess || p == nullptr) {
@@ -232,9 +237,10 @@ static int km_static_table(void** out)
                       cudaGetErrorString(e));
             return PTV3_ERR_CUDA;
         }
-        g_kmap_static_ptr[dev] = p;
+        g_kmap_static_ptr[dev].store(p, std::memory_order_release);
+        cached = p;
     }
-    *out = g_kmap_static_ptr[dev];
+    *out = cached;
     return PTV3_OK;
 }
 
@@ -266,8 +272,9 @@ extern "C" int ptv3_kmap_build_static(const int32_t* indices, int64_t n, int ksi
     uint32_t* vals = reinterpret_cast<uint32_t*>(static_cast<char*>(table) + KM_STATIC_KEY_BYTES);
     // the table still holds the previous call's entries: reset exactly the slots this call uses
     const uint64_t cap = km_capacity(n);   // <= KM_STATIC_SLOTS because n <= KM_STATIC_MAX_VOXELS
-    cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream);
-    cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream);
+    if (cudaMemsetAsync(keys, 0xff, cap * sizeof(uint64_t), stream) != cudaSuccess ||
+        cudaMemsetAsync(vals, 0xff, cap * sizeof(uint32_t), stream) != cudaSuccess)
+        return check_launch("ptv3_kmap_build_static: table reset");
     const unsigned blocks = (unsigned)((n + 255) / 256);
     km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
     km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(

@@ -203,12 +203,19 @@ class SerializedAttention(PointModule):
 
     @torch.no_grad()
     def get_padding_and_inverse(self, point):
-        """model.py:382-438; cached in the Point under the reference's keys."""
-        if not {"pad", "unpad", "cu_seqlens_key"}.issubset(point.keys()):
+        """model.py:382-438; cached in the Point under the reference's keys.
+
+        The reference reuses whatever plan is cached, also when a later block of the same
+        level has another patch size (encoder and decoder patch sizes may differ), which
+        there groups rows wrongly.  Here the patch size a plan was made for is kept beside
+        it and the plan is rebuilt when this module's differs."""
+        if (not {"pad", "unpad", "cu_seqlens_key"}.issubset(point.keys())
+                or point.get("_pad_patch", self.patch_size) != self.patch_size):
             pad, unpad, cu = ops.pad_plan(point.offset, point.host_counts(), self.patch_size,
                                           point.device_status())
             point.check_status("ptv3_pad_plan")
             point["pad"], point["unpad"], point["cu_seqlens_key"] = pad, unpad, cu
+            point["_pad_patch"] = self.patch_size
         return point["pad"], point["unpad"], point["cu_seqlens_key"]
 
     def core(self, point, qkv):

@@ -3,6 +3,7 @@
 Every wrapper allocates outputs and workspaces with torch, passes raw device
 pointers and the current CUDA stream, and raises on a non-zero status."""
 import ctypes
+import threading
 
 import torch
 
@@ -18,8 +19,8 @@ TIMER_FILTER = None     # optional set of operator names to time (None = all)
 
 
 class timed:
-    def __init__(self, name, work=0.0):
-        self.name, self.work = name, work
+    def __init__(self, name, work=0.0, extra=0.0):
+        self.name, self.work, self.extra = name, work, extra
 
     def __enter__(self):
         self.on = TIMERS is not None and (TIMER_FILTER is None or self.name in TIMER_FILTER)
@@ -32,17 +33,17 @@ class timed:
     def __exit__(self, *exc):
         if self.on:
             self.end.record()
-            TIMERS.setdefault(self.name, []).append((self.start, self.end, self.work))
+            TIMERS.setdefault(self.name, []).append((self.start, self.end, self.work, self.extra))
         return False
 
 
 def timer_summary():
-    """name -> dict(calls, ms, work) from the recorded events (synchronises)."""
+    """name -> dict(calls, ms, work, extra) from the recorded events (synchronises)."""
     torch.cuda.synchronize()
     out = {}
     for name, evs in (TIMERS or {}).items():
-        out[name] = dict(calls=len(evs), ms=sum(a.elapsed_time(b) for a, b, _ in evs),
-                         work=sum(w for _, _, w in evs))
+        out[name] = dict(calls=len(evs), ms=sum(e[0].elapsed_time(e[1]) for e in evs),
+                         work=sum(e[2] for e in evs), extra=sum(e[3] for e in evs))
     return out
 
 
@@ -147,8 +148,12 @@ def attention(qkv, order_row, pad, unpad, cu_seqlens, heads, max_seqlen, scale, 
     own = status is None
     if own:
         status = new_status(qkv.device)
-    # algorithmic work: QK^T and PV over every padded row against its whole patch
-    with timed("attention", 4.0 * pad.numel() * max_seqlen * C):
+    # algorithmic work: QK^T and PV of every sequence, 4 L^2 C FLOPs (read from the device only
+    # while per-operator timing is on)
+    work = 0.0
+    if TIMERS is not None:
+        work = 4.0 * C * float(torch.diff(cu_seqlens).double().square().sum().item())
+    with timed("attention", work, float(pad.numel()) * C):      # extra: padded rows x channels
         _lib.check(lib.ptv3_attention_fwd(_lib.ptr(qkv), _lib.ptr(order_row.contiguous()), _lib.ptr(pad),
                                           _lib.ptr(unpad), _lib.ptr(cu_seqlens), _lib.ptr(out), n,
                                           cu_seqlens.numel() - 1, int(max_seqlen), C, int(heads),
@@ -266,7 +271,8 @@ def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=
     torch.cuda.current_stream().synchronize()
     host = meta_host.tolist()
     if int(status_host[0]):
-        raise _lib.Ptv3Error("ptv3_pool_plan: device status 0x%x" % int(status_host[0]))
+        raise _lib.Ptv3Error("device status 0x%x (read after ptv3_pool_plan; the word is shared by "
+                             "every kernel queued with it)" % int(status_host[0]))
     m = host[0]
     # the k-row outputs are written packed (row stride m): views, no copies
     packed = lambda t: t.view(-1)[: k * m].view(k, m)
@@ -279,9 +285,10 @@ _PINNED = {}
 
 
 def _pinned(numel, dtype, tag):
-    """A cached pinned host buffer (the callers synchronise before reading it and do not
-    overlap, so one per call site is enough)."""
-    key = (tag, numel, dtype)
+    """A cached pinned host buffer per call site, host thread and CUDA stream (a caller
+    synchronises its stream before reading the buffer, so calls that share all three do
+    not overlap)."""
+    key = (tag, numel, dtype, threading.get_ident(), torch.cuda.current_stream().cuda_stream)
     buf = _PINNED.get(key)
     if buf is None:
         with torch.inference_mode(False):      # a plain tensor: it is written in and out of inference mode

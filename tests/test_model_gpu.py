@@ -183,7 +183,17 @@ def test_block_vs_oracle(dtype):
     else:
         ref32 = O.block({k: v.float() for k, v in sd.items()}, "b.", lv, feat.float(), H, K, 2)
         assert rel_l2(got, ref32) <= 1.5 * rel_l2(ref, ref32) + 1e-3
-        assert_close(got, ref, atol=6e-2, rtol=3e-2, what="block bf16")
+        # Element by element the per-operator tolerance (2e-2 abs, 1e-2 rel) is kept by all but
+        # a sliver of the outputs.  A Block chains nine bf16 roundings (convolution, Linear,
+        # LayerNorm, sum, LayerNorm, qkv, attention, projection, two MLP layers); where the
+        # oracle and the kernels round an intermediate value to different neighbours, the next
+        # LayerNorm (1 / sigma ~ 3 here) and GEMM spread that ulp over a row, so single elements
+        # may leave the one-operator bound; none may leave twice that bound.
+        tol = TOL[torch.bfloat16]
+        err = (got.float().cpu() - ref.float()).abs()
+        outside = err > tol["atol"] + tol["rtol"] * ref.float().abs()
+        assert float(outside.float().mean()) < 1e-3, float(outside.float().mean())
+        assert_close(got, ref, atol=2 * tol["atol"], rtol=2 * tol["rtol"], what="block bf16")
 
 
 def test_flash_flag_uses_full_patch_and_short_sequences():
@@ -234,6 +244,30 @@ def test_lidar_like_scenes_vs_oracle():
     assert torch.equal(out.serialized_order.cpu(), levels[0].order)
     assert torch.equal(out.serialized_code.cpu(), levels[0].code)
     assert_close(out.feat, ref, atol=5e-4, rtol=5e-4, what="lidar-like backbone fp32")
+
+
+@pytest.mark.parametrize("flash", [False, True])
+def test_encoder_and_decoder_patch_sizes_differ(flash):
+    """Encoder patch 256, decoder patch 128: the blocks of one level then need two padding
+    plans.  The reference would reuse the cached one (model.py:387-391); here the plan is
+    rebuilt for the block's own patch size, which is what the oracle (a fresh plan per
+    block) computes."""
+    data = small_batch([3000, 1400], seed=81)
+    cfg = dict(SMALL_CFG, enc_patch_size=(256,) * 5, dec_patch_size=(128,) * 4)
+    net = P.PointTransformerV3(in_channels=6, enable_flash=flash, **cfg).eval()
+    sd = weights.fill_state_dict(net, prefix="patchmix.")
+    net = net.cuda()
+    with torch.inference_mode():
+        torch.manual_seed(4)
+        out = net(cuda_data(data))
+        torch.manual_seed(4)
+        ref = O.ptv3_forward(sd, data, cfg, flash=flash)
+    assert_close(out.feat, ref, atol=5e-4, rtol=5e-4, what="mixed patch sizes, fp32")
+    net = net.bfloat16()
+    with torch.inference_mode():
+        torch.manual_seed(4)
+        out16 = net(cuda_data(data, torch.bfloat16))
+    assert rel_l2(out16.feat, ref) < 3e-2
 
 
 def test_cls_mode_and_single_order():

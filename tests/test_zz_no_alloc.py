@@ -44,6 +44,23 @@ def test_static_kmap_equals_workspace_kmap_twice_in_a_row():
         assert torch.equal(got, want)
 
 
+def test_static_kmap_full_table_then_small_cloud_and_7x7x7():
+    """The largest input the table serves (every slot range in use), a small cloud right after
+    it (which finds the large one's entries beyond its own slots), and the 7x7x7 map."""
+    lib = _lib.load()
+    n = lib.ptv3_kmap_static_max_voxels()
+    g = torch.Generator().manual_seed(5)
+    # n distinct voxels of a 64 x 64 x 32 block in random row order, two scenes
+    cells = torch.randperm(64 * 64 * 32, generator=g)[:n]
+    ind = torch.stack([(torch.arange(n) >= n // 2).long(), cells // (64 * 32), (cells // 32) % 64, cells % 32],
+                      1).int().contiguous().cuda()
+    for cloud, ksize in ((ind, 3), (_indices([1500], 73), 3), (_indices([2500, 800], 74), 7), (ind, 5)):
+        rc, got, status = _static_kmap(cloud, ksize)
+        assert rc == 0, lib.ptv3_last_error()
+        assert status == 0
+        assert torch.equal(got, ops.kmap_build(cloud, ksize))
+
+
 def test_static_kmap_rejects_inputs_beyond_its_table():
     lib = _lib.load()
     n = lib.ptv3_kmap_static_max_voxels() + 1
