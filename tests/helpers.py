@@ -36,6 +36,21 @@ def assert_close(got, ref, atol, rtol, what=""):
         what, int(bad.sum()), bad.numel(), atol, rtol, float(err.max()), float(ref.abs().max()))
 
 
+def assert_close_chain(got, ref, atol, rtol, what="", frac=1e-3, factor=2.0):
+    """For the output of a CHAIN of bf16 operators.  The one-operator tolerance must hold for
+    all but `frac` of the elements, and `factor` times that tolerance for every element.
+    Where the oracle and a kernel round an intermediate value to different bf16 neighbours,
+    the following LayerNorm / GEMM / residual sum carries that ulp on, and after a residual
+    sum that cancels (large operands, small result) one ulp of an operand exceeds a bound
+    taken relative to the result; the strict form cannot hold for every element then."""
+    g, r = got.float().cpu(), ref.float().cpu()
+    err = (g - r).abs()
+    outside = err > atol + rtol * r.abs()
+    share = float(outside.float().mean())
+    assert share <= frac, "%s: %.3g of the elements outside atol=%g rtol=%g" % (what, share, atol, rtol)
+    assert_close(got, ref, factor * atol, factor * rtol, what)
+
+
 def rel_l2(got, ref):
     got, ref = got.float().cpu(), ref.float().cpu()
     return float((got - ref).norm() / ref.norm().clamp_min(1e-30))

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from conftest import GOLDEN
-from helpers import TOL, assert_close, rel_l2, small_batch
+from helpers import TOL, assert_close, assert_close_chain, rel_l2, small_batch
 from oracle import ptv3_oracle as O, weights
 import pointtransformerv3_b200 as P
 
@@ -183,17 +183,8 @@ def test_block_vs_oracle(dtype):
     else:
         ref32 = O.block({k: v.float() for k, v in sd.items()}, "b.", lv, feat.float(), H, K, 2)
         assert rel_l2(got, ref32) <= 1.5 * rel_l2(ref, ref32) + 1e-3
-        # Element by element the per-operator tolerance (2e-2 abs, 1e-2 rel) is kept by all but
-        # a sliver of the outputs.  A Block chains nine bf16 roundings (convolution, Linear,
-        # LayerNorm, sum, LayerNorm, qkv, attention, projection, two MLP layers); where the
-        # oracle and the kernels round an intermediate value to different neighbours, the next
-        # LayerNorm (1 / sigma ~ 3 here) and GEMM spread that ulp over a row, so single elements
-        # may leave the one-operator bound; none may leave twice that bound.
-        tol = TOL[torch.bfloat16]
-        err = (got.float().cpu() - ref.float()).abs()
-        outside = err > tol["atol"] + tol["rtol"] * ref.float().abs()
-        assert float(outside.float().mean()) < 1e-3, float(outside.float().mean())
-        assert_close(got, ref, atol=2 * tol["atol"], rtol=2 * tol["rtol"], what="block bf16")
+        # nine bf16 operators in a chain: see assert_close_chain
+        assert_close_chain(got, ref, what="block bf16", **TOL[torch.bfloat16])
 
 
 def test_flash_flag_uses_full_patch_and_short_sequences():
