@@ -438,7 +438,7 @@ def run_operator_case(args):
                    encode_ms=t_enc, argsort_inverse_ms=t_sort,
                    roofline={"kernel": "encode_kernel", "bound": "hbm", "achieved": enc_b / t_enc / 1e6,
                              "peak": hbm, "unit": "GB/s", "frac": enc_b / t_enc / 1e6 / hbm, "traffic": None},
-                   roofline_argsort={"kernel": "rs_* (all passes)", "bound": "hbm",
+                   roofline_argsort={"kernel": "os_hist_kernel + os_pass_kernel (all passes)", "bound": "hbm",
                                      "achieved": sort_b / t_sort / 1e6, "peak": hbm, "unit": "GB/s",
                                      "frac": sort_b / t_sort / 1e6 / hbm, "traffic": None})
     elif args.case == "attention":

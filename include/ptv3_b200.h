@@ -86,10 +86,15 @@ int ptv3_decode(const int64_t* codes, int64_t n, int depth, int order, int64_t* 
  *   order     k x n int64: codes[r][order[r][j]] is non-decreasing in j, ties
  *             by ascending index
  *   inverse   k x n int64: inverse[r][order[r][j]] = j
+ *   status    one uint32 or NULL: the tiles of a pass wait for the tiles before them
+ *             (bounded); a wait that ran out ORs PTV3_STATUS_WAIT_LIMIT into it and the
+ *             outputs are then undefined
+ * n is limited to 2^28 - 1 elements per row.
  */
 size_t ptv3_argsort_workspace_bytes(int k, int64_t n, int sig_bits);
 int ptv3_argsort_inverse(const int64_t* codes, int k, int64_t n, int sig_bits, int64_t* order,
-                         int64_t* inverse, void* workspace, size_t workspace_bytes, void* stream);
+                         int64_t* inverse, uint32_t* status, void* workspace, size_t workspace_bytes,
+                         void* stream);
 
 /*
  * Patch padding plan of serialized attention.

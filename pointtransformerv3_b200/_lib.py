@@ -40,7 +40,7 @@ SIGNATURES = {
     "ptv3_encode": (c_int, [c_ptr, c_ptr, c_i64, c_int, ctypes.POINTER(c_int), c_int, c_ptr, c_ptr]),
     "ptv3_decode": (c_int, [c_ptr, c_i64, c_int, c_int, c_ptr, c_ptr, c_ptr]),
     "ptv3_argsort_workspace_bytes": (c_sz, [c_int, c_i64, c_int]),
-    "ptv3_argsort_inverse": (c_int, [c_ptr, c_int, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+    "ptv3_argsort_inverse": (c_int, [c_ptr, c_int, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_pad_plan": (c_int, [c_ptr, c_int, c_int, c_i64, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr]),
     "ptv3_attention_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int,
                                    c_int, c_f32, c_int, c_int, c_ptr, c_ptr]),

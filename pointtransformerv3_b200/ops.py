@@ -82,8 +82,10 @@ def decode(code, depth, order):
     return grid, batch
 
 
-def argsort_inverse(codes, sig_bits):
-    """codes (k,N) int64 -> (order, inverse), both (k,N) int64, stable."""
+def argsort_inverse(codes, sig_bits, status=None):
+    """codes (k,N) int64 -> (order, inverse), both (k,N) int64, stable.  status: the
+    caller's device status word (checked by the caller); without one a private word is
+    made and checked here."""
     _lib.require_cuda(codes)
     lib = _lib.load()
     codes = codes.contiguous()
@@ -92,10 +94,16 @@ def argsort_inverse(codes, sig_bits):
     inverse = torch.empty_like(codes)
     nbytes = lib.ptv3_argsort_workspace_bytes(k, n, int(sig_bits))
     ws = _lib.workspace(nbytes, codes.device)
+    own = status is None
+    if own:
+        status = new_status(codes.device)
     with timed("argsort_inverse", 24.0 * k * n):
         _lib.check(lib.ptv3_argsort_inverse(_lib.ptr(codes), k, n, int(sig_bits), _lib.ptr(order),
-                                            _lib.ptr(inverse), _lib.ptr(ws), nbytes, _lib.stream()),
+                                            _lib.ptr(inverse), _lib.ptr(status), _lib.ptr(ws), nbytes,
+                                            _lib.stream()),
                    "ptv3_argsort_inverse")
+    if own:
+        _lib.raise_on_status(status, "ptv3_argsort_inverse")
     return order, inverse
 
 

@@ -122,7 +122,8 @@ class Point(AttrDict):
         assert depth * 3 + n_scene_bits <= 63
         assert depth <= 16
         code = ops.encode(self.grid_coord, self.batch, depth, order)
-        sorted_order, inverse = ops.argsort_inverse(code, depth * 3 + n_scene_bits)
+        sorted_order, inverse = ops.argsort_inverse(code, depth * 3 + n_scene_bits, self.device_status())
+        self.check_status("ptv3_argsort_inverse")
         if shuffle_orders:
             perm = torch.randperm(code.shape[0]).tolist()
             code = torch.stack([code[i] for i in perm])
