@@ -130,7 +130,9 @@ int ptv3_pad_plan(const int64_t* offset, int n_scenes, int patch, int64_t n, int
  *               instruction (measured no faster on B200: the exp unit's rate
  *               per element is the same; kept for comparison), 4 = tcgen05 /
  *               tensor-memory path (bf16, head_dim 16, max_seqlen <= 1024,
- *               needs `status`; measured 12 % slower than 2 on B200)
+ *               needs `status`; measured 40 % slower than 2 on B200: at head
+ *               dimension 16 the tensor pipe is bound by the number of tiny
+ *               products, not by their arithmetic)
  *   status      one uint32 or NULL.  Every path ORs PTV3_STATUS_BAD_INDEX into it
  *               when cu_seqlens holds a patch longer than max_seqlen (that patch is
  *               skipped, its output rows stay unwritten; with NULL it is skipped

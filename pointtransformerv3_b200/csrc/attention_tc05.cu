@@ -1,43 +1,59 @@
 // Patch attention core on the 5th-generation tensor cores (tcgen05 + tensor memory)
 // for bf16 features, head dimension 16 and patches of up to 1024 rows: the shape
-// of every stage of the default backbone (model.py:452-484).  Selected with algo 4.
+// of every stage of the default backbone (model.py:452-484).
 //
 // At head dimension 16 a score costs 64 tensor FLOPs and one exponential, so the
-// exponential unit bounds the kernel.  With tcgen05 the two matrix products cost
-// the CUDA cores nothing (one thread issues one instruction per block instead of an
-// ldmatrix + mma.sync stream in every warp), and a thread owns a whole score row
-// (tensor-memory lane = query row), so row maxima and the running output need no
-// shuffles.
+// exponential unit bounds the kernel, not the tensor pipe.  With tcgen05 the two
+// matrix products cost the CUDA cores nothing (one thread issues one instruction
+// per block instead of an ldmatrix + mma.sync stream in every warp), and a thread
+// owns a whole score row (tensor-memory lane = query row), so row maxima need no
+// shuffles.  What is left per score on the CUDA cores is half a max, half a packed
+// multiply-add, the exponential and half a conversion.
 //
-// One CTA owns one (patch, head) pair (optionally a slice of its query tiles):
-//   gather  K and V of the whole patch, through order[pad[.]], with cp.async into
-//           the no-swizzle UMMA operand layout: planes [d chunk][key] of 16-byte
-//           chunks, which is K-major for K (B of Q K^T) and MN-major for V (B of P V).
-//           V carries a third plane holding a column of ones, so that P V' also
-//           yields the row sums of the rounded probabilities.
+// One CTA owns one (patch, head) pair (optionally a slice of its query tiles).
+//   gather   K and V of the whole patch, through order[pad[.]], with cp.async into
+//            the no-swizzle UMMA operand layout: planes [d chunk][key] of 16-byte
+//            chunks, which is K-major for K (B of Q K^T) and MN-major for V (B of P V).
+//            V carries a third plane holding a column of ones, so that P V' also
+//            yields the row sums of the rounded probabilities.  The gather is issued
+//            by the four issuing warps in blocks of 128 keys, each with its own
+//            mbarrier, so the first products start when the first block has landed.
 //   four softmax groups of 128 threads, each walking 128-query tiles on its own, and
-//   one issuing warp per group; they talk through mbarriers only:
-//     issuer   S[128 x 64] = Q K_j^T                (one tcgen05.mma, K = 16)
-//     softmax  tcgen05.ld S -> registers, arrive "S free" (the issuer starts S_j+1),
-//              row maximum, exp2, P rounded to bf16 -> tensor memory (tcgen05.st),
-//              arrive "P ready"
-//     issuer   R|l [128 x 32] = P V'_j              (A from tensor memory, 4 instructions)
-//     softmax  O = O * exp2(m_old - m_new) + R on the 16 + 1 registers of the row
-//   The groups fill each other's latencies on the exponential unit.  Tensor memory
-//   (512 columns: 64 S + 32 P + 32 R per group) is what limits a CTA to four groups.
+//   one issuing warp per group; they talk through mbarriers only.  Per 48-key block:
+//     issuer   S[128 x 48] = Q K_j^T into one of two score buffers (one tcgen05.mma, K = 16),
+//              always one block ahead of the group
+//     softmax  tcgen05.ld S -> registers, block maximum, P = exp2(S - m) rounded to bf16
+//              and written over the first half of that S (tcgen05.st), arrive "P ready"
+//     issuer   O|l [128 x 32] += P V'_j  (A from tensor memory, accumulating over all key
+//              blocks), then S_j+2 into the buffer P_j occupied
+//   and at the end of a tile the group reads O|l once, divides and writes its rows.
+//   With two score buffers the next S is ready when a group has finished a block, so the
+//   groups never wait in step and the exponential unit always has a group to serve.
+//   The output stays in tensor memory for the whole tile.  The reference value m of the
+//   exponentials is raised lazily (only when a score exceeds it by 2^8); in that rare case
+//   the group waits for the product before it and rescales O|l in place.
+//   A share of the exponentials (AT_POLY of every 8 pairs) is evaluated on the FMA pipe
+//   (range reduction + cubic), the rest on the exponential unit: with the products off
+//   the CUDA cores there are issue slots to spare, and the exponential unit is the
+//   bottleneck otherwise.
+// Tensor memory: 128 columns per group (S_0 in 0..47, S_1 in 48..95, each P over the first 24
+// columns of its S; O|l in 96..127).
 // Every mbarrier wait is bounded; a wait that runs out sets PTV3_STATUS_WAIT_LIMIT.
 //
-// Measured on B200 (407 000 points, C = 64, 4 heads): 0.65 ms against 0.57 ms of the
-// mma.sync kernel (attention_mma.cu), i.e. 2.6e12 against 2.9e12 exponentials per
-// second of the unit's 4.5e12.  Cycle stamps of one thread show why: a key block takes
-// a group ~2600 cycles, of which the exponentials are 1100-1300 (512 alone); every
-// round trip through an mbarrier (try_wait on a completed phase) or tensor memory
-// (tcgen05.ld / st + wait) costs 100-300 cycles, there are seven of them per block, and
-// only four groups fit in the 512 columns to hide them.  With the exponentials removed
-// altogether the kernel still takes 0.52 ms; moving a third of them to the FMA pipe or
-// staggering the groups changes nothing.  A CTA also spends ~15 % of its life in the
-// exposed K / V gather, which three co-resident CTAs hide in the mma.sync kernel.  The
-// automatic choice therefore stays with the mma.sync kernel.
+// Measured on B200 (240 000 points, C = 64, 4 heads): 0.45 ms against 0.32 ms of the mma.sync
+// kernel (attention_mma.cu), which therefore stays the automatic choice.  Cycle stamps of one
+// group against its issuer show what bounds this kernel: a key block takes a group ~2400
+// cycles whatever the softmax does (all exponentials on the exponential unit, three of eight
+// on the FMA pipe, or none at all), and the next S is seen one block period after the product
+// that makes it was issued.  The period is the tensor pipe working through the 16 products of
+// a round of the four groups (3 x P V' + 1 x Q K^T each): at head dimension 16 every product is
+// tiny (128 x 32 x 16 or 128 x 48 x 16), K is 16 per instruction by the instruction set, so
+// a (patch, head) pair needs ~690 of them at ~150 cycles each, whatever their size; the pipe's
+// time goes to per-instruction overhead, not to arithmetic (~10 % of its rate).  The mma.sync
+// kernel pays for its products with issue slots of the CUDA cores instead, which it has.
+// Earlier forms of this kernel (scores read back every block with the output in registers;
+// two passes with the exact maximum first; one score buffer) all ran at 0.42-0.49 ms for
+// the same reason.
 #include "common.cuh"
 #include "attention_mma.cuh"
 #include "mma_util.cuh"
@@ -51,28 +67,33 @@ constexpr int AT_WG = 4;                    // softmax groups of 128 threads
 constexpr int AT_SOFTMAX_THREADS = 128 * AT_WG;
 constexpr int AT_THREADS = AT_SOFTMAX_THREADS + 32 * AT_WG;   // + one issuing warp per group
 constexpr int AT_BM = 128;                  // query rows per tile
-constexpr int AT_BK = 64;                   // keys per block
+constexpr int AT_BK = 48;                   // keys per block (two score buffers of 48 columns)
+constexpr int AT_POLY = 3;                  // of every 8 pairs of exponentials, this many on the FMA pipe
+constexpr float AT_LAZY = 8.f;              // slack of the reference value, in powers of two
 constexpr int AT_D = 16;
+constexpr int AT_KV_BLOCK = 128;            // keys per gather block (one mbarrier each)
+constexpr int AT_KV_BLOCKS = ATTN_TC05_MAX_SEQLEN / AT_KV_BLOCK;
 constexpr float AT_LOG2E = 1.4426950408889634f;
 constexpr int AT_Q_BYTES = 128 * AT_D * 2;
-// tensor-memory columns of a group: S (fp32), P (bf16 pairs), R (16) + l (16)
-constexpr int AT_TM_S = 0, AT_TM_P = AT_BK, AT_TM_R = AT_BK + AT_BK / 2, AT_TMEM_GROUP = AT_TM_R + 32;
-static_assert(AT_TMEM_GROUP * AT_WG <= 512, "tensor memory holds 512 columns");
-// columns a CTA allocates (a power of two); 512 / AT_TMEM_COLS CTAs share an SM
-constexpr int AT_TMEM_COLS = AT_TMEM_GROUP * AT_WG <= 256 ? 256 : 512;
-constexpr int AT_CTAS_PER_SM = 512 / AT_TMEM_COLS;
+// tensor-memory columns of a group: two score buffers (P re-uses the first half of its S), O|l
+constexpr int AT_TM_S = 0, AT_TM_O = 2 * AT_BK, AT_TMEM_GROUP = 128;
+static_assert(AT_TM_O + 32 <= AT_TMEM_GROUP, "two score buffers and the output fit a group's columns");
+constexpr int AT_PAD_ROWS = AT_BK;          // zero rows behind the last 128-row block (key blocks of 48)
+constexpr int AT_TMEM_COLS = AT_TMEM_GROUP * AT_WG;
+static_assert(AT_TMEM_COLS == 512, "the CTA takes the whole tensor memory of its SM");
 // mbarriers of a group
-constexpr int AT_BAR_Q = 0, AT_BAR_S = 1, AT_BAR_SFREE = 2, AT_BAR_P = 3, AT_BAR_PV = 4, AT_BARS_PER_WG = 5;
-constexpr int AT_NBAR = AT_BARS_PER_WG * AT_WG;
+constexpr int AT_BAR_Q = 0, AT_BAR_S = 1 /* two */, AT_BAR_P = 3, AT_BAR_PV = 4, AT_BARS_PER_WG = 5;
+constexpr int AT_NBAR = AT_BARS_PER_WG * AT_WG + AT_KV_BLOCKS;
 
 // shared-memory map for a patch padded to lpad keys
 struct AtLayout {
     int off_k, off_v, off_q, off_bar, total;
     __host__ __device__ explicit AtLayout(int lpad)
     {
-        off_k = 0;                      // 2 planes of lpad 16-byte chunks
-        off_v = off_k + lpad * 32;      // 4 planes: V d 0-7, V d 8-15, the ones column, zeros
-        off_q = off_v + lpad * 64;
+        const int rows = lpad + AT_PAD_ROWS;
+        off_k = 0;                      // 2 planes of 16-byte chunks
+        off_v = off_k + rows * 32;      // 4 planes: V d 0-7, V d 8-15, the ones column, zeros
+        off_q = off_v + rows * 64;
         off_bar = off_q + AT_WG * AT_Q_BYTES;
         total = off_bar + 8 * AT_NBAR + 16;
     }
@@ -115,7 +136,84 @@ __device__ __forceinline__ uint32_t at_scale_bf16x2(uint32_t v, float s)
 
 __device__ __forceinline__ float max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 
-__global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kernel(
+// Packed fp32 pairs (two floats in one 64-bit register, one instruction for both).
+__device__ __forceinline__ uint64_t pack2(float x, float y)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t r, float& x, float& y)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(r));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// Constants of the exponentials, packed once per thread.
+struct AtExpConst {
+    uint64_t log2e, magic, neg_magic, neg_one, c3, c2, c1, one;
+    __device__ __forceinline__ AtExpConst()
+    {
+        log2e = pack2(AT_LOG2E, AT_LOG2E);
+        magic = pack2(12582912.f, 12582912.f);
+        neg_magic = pack2(-12582912.f, -12582912.f);
+        neg_one = pack2(-1.f, -1.f);
+        c3 = pack2(0.0555041086f, 0.0555041086f);
+        c2 = pack2(0.2402265070f, 0.2402265070f);
+        c1 = pack2(0.6931471806f, 0.6931471806f);
+        one = pack2(1.f, 1.f);
+    }
+};
+
+// 2^x for a pair on the FMA pipe: x = n + r with n integer (round to nearest, read off the low
+// mantissa bits after adding 1.5 * 2^23) and r in [-0.5, 0.5], 2^r by a cubic (relative error
+// 1e-4, far below the bf16 rounding that follows), n added to the exponent field.
+__device__ __forceinline__ uint32_t exp2_poly2_bf16(uint64_t x2, const AtExpConst& k)
+{
+    float x, y;
+    unpack2(x2, x, y);
+    x2 = pack2(fmaxf(x, -125.f), fmaxf(y, -125.f));
+    const uint64_t t2 = add2(x2, k.magic);
+    const uint64_t n2 = add2(t2, k.neg_magic);
+    const uint64_t r2 = fma2(n2, k.neg_one, x2);
+    uint64_t p2 = fma2(r2, k.c3, k.c2);
+    p2 = fma2(p2, r2, k.c1);
+    p2 = fma2(p2, r2, k.one);
+    float px, py, tx, ty;
+    unpack2(p2, px, py);
+    unpack2(t2, tx, ty);
+    px = __int_as_float(__float_as_int(px) + (__float_as_int(tx) << 23));
+    py = __int_as_float(__float_as_int(py) + (__float_as_int(ty) << 23));
+    return pack_bf16(px, py);
+}
+
+// waits until this thread's cp.async groups, except the newest `pending`, have landed
+__device__ __forceinline__ void cp_async_wait_pending(int pending)
+{
+    switch (pending) {
+        case 0: cp_async_wait<0>(); break;
+        case 1: cp_async_wait<1>(); break;
+        case 2: cp_async_wait<2>(); break;
+        case 3: cp_async_wait<3>(); break;
+        case 4: cp_async_wait<4>(); break;
+        case 5: cp_async_wait<5>(); break;
+        case 6: cp_async_wait<6>(); break;
+        default: cp_async_wait<7>(); break;
+    }
+}
+
+__global__ void __launch_bounds__(AT_THREADS, 1) attn_tc05_d16_kernel(
     const __nv_bfloat16* __restrict__ qkv, const int64_t* __restrict__ order,
     const int64_t* __restrict__ pad, const int64_t* __restrict__ unpad,
     const int32_t* __restrict__ cu_seqlens, __nv_bfloat16* __restrict__ out, int C, float scale,
@@ -142,8 +240,10 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
         return;
     }
     const int ntiles = (L + AT_BM - 1) / AT_BM;      // query tiles
-    const int nb = (L + AT_BK - 1) / AT_BK;          // key blocks
-    const int Lp = ntiles * AT_BM;                   // rows of the zero-padded K / V planes
+    const int nkv = ntiles;                          // gather blocks (128 keys, zero padded)
+    const int nb = (L + AT_BK - 1) / AT_BK;          // key blocks of pass 2
+    const int Lp = ntiles * AT_BM;                   // rows covered by the gather blocks
+    const int Lk = max(Lp, nb * AT_BK);              // rows of the zero-padded K / V planes
     const int tiles_per_slice = (ntiles + n_slices - 1) / n_slices;
     const int tile_lo = slice * tiles_per_slice;
     const int tile_hi = min(ntiles, tile_lo + tiles_per_slice);
@@ -154,90 +254,92 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + AT_NBAR);
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t bar0 = sbase + lay.off_bar;
+    const uint32_t kvbar0 = bar0 + 8 * AT_BARS_PER_WG * AT_WG;
 
     if (tid == 0) {
         for (int g = 0; g < AT_WG; ++g) {
             const uint32_t b = bar0 + 8 * AT_BARS_PER_WG * g;
-            mbar_init(b + 8 * AT_BAR_Q, 128);
+            mbar_init(b + 8 * AT_BAR_Q, 4);      // one arrival per warp of the group
             mbar_init(b + 8 * AT_BAR_S, 1);
-            mbar_init(b + 8 * AT_BAR_SFREE, 128);
-            mbar_init(b + 8 * AT_BAR_P, 128);
+            mbar_init(b + 8 * (AT_BAR_S + 1), 1);
             mbar_init(b + 8 * AT_BAR_PV, 1);
+            mbar_init(b + 8 * AT_BAR_P, 4);
         }
+        for (int b = 0; b < AT_KV_BLOCKS; ++b) mbar_init(kvbar0 + 8 * b, 32 * AT_WG);
         *abort = 0;
         fence_barrier_init();
     }
     if (warp == 0) tmem_alloc(sbase + lay.off_bar + 8 * AT_NBAR, AT_TMEM_COLS);
-
-    // ---- gather K and V of the whole patch into [d half][key] planes ------------
-    const uint32_t ks = sbase + lay.off_k, vs = sbase + lay.off_v;
-    const uint32_t plane = (uint32_t)Lp * 16;
-    const bool issuer = tid >= AT_SOFTMAX_THREADS;
-    const int wg = issuer ? warp - AT_SOFTMAX_THREADS / 32 : tid >> 7;
-    const int t = tid & 127;
-
-    // ---- gather K and V of the whole patch into [d chunk][key] planes; the chain
-    //      pad -> order -> row of every thread's (at most two) key rows and of its first
-    //      query row is walked level by level, so the loads of a level overlap --------------
-    static_assert(2 * AT_THREADS >= ATTN_TC05_MAX_SEQLEN, "two key rows per thread cover a patch");
-    const int r0 = tid, r1 = tid + AT_THREADS;
-    const bool g0 = r0 < L, g1 = r1 < L;
-    const int rq = (tile_lo + wg) * AT_BM + t;
-    const bool gq = !issuer && tile_lo + wg < tile_hi && rq < L;
-    // row numbers fit 32 bits (cu_seqlens is 32-bit); kept narrow to spare registers
-    const int pd0 = g0 ? (int)pad[start + r0] : 0, pd1 = g1 ? (int)pad[start + r1] : 0;
-    const int pdq = gq ? (int)pad[start + rq] : 0;
-    const int s0 = g0 ? (int)order[pd0] : 0, s1 = g1 ? (int)order[pd1] : 0;
-    const int sq = gq ? (int)order[pdq] : 0;
-    uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
-    if (gq) {
-        const uint4* qp = reinterpret_cast<const uint4*>(qkv + (int64_t)sq * row_stride + h * AT_D);
-        q0 = qp[0];
-        q1 = qp[1];
-    }
-#pragma unroll
-    for (int k = 0; k < 2; ++k) {
-        const int r = k ? r1 : r0;
-        if (r >= Lp) continue;
-        // V is extended by a column of ones (and seven of zeros, then a plane of zeros): the
-        // product P V' also yields the row sums of the rounded probabilities
-        *reinterpret_cast<uint4*>(smem + lay.off_v + 2 * plane + r * 16) = make_uint4(0x3f80u, 0, 0, 0);
-        *reinterpret_cast<uint4*>(smem + lay.off_v + 3 * plane + r * 16) = make_uint4(0, 0, 0, 0);
-        if (r < L) {
-            const __nv_bfloat16* kp = qkv + (int64_t)(k ? s1 : s0) * row_stride + C + h * AT_D;
-            cp_async16(ks + r * 16, kp);
-            cp_async16(ks + plane + r * 16, kp + 8);
-            cp_async16(vs + r * 16, kp + C);
-            cp_async16(vs + plane + r * 16, kp + C + 8);
-        } else {
-            const uint4 z = make_uint4(0, 0, 0, 0);
-            *reinterpret_cast<uint4*>(smem + lay.off_k + r * 16) = z;
-            *reinterpret_cast<uint4*>(smem + lay.off_k + plane + r * 16) = z;
-            *reinterpret_cast<uint4*>(smem + lay.off_v + r * 16) = z;
-            *reinterpret_cast<uint4*>(smem + lay.off_v + plane + r * 16) = z;
-        }
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    fence_proxy_async();
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
 
+    const uint32_t ks = sbase + lay.off_k, vs = sbase + lay.off_v;
+    const uint32_t plane = (uint32_t)Lk * 16;
+    const bool issuer = tid >= AT_SOFTMAX_THREADS;
+    const int wg = issuer ? warp - AT_SOFTMAX_THREADS / 32 : tid >> 7;
+    const int t = tid & 127;
+
     const uint32_t wbar = bar0 + 8 * AT_BARS_PER_WG * wg;
-    const uint32_t qbar = wbar + 8 * AT_BAR_Q, sbar = wbar + 8 * AT_BAR_S, sfree = wbar + 8 * AT_BAR_SFREE,
-                   pbar = wbar + 8 * AT_BAR_P, pvbar = wbar + 8 * AT_BAR_PV;
+    const uint32_t qbar = wbar + 8 * AT_BAR_Q, sbar = wbar + 8 * AT_BAR_S, pbar = wbar + 8 * AT_BAR_P,
+                   pvbar = wbar + 8 * AT_BAR_PV;
     const uint32_t tm_group = tmem_base + wg * AT_TMEM_GROUP;
 
     // The issuing warps (one whole warpgroup) need few registers; they hand theirs to the
-    // softmax warpgroups, which hold a block of scores per thread.  The kernel starts with
-    // 96 registers per thread (640 threads); the increase must fit in what the decrease
-    // releases, or it would wait for ever: 128 x (96 - 40) = 7168 >= 512 x (104 - 96) = 4096.
+    // softmax warpgroups.  The kernel starts with 96 registers per thread (640 threads); the
+    // increase must fit in what the decrease releases, or it would wait for ever:
+    // 128 x (96 - 64) = 4096 >= 512 x (104 - 96) = 4096.
     static_assert(AT_THREADS == 640, "the setmaxnreg budget below assumes 640 threads at 96 registers");
     static_assert(AT_WG == 4, "the issuing warps must form one warpgroup for setmaxnreg");
     if (issuer) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        // ---- gather: the 128 issuer threads own one key row of every 128-key block -----------
+        const int a = tid - AT_SOFTMAX_THREADS;     // 0..127
+        {
+            int src[AT_KV_BLOCKS];
+#pragma unroll
+            for (int b = 0; b < AT_KV_BLOCKS; ++b) {
+                const int r = b * AT_KV_BLOCK + a;
+                src[b] = (b < nkv && r < L) ? (int)pad[start + r] : -1;
+            }
+#pragma unroll
+            for (int b = 0; b < AT_KV_BLOCKS; ++b)
+                if (src[b] >= 0) src[b] = (int)order[src[b]];
+#pragma unroll
+            for (int b = 0; b < AT_KV_BLOCKS; ++b) {
+                if (b < nkv) {
+                    const int r = b * AT_KV_BLOCK + a;
+                    // V is extended by a column of ones (and seven of zeros, then a plane of zeros):
+                    // the product P V' also yields the row sums of the rounded probabilities
+                    *reinterpret_cast<uint4*>(smem + lay.off_v + 2 * plane + r * 16) = make_uint4(0x3f80u, 0, 0, 0);
+                    *reinterpret_cast<uint4*>(smem + lay.off_v + 3 * plane + r * 16) = make_uint4(0, 0, 0, 0);
+                    if (src[b] >= 0) {
+                        const __nv_bfloat16* kp = qkv + (int64_t)src[b] * row_stride + C + h * AT_D;
+                        cp_async16(ks + r * 16, kp);
+                        cp_async16(ks + plane + r * 16, kp + 8);
+                        cp_async16(vs + r * 16, kp + C);
+                        cp_async16(vs + plane + r * 16, kp + C + 8);
+                    } else {
+                        const uint4 z = make_uint4(0, 0, 0, 0);
+                        *reinterpret_cast<uint4*>(smem + lay.off_k + r * 16) = z;
+                        *reinterpret_cast<uint4*>(smem + lay.off_k + plane + r * 16) = z;
+                        *reinterpret_cast<uint4*>(smem + lay.off_v + r * 16) = z;
+                        *reinterpret_cast<uint4*>(smem + lay.off_v + plane + r * 16) = z;
+                    }
+                }
+                cp_async_commit();      // one group per block, empty ones included
+            }
+            // key blocks are 48 rows: the last one may reach behind the last gather block
+            if (Lp + a < Lk) {
+                const int r = Lp + a;
+                const uint4 z = make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int pl = 0; pl < 2; ++pl) *reinterpret_cast<uint4*>(smem + lay.off_k + pl * plane + r * 16) = z;
+#pragma unroll
+                for (int pl = 0; pl < 4; ++pl) *reinterpret_cast<uint4*>(smem + lay.off_v + pl * plane + r * 16) = z;
+            }
+        }
         // ---- one warp per group: waits for the group's mbarriers, lane 0 issues ----------
         const bool lead = (tid & 31) == 0;
         constexpr uint32_t IDESC_S = umma_idesc_bf16(128, AT_BK);
@@ -245,100 +347,136 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
         // S = Q K_j^T: A = Q planes [d half][row], B = K planes [d half][key]
         const uint64_t desc_q = umma_desc_plain(sbase + lay.off_q + wg * AT_Q_BYTES, AT_BM * 16, 128);
         const uint64_t desc_k = umma_desc_plain(ks, plane, 128);
-        // R|l = P V': A = P (tensor memory), B = V' planes [d chunk][key]
+        // O|l += P V': A = P (tensor memory), B = V' planes [d chunk][key]
         const uint64_t desc_v = umma_desc_plain(vs, 128, plane);
-        uint32_t qph = 0, fph = 0, pph = 0;
+        uint32_t qph = 0, pph = 0;
+        int landed = 0;      // gather blocks handed over so far
+        // this thread's copies of the gather blocks up to the one holding key row `row` have
+        // landed: tell the tensor-core proxy and the other issuing warps, then wait for theirs
+        auto land_upto = [&](int row) {
+            const int need = min(row / AT_KV_BLOCK, nkv - 1);
+            while (landed <= need) {
+                cp_async_wait_pending(AT_KV_BLOCKS - 1 - landed);
+                fence_proxy_async();
+                mbar_arrive(kvbar0 + 8 * landed);
+                mbar_wait(kvbar0 + 8 * landed, 0, abort);
+                ++landed;
+            }
+        };
+        auto issue_s = [&](int jj) {      // S_jj = Q K_jj^T into buffer jj & 1
+            // a descriptor's low word holds the address / 16: blocks are AT_BK chunks apart
+            umma_bf16(tm_group + AT_TM_S + (jj & 1) * AT_BK, desc_q, desc_k + (uint64_t)(jj * AT_BK), IDESC_S, false);
+            umma_commit(sbar + 8 * (jj & 1));
+        };
         for (int tile = tile_lo + wg; tile < tile_hi; tile += AT_WG) {
             mbar_wait(qbar, qph, abort);
             qph ^= 1;
+            land_upto(min(2, nb) * AT_BK - 1);
             if (lead) {
                 fence_after_sync();
-                umma_bf16(tm_group + AT_TM_S, desc_q, desc_k, IDESC_S, false);
-                umma_commit(sbar);
+                issue_s(0);
+                if (nb > 1) issue_s(1);
             }
+            __syncwarp();
             for (int j = 0; j < nb; ++j) {
-                mbar_wait(sfree, fph, abort);   // S_j is in the group's registers
-                fph ^= 1;
-                if (lead && j + 1 < nb) {
-                    fence_after_sync();
-                    // a descriptor's low word holds the address / 16: blocks are AT_BK chunks apart
-                    umma_bf16(tm_group + AT_TM_S, desc_q, desc_k + (uint64_t)((j + 1) * AT_BK), IDESC_S, false);
-                    umma_commit(sbar);
-                }
-                mbar_wait(pbar, pph, abort);    // P_j is in tensor memory, R_j-1 has been read
+                mbar_wait(pbar, pph, abort);    // P_j is in tensor memory (over the first half of S_j)
                 pph ^= 1;
+                if (j + 2 < nb) land_upto((j + 3) * AT_BK - 1);
                 if (lead) {
                     fence_after_sync();
                     const uint64_t dv = desc_v + (uint64_t)(j * AT_BK);
+                    const uint32_t tm_p = tm_group + AT_TM_S + (j & 1) * AT_BK;
 #pragma unroll
                     for (int i = 0; i < AT_BK / 16; ++i)
-                        umma_bf16_ts(tm_group + AT_TM_R, tm_group + AT_TM_P + 8 * i, dv + 16 * i, IDESC_R, i > 0);
+                        umma_bf16_ts(tm_group + AT_TM_O, tm_p + 8 * i, dv + 16 * i, IDESC_R, j > 0 || i > 0);
                     umma_commit(pvbar);
+                    // the next product into this buffer runs after the ones above, which read it
+                    if (j + 2 < nb) issue_s(j + 2);
                 }
                 __syncwarp();
             }
         }
+        const bool kv_landed = landed >= nkv;
+        if (!kv_landed) {
+            // a warp whose group has no tile in this CTA (or a patch shorter than its planes): its
+            // share of the gather still has to be handed over, the other issuing warps wait for it
+            for (int jb = landed; jb < nkv; ++jb) {
+                cp_async_wait_pending(AT_KV_BLOCKS - 1 - jb);
+                fence_proxy_async();
+                mbar_arrive(kvbar0 + 8 * jb);
+            }
+        }
+        cp_async_wait<0>();
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
         // ---- softmax groups: thread t owns query row t of the tile ---------------------
         unsigned char* qs_ptr = smem + lay.off_q + wg * AT_Q_BYTES;
         const uint32_t tm_lane = (uint32_t)((warp & 3) * 32) << 16;
-        const uint32_t tm_s = tm_group + tm_lane + AT_TM_S, tm_p = tm_group + tm_lane + AT_TM_P,
-                       tm_r = tm_group + tm_lane + AT_TM_R;
-        uint32_t sph = 0, pvph = 0;
+        const uint32_t tm_s0 = tm_group + tm_lane + AT_TM_S, tm_o = tm_group + tm_lane + AT_TM_O;
+        uint32_t sph0 = 0, sph1 = 0, pvph = 0;
+        const AtExpConst kexp;
 
-        int pd = pdq, src = sq;                      // of this tile's row
-        int pd_next = 0, src_next = 0;               // of the group's next tile, fetched ahead
+        // pad -> order -> q row of this thread's row in the group's NEXT tile is walked one level
+        // per key block while the current tile is computed
+        int pd = 0, src = 0, pd_next = 0, src_next = 0;
+        {
+            const int r = (tile_lo + wg) * AT_BM + t;
+            if (tile_lo + wg < tile_hi && r < L) {
+                pd = (int)pad[start + r];
+                src = (int)order[pd];
+            }
+        }
         for (int tile = tile_lo + wg; tile < tile_hi; tile += AT_WG) {
             const int r = tile * AT_BM + t;
             const bool ok = r < L;
             if (tile != tile_lo + wg) {
                 pd = pd_next;
                 src = src_next;
-                q0 = q1 = make_uint4(0, 0, 0, 0);
-                if (ok) {
-                    const uint4* qp = reinterpret_cast<const uint4*>(qkv + (int64_t)src * row_stride + h * AT_D);
-                    q0 = qp[0];
-                    q1 = qp[1];
-                }
+            }
+            uint4 q0 = make_uint4(0, 0, 0, 0), q1 = q0;
+            if (ok) {
+                const uint4* qp = reinterpret_cast<const uint4*>(qkv + (int64_t)src * row_stride + h * AT_D);
+                q0 = qp[0];
+                q1 = qp[1];
+                q0.x = at_scale_bf16x2(q0.x, scale); q0.y = at_scale_bf16x2(q0.y, scale);
+                q0.z = at_scale_bf16x2(q0.z, scale); q0.w = at_scale_bf16x2(q0.w, scale);
+                q1.x = at_scale_bf16x2(q1.x, scale); q1.y = at_scale_bf16x2(q1.y, scale);
+                q1.z = at_scale_bf16x2(q1.z, scale); q1.w = at_scale_bf16x2(q1.w, scale);
             }
             // used at the end of the tile only
             const bool own = ok && unpad[pd] == start + r;
             const int rn = r + AT_WG * AT_BM;
             const bool okn = tile + AT_WG < tile_hi && rn < L;
             if (okn) pd_next = (int)pad[start + rn];
-            if (ok) {
-                q0.x = at_scale_bf16x2(q0.x, scale); q0.y = at_scale_bf16x2(q0.y, scale);
-                q0.z = at_scale_bf16x2(q0.z, scale); q0.w = at_scale_bf16x2(q0.w, scale);
-                q1.x = at_scale_bf16x2(q1.x, scale); q1.y = at_scale_bf16x2(q1.y, scale);
-                q1.z = at_scale_bf16x2(q1.z, scale); q1.w = at_scale_bf16x2(q1.w, scale);
-            }
-            // every product that read the previous tile's Q has completed (its R was awaited)
+            // every product that read the previous tile's Q has completed (its O was awaited)
             *reinterpret_cast<uint4*>(qs_ptr + t * 16) = q0;
             *reinterpret_cast<uint4*>(qs_ptr + 2048 + t * 16) = q1;
             fence_proxy_async();
-            mbar_arrive(qbar);
+            // one arrival per warp: 128 arrivals on one mbarrier are 128 updates of one shared-memory
+            // word, one after the other
+            __syncwarp();
+            if ((tid & 31) == 0) mbar_arrive(qbar);
 
-            float m = -INFINITY, alpha_prev = 1.f, lsum = 0.f;
-            float o[AT_D];
-#pragma unroll
-            for (int i = 0; i < AT_D; ++i) o[i] = 0.f;
-
+            float m = -INFINITY;     // reference value of the exponentials (raw score units)
+            float mb = 0.f;          // -m * log2(e)
             for (int j = 0; j < nb; ++j) {
-                mbar_wait(sbar, sph, abort);
-                sph ^= 1;
+                const int buf = j & 1;
+                const uint32_t tm_s = tm_s0 + buf * AT_BK;
+                if (buf) {
+                    mbar_wait(sbar + 8, sph1, abort);
+                    sph1 ^= 1;
+                } else {
+                    mbar_wait(sbar, sph0, abort);
+                    sph0 ^= 1;
+                }
                 fence_after_sync();
                 float v[AT_BK];
                 {
-                    uint32_t (&u)[AT_BK] = reinterpret_cast<uint32_t (&)[AT_BK]>(v);
+                    uint32_t* u = reinterpret_cast<uint32_t*>(v);
 #pragma unroll
-                    for (int c = 0; c < AT_BK / 32; ++c)
-                        tmem_ld32(tm_s + 32 * c, reinterpret_cast<uint32_t (&)[32]>(u[32 * c]));
+                    for (int c = 0; c < AT_BK / 16; ++c) tmem_ld16(tm_s + 16 * c, u + 16 * c);
                     tmem_ld_wait();
                 }
-                // the scores are in registers: the next block's product may overwrite them
-                fence_before_sync();
-                mbar_arrive(sfree);
                 const int valid = L - j * AT_BK;
                 if (valid < AT_BK) {
 #pragma unroll
@@ -355,62 +493,85 @@ __global__ void __launch_bounds__(AT_THREADS, AT_CTAS_PER_SM) attn_tc05_d16_kern
                         mx3 = max3(mx3, v[i + 6], v[i + 7]);
                     }
                 }
-                // every block holds at least one real key, so the new maximum is finite
-                const float mn = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m);
-                const float alpha = fast_exp2((m - mn) * AT_LOG2E);
-                m = mn;
-                const float mb = m * AT_LOG2E;
-                uint32_t pk[AT_BK / 2];
+                // every block holds at least one real key, so the block maximum is finite
+                const float bm = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                const bool raise = (bm - m) * AT_LOG2E > AT_LAZY;     // always on the first block
+                // tensor-memory loads and stores are warp-wide: the rare rescaling is taken by the
+                // whole warp, with factor 1 for the rows that keep their reference value
+                bool pv_awaited = j == 0;
+                if (__any_sync(0xffffffffu, raise)) {
+                    const float mn = raise ? bm : m;
+                    if (j > 0) {
+                        // the product P_j-1 V' may still be running
+                        mbar_wait(pvbar, pvph, abort);
+                        pvph ^= 1;
+                        pv_awaited = true;
+                        fence_after_sync();
+                        const float alpha = raise ? fast_exp2((m - mn) * AT_LOG2E) : 1.f;
+                        uint32_t rr[32];
+                        tmem_ld32(tm_o, rr);
+                        tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < AT_BK / 2; ++i)
-                    pk[i] = pack_bf16(fast_exp2(fmaf(v[2 * i], AT_LOG2E, -mb)),
-                                      fast_exp2(fmaf(v[2 * i + 1], AT_LOG2E, -mb)));
-                if (j > 0) {
-                    // the previous block's P V has finished: its result can be read and the
-                    // probability columns rewritten
+                        for (int i = 0; i <= AT_D; ++i) rr[i] = __float_as_uint(__uint_as_float(rr[i]) * alpha);
+                        tmem_st32(tm_o, rr);
+                    }
+                    m = mn;
+                    mb = -m * AT_LOG2E;
+                }
+                uint32_t pk[AT_BK / 2];
+                const uint64_t mb2 = pack2(mb, mb);
+#pragma unroll
+                for (int i = 0; i < AT_BK / 2; ++i) {
+                    const uint64_t x2 = fma2(pack2(v[2 * i], v[2 * i + 1]), kexp.log2e, mb2);
+                    if ((i & 7) < AT_POLY) {
+                        pk[i] = exp2_poly2_bf16(x2, kexp);
+                    } else {
+                        float x, y;
+                        unpack2(x2, x, y);
+                        pk[i] = pack_bf16(fast_exp2(x), fast_exp2(y));
+                    }
+                }
+                // every block consumes one completion of the "P V done" barrier (of the block before
+                // it), here in the common case, where that product has long finished
+                if (!pv_awaited) {
                     mbar_wait(pvbar, pvph, abort);
                     pvph ^= 1;
-                    fence_after_sync();
-                    uint32_t rr[32];
-                    tmem_ld32(tm_r, rr);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < AT_D; ++i) o[i] = fmaf(o[i], alpha_prev, __uint_as_float(rr[i]));
-                    lsum = fmaf(lsum, alpha_prev, __uint_as_float(rr[16]));
                 }
-                alpha_prev = alpha;
+                // P over the first half of S_j (all of S_j is in registers)
 #pragma unroll
-                for (int c = 0; c < AT_BK / 64; ++c)
-                    tmem_st32(tm_p + 32 * c, reinterpret_cast<const uint32_t (&)[32]>(pk[32 * c]));
+                for (int c = 0; c < AT_BK / 16; ++c) tmem_st8(tm_s + 8 * c, pk + 8 * c);
                 tmem_st_wait();
                 fence_before_sync();
-                mbar_arrive(pbar);
+                __syncwarp();
+                if ((tid & 31) == 0) mbar_arrive(pbar);
                 // walk the next tile's pad -> order -> row chain one level per key block
                 if (j == 0 && okn) src_next = (int)order[pd_next];
                 if (j == 1 && okn)
                     asm volatile("prefetch.global.L2 [%0];" ::"l"(qkv + (int64_t)src_next * row_stride + h * AT_D));
             }
-            mbar_wait(pvbar, pvph, abort);
+            mbar_wait(pvbar, pvph, abort);      // the last product of the tile
             pvph ^= 1;
             fence_after_sync();
             {
                 uint32_t rr[32];
-                tmem_ld32(tm_r, rr);
+                tmem_ld32(tm_o, rr);
                 tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < AT_D; ++i) o[i] = fmaf(o[i], alpha_prev, __uint_as_float(rr[i]));
-                lsum = fmaf(lsum, alpha_prev, __uint_as_float(rr[16]));
-            }
-            if (ok && own) {
-                const float inv = 1.f / lsum;
-                uint4 w0, w1;
-                w0.x = pack_bf16(o[0] * inv, o[1] * inv);   w0.y = pack_bf16(o[2] * inv, o[3] * inv);
-                w0.z = pack_bf16(o[4] * inv, o[5] * inv);   w0.w = pack_bf16(o[6] * inv, o[7] * inv);
-                w1.x = pack_bf16(o[8] * inv, o[9] * inv);   w1.y = pack_bf16(o[10] * inv, o[11] * inv);
-                w1.z = pack_bf16(o[12] * inv, o[13] * inv); w1.w = pack_bf16(o[14] * inv, o[15] * inv);
-                uint4* op = reinterpret_cast<uint4*>(out + (int64_t)src * C + h * AT_D);
-                op[0] = w0;
-                op[1] = w1;
+                // the next tile's first product overwrites these columns; it is issued only after
+                // this thread's arrival on the Q barrier, which comes after this load
+                fence_before_sync();
+                if (own) {
+                    const float inv = 1.f / __uint_as_float(rr[16]);
+                    uint4 w0, w1;
+#define AT_O(i) (__uint_as_float(rr[i]) * inv)
+                    w0.x = pack_bf16(AT_O(0), AT_O(1));   w0.y = pack_bf16(AT_O(2), AT_O(3));
+                    w0.z = pack_bf16(AT_O(4), AT_O(5));   w0.w = pack_bf16(AT_O(6), AT_O(7));
+                    w1.x = pack_bf16(AT_O(8), AT_O(9));   w1.y = pack_bf16(AT_O(10), AT_O(11));
+                    w1.z = pack_bf16(AT_O(12), AT_O(13)); w1.w = pack_bf16(AT_O(14), AT_O(15));
+#undef AT_O
+                    uint4* op = reinterpret_cast<uint4*>(out + (int64_t)src * C + h * AT_D);
+                    op[0] = w0;
+                    op[1] = w1;
+                }
             }
         }
     }
@@ -436,24 +597,24 @@ int launch_attn_tc05(const void* qkv, const int64_t* order, const int64_t* pad, 
 {
     const int lpad = (max_seqlen + AT_BM - 1) / AT_BM * AT_BM;
     const AtLayout lay(lpad);
-    // Each CTA takes 1 / AT_CTAS_PER_SM of tensor memory: ask for enough shared memory that no
-    // more than that many CTAs share an SM (one more would wait in tcgen05.alloc).
-    const size_t floor_smem = (size_t)(228 * 1024 / (AT_CTAS_PER_SM + 1) + 1024);
+    // A CTA takes the whole tensor memory of its SM: ask for enough shared memory that no
+    // second CTA shares the SM (it would wait in tcgen05.alloc).
+    const size_t floor_smem = (size_t)(228 * 1024 / 2 + 1024);
     const size_t smem = lay.total + 128 < floor_smem ? floor_smem : (size_t)lay.total + 128;
     if (cudaFuncSetAttribute(attn_tc05_d16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
         return check_launch("ptv3_attention_fwd: shared memory attribute");
     // Query tiles of a patch can be sliced over CTAs (each gathers K and V again).  Pick the
     // slicing with the shortest estimated time: waves of 148 CTAs, each taking one gather
-    // (about 0.3 of a tile pair) plus its tile pairs.
+    // (about 0.2 of a tile round) plus its rounds of up to four tiles.
     const int tiles = lpad / AT_BM;
     const long pairs = (long)n_seq * H;
     int qsplit = 1;
     double best = 0;
     for (int q = 1; q <= tiles; q *= 2) {
         const long waves = (pairs * q + 147) / 148;
-        const int tile_pairs = ((tiles + q - 1) / q + AT_WG - 1) / AT_WG;
-        const double cost = (double)waves * (tile_pairs + 0.3);
+        const int rounds = ((tiles + q - 1) / q + AT_WG - 1) / AT_WG;
+        const double cost = (double)waves * (rounds + 0.2);
         if (q == 1 || cost < best) {
             best = cost;
             qsplit = q;
@@ -467,3 +628,4 @@ int launch_attn_tc05(const void* qkv, const int64_t* order, const int64_t* pad, 
 }
 
 }  // namespace ptv3
+
