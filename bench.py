@@ -10,6 +10,13 @@ so the data path has no collective (`--gather-outputs` adds an NCCL all-gather o
 the output features to every step, for a caller that wants them on every rank).
 One JSON line is printed by rank 0.
 
+The same line carries a second measurement under "lidar16": one batch of 16
+LiDAR-like scenes (grid 0.05 m, four input channels) sharded over the N GPUs by
+scene (16 / N scenes per GPU: strong scaling), with the batch-global
+serialization depth and the output features of all scenes gathered on every
+rank over NCCL inside the step, on a side stream that overlaps the next step's
+forward.  `--no-lidar` skips it.
+
 `--impl reference` times the CPU restatement of the reference path (the oracle)
 on the host cores, on a bounded sample of the same workload.
 """
@@ -33,6 +40,8 @@ SCENES_PER_GPU = 4
 TARGET_VOXELS = 100_000
 GRID = 0.02
 CPU_SAMPLE_VOXELS = 100_000
+LIDAR_SCENES = 16
+LIDAR_GRID = 0.05
 # DRAM read + write bytes per row and channel of one attention launch (ncu, dram__bytes_read.sum +
 # dram__bytes_write.sum of a single launch on 240 640 rows x 64 channels gathered through a random
 # permutation, the least local case)
@@ -44,7 +53,9 @@ def workload_config(n_gpus, gather=False):
                         "%d synthetic indoor scenes of ~100k voxels per GPU, grid 0.02" % SCENES_PER_GPU,
             "scenes_per_gpu": SCENES_PER_GPU, "parallelism": "scene-parallel x%d, %s" % (
                 n_gpus, "outputs all-gathered" if gather else "no data-path collective"),
-            "l2": "256 MiB buffer written between timed steps (outside the per-step events)"}
+            "l2": "256 MiB buffer written between timed steps (outside the per-step events)",
+            "second_workload": "lidar16: 16 LiDAR-like scenes sharded by scene with the outputs gathered over "
+                               "NCCL (strong scaling), reported under the key of that name"}
 
 
 # --------------------------------------------------------------------------- #
@@ -179,6 +190,8 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # the gather runs beside the next forward: give NCCL's stream priority over it
+        os.environ.setdefault("TORCH_NCCL_HIGH_PRIORITY", "1")
         dist.init_process_group("nccl", device_id=dev)
         # One launching thread per rank: give every rank its own slice of the host cores, so that
         # the ranks' Python threads and the driver's helper threads do not migrate onto each other
@@ -289,6 +302,89 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), t0, t1
 
+    def run_lidar():
+        """16 LiDAR-like scenes sharded over the ranks by scene; returns the "lidar16" entry."""
+        lo, hi = distributed.shard_scenes(LIDAR_SCENES, rank, world)
+        scenes = [synthetic.lidar_scene(s, LIDAR_GRID) for s in range(lo, hi)]
+        shard = synthetic.make_batch(scenes, 1, lo, torch.bfloat16)
+        n_local = int(shard["offset"][-1])
+        shard_dev = {k: v.to(dev) for k, v in shard.items()}
+        # batch-global quantities, fixed for a sensor and a grid size: made once, outside the steps
+        depth = distributed.global_depth(shard_dev["grid_coord"])
+        counts_t = torch.tensor([n_local], dtype=torch.int64, device=dev)
+        all_counts = [n_local]
+        if world > 1:
+            buf = torch.empty(world, dtype=torch.int64, device=dev)
+            dist.all_gather_into_tensor(buf, counts_t)
+            all_counts = buf.tolist()
+        total = sum(all_counts)
+        torch.manual_seed(0)
+        net4 = PointTransformerV3(in_channels=4).eval().to(dev).bfloat16()
+        side = torch.cuda.Stream(device=dev)
+        steps_l, warm_l = min(args.steps, 10), 3
+
+        def run(n_steps, with_gather):
+            """n_steps forwards back to back; the gather of step i runs on the side stream while
+            step i + 1 computes; the timed region ends when the last gather has landed."""
+            main = torch.cuda.current_stream()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            start.record(main)
+            for _ in range(n_steps):
+                with torch.inference_mode():
+                    torch.manual_seed(1)
+                    d = dict(shard_dev)
+                    d["serialization_depth"] = depth
+                    feat = net4(d).feat
+                    if with_gather and world > 1:
+                        out, _, ev = distributed.gather_features(feat, counts=all_counts, stream=side)
+            main.wait_stream(side)
+            end.record(main)
+            barrier()
+            t = torch.tensor([start.elapsed_time(end)], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        def gather_alone(n_steps):
+            with torch.inference_mode():
+                torch.manual_seed(1)
+                d = dict(shard_dev)
+                d["serialization_depth"] = depth
+                feat = net4(d).feat
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            a.record()
+            for _ in range(n_steps):
+                distributed.gather_features(feat, counts=all_counts)
+            b.record()
+            barrier()
+            t = torch.tensor([a.elapsed_time(b) / n_steps], dtype=torch.float64, device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        run(warm_l, True)
+        ms_g = run(steps_l, True)
+        ms_n = run(steps_l, False)
+        g_ms = gather_alone(5) if world > 1 else 0.0
+        del net4
+        return {
+            "workload": "full PTv3 backbone forward, default config, in_channels 4, bf16 eval, random init; one "
+                        "batch of %d synthetic LiDAR-like scenes (two 64-beam sweeps each, grid %.2f), sharded "
+                        "over the GPUs by scene, batch-global serialization depth" % (LIDAR_SCENES, LIDAR_GRID),
+            "scaling": "strong", "scenes_per_gpu": hi - lo, "points_total": total, "points_per_gpu": all_counts,
+            "serialization_depth": depth, "steps": steps_l, "warmup": warm_l,
+            "value": total * steps_l / (ms_g * 1e-3), "unit": UNIT, "ms_per_step": ms_g / steps_l,
+            "value_without_gather": total * steps_l / (ms_n * 1e-3), "ms_per_step_without_gather": ms_n / steps_l,
+            "gather_ms": g_ms,
+            "collective": ("none (one GPU holds every scene)" if world == 1 else
+                           "uneven all-gather of the (N_total, 64) bf16 output features to every rank: one "
+                           "grouped launch of %d ncclBroadcast, received in place, on a side stream that "
+                           "overlaps the next step's forward" % world),
+            "gathered_bytes_per_step": total * 64 * 2,
+        }
+
     for _ in range(max(args.warmup, 3)):
         step_resident()
     sampler = ClockSampler(local) if rank == 0 else None
@@ -314,6 +410,11 @@ def run_ours(args):
     if not args.no_e2e:
         run_e2e(2)
         ms_e2e = run_e2e(args.steps)
+
+    lidar = None
+    if not args.no_lidar:
+        torch.cuda.empty_cache()
+        lidar = run_lidar()
 
     total_points = torch.tensor([n_points], dtype=torch.float64, device=dev)
     if world > 1:
@@ -366,6 +467,7 @@ def run_ours(args):
             "gpu_launches": int(launches),
             "roofline": roofline,
             "kernel_ms_per_step": breakdown,
+            "lidar16": lidar,
             "kernel_ms_note": "second pass on the per-operator host path (one event pair per operator); the "
                               "timed steps queue a whole block per C call and carry no events inside",
         }
@@ -632,6 +734,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
+    ap.add_argument("--no-lidar", action="store_true", help="skip the sharded LiDAR-like batch (\"lidar16\")")
     ap.add_argument("--gather-outputs", action="store_true",
                     help="N > 1: all-gather the output features over NCCL inside every step")
     ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "linear", "pooling", "seghead"],

@@ -36,25 +36,60 @@ def global_depth(grid_coord, group=None):
     return max(int(m.item()).bit_length(), 1)
 
 
-def gather_features(feat, group=None):
-    """All-gathers per-rank feature matrices of different lengths.
+def gather_features(feat, counts=None, group=None, stream=None):
+    """All-gathers per-rank feature matrices of different lengths into one matrix, rows in
+    rank order, on every rank.
 
-    Returns (features of all ranks concatenated in rank order, list of row
-    counts).  Rows are padded to the longest rank for one all_gather_into_tensor
-    over NCCL; the padding is dropped afterwards."""
+    Every rank's rows are received straight into their place in the result (NCCL: one
+    grouped launch of one broadcast per rank; other backends: the same broadcasts one by
+    one), so nothing is padded and nothing is copied afterwards.
+
+    counts: the row counts of all ranks, when the caller knows them (scene sizes are host
+    metadata of the batch); without them they are exchanged first, which costs one small
+    all-gather and a host read.
+    stream: a CUDA stream to run the collective on, so that it overlaps work queued later on
+    the current stream (the next forward).  The collective waits for the work queued on the
+    current stream so far.  With a stream the function returns (features, counts, event);
+    wait for the event (``torch.cuda.current_stream().wait_event(event)``) before using the
+    features.  Without one it returns (features, counts), ready for the current stream."""
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
-        return feat, [feat.shape[0]]
+        counts = [feat.shape[0]]
+        if stream is None:
+            return feat, counts
+        event = torch.cuda.Event()
+        event.record(torch.cuda.current_stream())
+        return feat, counts, event
     world = dist.get_world_size(group)
-    n = torch.tensor([feat.shape[0]], dtype=torch.int64, device=feat.device)
-    counts = torch.empty(world, dtype=torch.int64, device=feat.device)
-    dist.all_gather_into_tensor(counts, n, group=group)
-    counts = counts.tolist()
-    longest = max(counts)
-    send = feat
-    if feat.shape[0] != longest:
-        send = torch.zeros((longest,) + tuple(feat.shape[1:]), dtype=feat.dtype, device=feat.device)
-        send[: feat.shape[0]] = feat
-    recv = torch.empty((world * longest,) + tuple(feat.shape[1:]), dtype=feat.dtype, device=feat.device)
-    dist.all_gather_into_tensor(recv, send.contiguous(), group=group)
-    parts = [recv[r * longest: r * longest + counts[r]] for r in range(world)]
-    return torch.cat(parts), counts
+    rank = dist.get_rank(group)
+    if counts is None:
+        n = torch.tensor([feat.shape[0]], dtype=torch.int64, device=feat.device)
+        all_n = torch.empty(world, dtype=torch.int64, device=feat.device)
+        dist.all_gather_into_tensor(all_n, n, group=group)
+        counts = all_n.tolist()
+    counts = [int(c) for c in counts]
+    if counts[rank] != feat.shape[0]:
+        raise ValueError("rank %d holds %d rows, counts say %d" % (rank, feat.shape[0], counts[rank]))
+    feat = feat.contiguous()
+
+    def run():
+        out = torch.empty((sum(counts),) + tuple(feat.shape[1:]), dtype=feat.dtype, device=feat.device)
+        views = list(out.split(counts))
+        if dist.get_backend(group) == "nccl":
+            # rows differ per rank: torch issues this as one group of broadcasts
+            dist.all_gather(views, feat, group=group)
+        else:
+            views[rank].copy_(feat)
+            for r in range(world):
+                src = dist.get_global_rank(group, r) if group is not None else r
+                dist.broadcast(views[r], src=src, group=group)
+        return out
+
+    if stream is None:
+        return run(), counts
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        out = run()
+        event = torch.cuda.Event()
+        event.record(stream)
+    feat.record_stream(stream)
+    return out, counts, event

@@ -38,6 +38,14 @@ def _worker(rank, world, port, out):
         assert mine["feat"].shape[0] == sum(counts[lo:hi])
         depth = D.global_depth(mine["grid_coord"])
         feats, rows = D.gather_features(mine["feat"] + 100 * rank)
+        # the same with the counts supplied by the caller (no exchange of sizes)
+        feats2, rows2 = D.gather_features(mine["feat"] + 100 * rank, counts=[12, 3])
+        assert rows2 == rows and torch.equal(feats, feats2)
+        try:
+            D.gather_features(mine["feat"], counts=[1, 1])
+            raise AssertionError("wrong counts must be refused")
+        except ValueError:
+            pass
         out.put((rank, lo, hi, depth, rows, feats.clone()))
     finally:
         dist.destroy_process_group()

@@ -39,6 +39,12 @@ def _worker(rank, world, port, q):
             torch.manual_seed(7)                      # same shuffle draws on every rank
             feat = net(mine).feat
             gathered, rows = D.gather_features(feat)
+            # the same on a side stream with the counts known up front
+            side = torch.cuda.Stream()
+            g2, rows2, ev = D.gather_features(feat, counts=rows, stream=side)
+            torch.cuda.current_stream().wait_event(ev)
+            g2.record_stream(torch.cuda.current_stream())
+            assert rows2 == rows and torch.equal(g2, gathered)
         if rank == 0:
             q.put((gathered.cpu(), rows))
     finally:
