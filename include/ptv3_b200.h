@@ -221,13 +221,14 @@ int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight,
  * output voxels by every offset that any of them has; on coarse levels most of
  * those rows are zero).  ptv3_conv_pairs_build lists, offset by offset, the pairs
  * (nbr[o][j], j) with nbr[o][j] >= 0; ptv3_subm_conv_pairs_fwd multiplies 128
- * pairs of one offset at a time and accumulates in fp32 with atomics, so the
- * summation order (and the last bit of the result) can differ between runs.
+ * pairs of one offset at a time and accumulates with atomics in 64-bit fixed
+ * point (32 fractional bits): integer sums do not depend on the order of the
+ * additions, so the result is the same bit for bit on every run.
  * Replaces spconv's gather-GEMM-scatter behind model.py:546-552.
  *   nbr, row_order   as for ptv3_subm_conv_fwd (pair_out = row_order[j] when given)
  *   pair_in/out      kernel_volume * n int32 each (upper bound)
  *   off_start, tile_start   kernel_volume + 1 int32 each (device)
- *   workspace (conv) n x c_out floats
+ *   workspace (conv) n x c_out 64-bit integers (8 bytes each)
  */
 size_t ptv3_conv_pairs_workspace_bytes(int64_t n, int kernel_volume);
 int ptv3_conv_pairs_build(const int32_t* nbr, const int64_t* row_order, int64_t n, int kernel_volume,

@@ -169,7 +169,7 @@ static size_t carve_block(const ptv3_block_args* a, void* base, BlockBuffers* b)
     t.att = t.x;   // the convolution output is dead once f1 exists
     t.f2 = c.take<char>(n * row);
     t.hidden = fused_mlp ? nullptr : c.take<char>(n * (size_t)a->hidden * 2);
-    t.acc32 = a->pair_in ? c.take<char>(n * (size_t)a->channels * 4) : nullptr;
+    t.acc32 = a->pair_in ? c.take<char>(n * (size_t)a->channels * 8) : nullptr;
     t.lt = c.take<char>(BLOCK_LT_WORKSPACE);
     if (b) *b = t;
     return c.off;
@@ -222,7 +222,7 @@ extern "C" int ptv3_block_fwd(const ptv3_block_args* a, void* stream_)
     // xCPE convolution
     if (a->pair_in)
         STEP(ptv3_subm_conv_pairs_fwd(a->conv_in, a->pair_in, a->pair_out, a->off_start, a->tile_start,
-                                      a->conv_weight, a->conv_bias, b.x, b.acc32, (size_t)n * C * 4, n, C, C, 27,
+                                      a->conv_weight, a->conv_bias, b.x, b.acc32, (size_t)n * C * 8, n, C, C, 27,
                                       dt, stream_));
     else
         STEP(ptv3_subm_conv_fwd(a->conv_in, a->nbr, a->conv_weight, a->conv_bias, b.x, a->row_order, n, C, C, 27,

@@ -21,6 +21,7 @@ namespace ptv3 {
 
 constexpr int CM_MAX_KVOL = 27;
 constexpr int CM_STAGES = 3;
+constexpr float CM_FIXED_ONE = 4294967296.f;    // 2^32: scale of the fixed-point accumulation
 
 // physical 16-byte chunk of logical chunk c in row r for rows of NCH chunks
 template <int NCH>
@@ -35,15 +36,20 @@ __device__ __forceinline__ int swz(int r, int c)
 // stage; WM x WN warps
 // PAIRS: instead of 128 output voxels and all their offsets, a CTA owns 128
 // (input row, output row) pairs of ONE offset from an offset-sorted pair list and
-// adds its products into an fp32 buffer with atomics (no zero rows are multiplied;
-// used for the coarse levels, where tiles are not planar and most of the 27
-// offsets of an output-stationary tile would be half empty).
+// adds its products into an accumulation buffer with atomics (no zero rows are
+// multiplied; used for the coarse levels, where tiles are not planar and most of
+// the 27 offsets of an output-stationary tile would be half empty).  The buffer
+// holds 64-bit fixed-point numbers (32 fractional bits): integer addition is
+// associative, so the sum does not depend on the order in which the CTAs arrive
+// and the result is the same bit for bit on every run.  Every tile's fp32 product
+// is rounded to 2^-32 once (absolute error below 1.2e-10 per contribution; values
+// up to 2^31 in magnitude are representable, beyond that the conversion saturates).
 struct PairList {
     const int32_t* pair_in;     // input row of every pair, sorted by offset
     const int32_t* pair_out;    // output row of every pair
     const int32_t* off_start;   // kvol + 1: first pair of every offset
     const int32_t* tile_start;  // kvol + 1: first 128-pair tile of every offset
-    float* out32;               // n x cout accumulation buffer (zeroed by the launcher)
+    long long* acc;             // n x cout fixed-point accumulation buffer (zeroed by the launcher)
 };
 
 template <int CM_TM, int CN, int KC, int WM, int WN, bool PAIRS>
@@ -204,12 +210,14 @@ __global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
             const int64_t v = rows_s[r];
             if (v < 0) continue;
             if (PAIRS) {
-                float* op32 = pl.out32 + v * (int64_t)cout + col0 + wn * WTN;
+                long long* op64 = pl.acc + v * (int64_t)cout + col0 + wn * WTN;
 #pragma unroll
-                for (int b = 0; b < NT; ++b)
-                    asm volatile("red.global.add.v2.f32 [%0], {%1, %2};" ::"l"(op32 + b * 8 + 2 * t),
-                                 "f"(acc[a][b][half * 2]), "f"(acc[a][b][half * 2 + 1])
-                                 : "memory");
+                for (int b = 0; b < NT; ++b) {
+                    const long long f0 = __float2ll_rn(acc[a][b][half * 2] * CM_FIXED_ONE);
+                    const long long f1 = __float2ll_rn(acc[a][b][half * 2 + 1] * CM_FIXED_ONE);
+                    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(op64 + b * 8 + 2 * t), "l"(f0) : "memory");
+                    asm volatile("red.global.add.u64 [%0], %1;" ::"l"(op64 + b * 8 + 2 * t + 1), "l"(f1) : "memory");
+                }
                 continue;
             }
             __nv_bfloat16* op = out + v * (int64_t)cout + col0 + wn * WTN;
@@ -257,15 +265,20 @@ static int launch_one(const void* feat, const int32_t* nbr, const void* weight, 
     return check_launch("ptv3_subm_conv_fwd");
 }
 
-// out = bf16(out32 + bias)
-__global__ void __launch_bounds__(256) conv_pairs_finalize_kernel(const float* __restrict__ acc,
+// out = bf16(acc * 2^-32 + bias)
+__global__ void __launch_bounds__(256) conv_pairs_finalize_kernel(const long long* __restrict__ acc,
                                                                   const __nv_bfloat16* __restrict__ bias,
                                                                   __nv_bfloat16* __restrict__ out, int64_t total,
                                                                   int cout)
 {
     const int64_t i = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 4;
     if (i >= total) return;
-    const float4 v = *reinterpret_cast<const float4*>(acc + i);
+    const longlong2 lo = *reinterpret_cast<const longlong2*>(acc + i);
+    const longlong2 hi = *reinterpret_cast<const longlong2*>(acc + i + 2);
+    constexpr float inv = 1.f / CM_FIXED_ONE;
+    // (the integer is split so that the conversion to fp32 rounds once, at 24 bits of the value)
+    const float4 v = make_float4((float)((double)lo.x * inv), (float)((double)lo.y * inv),
+                                 (float)((double)hi.x * inv), (float)((double)hi.y * inv));
     const int c = (int)(i % cout);
     float b0 = 0.f, b1 = 0.f, b2 = 0.f, b3 = 0.f;
     if (bias) {
@@ -287,21 +300,22 @@ bool conv_pairs_supported(int c_in, int c_out, int kernel_volume)
 
 int launch_conv_pairs(const void* feat, const int32_t* pair_in, const int32_t* pair_out,
                       const int32_t* off_start, const int32_t* tile_start, int64_t max_tiles,
-                      const void* weight, const void* bias, void* out, float* out32, int64_t n, int c_in,
+                      const void* weight, const void* bias, void* out, long long* acc, int64_t n, int c_in,
                       int c_out, int kvol, cudaStream_t stream)
 {
     constexpr size_t smem = conv_mma_smem<128, 128, 64>();
     auto kern = conv_mma_kernel<128, 128, 64, 4, 2, true>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_subm_conv_pairs_fwd: shared memory attribute");
-    cudaMemsetAsync(out32, 0, (size_t)n * c_out * sizeof(float), stream);
-    const PairList pl{pair_in, pair_out, off_start, tile_start, out32};
+    if (cudaMemsetAsync(acc, 0, (size_t)n * c_out * sizeof(long long), stream) != cudaSuccess)
+        return check_launch("ptv3_subm_conv_pairs_fwd: memset");
+    const PairList pl{pair_in, pair_out, off_start, tile_start, acc};
     kern<<<dim3((unsigned)max_tiles, c_out / 128), 256, smem, stream>>>(
         (const __nv_bfloat16*)feat, nullptr, (const __nv_bfloat16*)weight, nullptr, nullptr, nullptr, n, c_in,
         c_out, kvol, pl);
     const int64_t total = n * (int64_t)c_out;
     conv_pairs_finalize_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(
-        out32, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, total, c_out);
+        acc, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, total, c_out);
     count_launches(2);
     return check_launch("ptv3_subm_conv_pairs_fwd");
 }

@@ -14,12 +14,12 @@ int launch_conv_mma(const void* feat, const int32_t* nbr, const void* weight, co
                     int kernel_volume, cudaStream_t stream);
 
 // Pair-list form (coarse levels): pairs sorted by kernel offset, 128-pair tiles,
-// fp32 atomic accumulation into out32 (n x c_out floats of workspace), then
+// atomic fixed-point accumulation into acc (n x c_out 64-bit integers of workspace), then
 // bias + rounding into out.
 bool conv_pairs_supported(int c_in, int c_out, int kernel_volume);
 int launch_conv_pairs(const void* feat, const int32_t* pair_in, const int32_t* pair_out,
                       const int32_t* off_start, const int32_t* tile_start, int64_t max_tiles,
-                      const void* weight, const void* bias, void* out, float* out32, int64_t n, int c_in,
+                      const void* weight, const void* bias, void* out, long long* acc, int64_t n, int c_in,
                       int c_out, int kernel_volume, cudaStream_t stream);
 
 }  // namespace ptv3

@@ -108,14 +108,14 @@ extern "C" int ptv3_subm_conv_pairs_fwd(const void* feat, const int32_t* pair_in
     if (n == 0) return PTV3_OK;
     PTV3_REQUIRE(feat && pair_in && pair_out && off_start && tile_start && weight && out && workspace,
                  PTV3_ERR_INVALID_ARGUMENT, "ptv3_subm_conv_pairs_fwd: null pointer");
-    PTV3_REQUIRE(workspace_bytes >= (size_t)n * c_out * sizeof(float), PTV3_ERR_WORKSPACE,
+    PTV3_REQUIRE(workspace_bytes >= (size_t)n * c_out * sizeof(long long), PTV3_ERR_WORKSPACE,
                  "ptv3_subm_conv_pairs_fwd: workspace %zu < %zu bytes", workspace_bytes,
-                 (size_t)n * c_out * sizeof(float));
+                 (size_t)n * c_out * sizeof(long long));
     PTV3_REQUIRE((((uintptr_t)feat | (uintptr_t)weight | (uintptr_t)workspace) & 15) == 0,
                  PTV3_ERR_INVALID_ARGUMENT, "ptv3_subm_conv_pairs_fwd: tensors must be 16-byte aligned");
     // every offset ends with at most one partial tile
     const int64_t max_tiles = (n * kernel_volume + 127) / 128 + kernel_volume;
     return launch_conv_pairs(feat, pair_in, pair_out, off_start, tile_start, max_tiles, weight, bias, out,
-                             static_cast<float*>(workspace), n, c_in, c_out, kernel_volume,
+                             static_cast<long long*>(workspace), n, c_in, c_out, kernel_volume,
                              (cudaStream_t)stream);
 }

@@ -455,7 +455,7 @@ def subm_conv_pairs(feat, pairs, weight, bias=None):
     n, cin = feat.shape
     cout = weight.shape[0]
     out = torch.empty((n, cout), dtype=feat.dtype, device=feat.device)
-    nbytes = n * cout * 4
+    nbytes = n * cout * 8
     ws = _lib.workspace(nbytes, feat.device)
     with timed("subm_conv_pairs", 2.0 * n * pairs["kvol"] * cin * cout):
         _lib.check(lib.ptv3_subm_conv_pairs_fwd(

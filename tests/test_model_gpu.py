@@ -437,11 +437,13 @@ def test_forward_with_host_metadata_and_deferred_status():
 
 @pytest.mark.gpu
 def test_repeated_passes_over_changing_batches_are_bit_identical():
-    """Batches of different shapes interleaved and repeated: with the atomic pair-list
-    convolution switched off every kernel is deterministic, so any difference between
+    """Batches of different shapes interleaved and repeated, on the default path: every kernel
+    is deterministic (the pair-list convolution of the coarse levels accumulates in fixed
+    point, whose sums do not depend on the order of the atomics), so any difference between
     repeats would be a hazard between the planning stream, the feature stream and the
     allocator (plans are made two stages ahead on a second stream)."""
     from pointtransformerv3_b200 import sparse
+    assert sparse.PAIR_PATH_MAX_VOXELS > 0, "the pair-list convolution must be part of this test"
     torch.manual_seed(0)
     net = P.PointTransformerV3(in_channels=6).eval().cuda().bfloat16()
     batches = []
@@ -455,12 +457,23 @@ def test_repeated_passes_over_changing_batches_are_bit_identical():
             torch.manual_seed(1)
             return net(dict(d)).feat
 
-    keep = sparse.PAIR_PATH_MAX_VOXELS
-    sparse.PAIR_PATH_MAX_VOXELS = 0
-    try:
-        first = [run(d).clone() for d in batches]
-        for order in ([3, 0, 2, 1], [1, 1, 3, 0], [2, 3, 0, 2]):
-            for i in order:
-                assert torch.equal(run(batches[i]), first[i]), "batch %d differs between repeats" % i
-    finally:
-        sparse.PAIR_PATH_MAX_VOXELS = keep
+    first = [run(d).clone() for d in batches]
+    for order in ([3, 0, 2, 1], [1, 1, 3, 0], [2, 3, 0, 2]):
+        for i in order:
+            assert torch.equal(run(batches[i]), first[i]), "batch %d differs between repeats" % i
+
+
+def test_bench_batch_is_bit_identical_between_passes():
+    """The benchmark's batch (coarse levels of 27 000, 7 000 and 2 000 voxels on the pair-list
+    convolution) gives the same bits on three passes."""
+    from pointtransformerv3_b200 import synthetic
+    data = synthetic.indoor_batch(4, first_seed=0, target_voxels=100_000, grid_size=0.02, dtype=torch.bfloat16)
+    d = {k: v.cuda() for k, v in data.items()}
+    torch.manual_seed(0)
+    net = P.PointTransformerV3(in_channels=6).eval().cuda().bfloat16()
+    outs = []
+    for _ in range(3):
+        with torch.inference_mode():
+            torch.manual_seed(1)
+            outs.append(net(dict(d)).feat.clone())
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
