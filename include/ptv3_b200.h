@@ -274,6 +274,12 @@ int ptv3_subm_conv_direct_fwd(const void* feat, const int32_t* indices, const vo
  *               their k x n buffers, so that a view of the first k * m
  *               elements is the contiguous result
  *   meta        1 + n_scenes int64: m, then the number of clusters per scene
+ *   meta_host   NULL, or 3 + n_scenes int64 of page-locked HOST memory that the
+ *               device can address (cudaHostAlloc / a pinned torch tensor): the last
+ *               kernel stores meta, then the status word, then the value 1 there, so
+ *               the host can read them without a device-to-host copy, either after
+ *               waiting for the stream or by zeroing the last word before the call
+ *               and polling it
  */
 size_t ptv3_pool_plan_workspace_bytes(int k, int64_t n, int n_scenes);
 int ptv3_pool_plan(const int64_t* code, const int64_t* order, const int32_t* grid_coord,
@@ -281,7 +287,8 @@ int ptv3_pool_plan(const int64_t* code, const int64_t* order, const int32_t* gri
                    const int* row_perm, int64_t* cluster, int64_t* idx_ptr, int64_t* head,
                    int64_t* pooled_code, int64_t* pooled_order, int64_t* pooled_inverse,
                    int32_t* pooled_grid_coord, int64_t* pooled_batch, int64_t* meta,
-                   uint32_t* status, void* workspace, size_t workspace_bytes, void* stream);
+                   int64_t* meta_host, uint32_t* status, void* workspace, size_t workspace_bytes,
+                   void* stream);
 
 /*
  * Segment reduction over clusters (reduce: 0 max, 1 min, 2 sum, 3 mean, as

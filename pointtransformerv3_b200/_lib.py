@@ -62,7 +62,7 @@ SIGNATURES = {
     "ptv3_pool_plan_workspace_bytes": (c_sz, [c_int, c_i64, c_int]),
     "ptv3_pool_plan": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_i64, c_int, c_int,
                                ctypes.POINTER(c_int), c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr,
-                               c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+                               c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_pool_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_int,
                               c_ptr]),
     "ptv3_add_layernorm_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_f32, c_ptr,

@@ -158,7 +158,7 @@ struct OrderSink {
 __global__ void pool_meta_kernel(const uint32_t* __restrict__ totals, int k, int64_t n, int B,
                                  const unsigned long long* __restrict__ scene_count,
                                  int64_t* __restrict__ idx_ptr, int64_t* __restrict__ meta,
-                                 uint32_t* __restrict__ status)
+                                 int64_t* __restrict__ meta_host, uint32_t* __restrict__ status)
 {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         const int64_t m = totals[0];
@@ -167,6 +167,18 @@ __global__ void pool_meta_kernel(const uint32_t* __restrict__ totals, int k, int
         for (int r = 1; r <= k; ++r)
             if ((int64_t)totals[r] != m) atomicOr(status, PTV3_STATUS_BAD_INDEX);
         for (int b = 0; b < B; ++b) meta[1 + b] = (int64_t)scene_count[b];
+        if (meta_host) {
+            // the same numbers and the status word, stored straight into the caller's mapped host
+            // memory: the host reads them after waiting for the stream, with no copy in between
+            // (a copy would queue behind whatever else the copy engine is busy with)
+            for (int b = 0; b <= B; ++b) meta_host[b] = meta[b];
+            meta_host[1 + B] = (int64_t)*reinterpret_cast<volatile uint32_t*>(status);
+            __threadfence_system();
+            // "everything above has been stored": a host that zeroed this word before the call may
+            // poll it instead of waiting for the stream
+            *reinterpret_cast<volatile int64_t*>(&meta_host[2 + B]) = 1;
+            __threadfence_system();
+        }
     }
 }
 
@@ -219,8 +231,8 @@ extern "C" int ptv3_pool_plan(const int64_t* code, const int64_t* order, const i
                               int64_t* idx_ptr, int64_t* head, int64_t* pooled_code,
                               int64_t* pooled_order, int64_t* pooled_inverse,
                               int32_t* pooled_grid_coord, int64_t* pooled_batch, int64_t* meta,
-                              uint32_t* status, void* workspace, size_t workspace_bytes,
-                              void* stream_)
+                              int64_t* meta_host, uint32_t* status, void* workspace,
+                              size_t workspace_bytes, void* stream_)
 {
     using namespace ptv3;
     PTV3_REQUIRE(k >= 1 && k <= PTV3_MAX_ORDERS && n >= 1 && n_scenes >= 1,
@@ -263,7 +275,7 @@ extern "C" int ptv3_pool_plan(const int64_t* code, const int64_t* order, const i
     scan_tile_sums_kernel<<<dim3(w.ntiles, k), SC_THREADS, 0, stream>>>(of, n, w.ntiles, ts2);
     scan_sums_kernel<<<k, SC_THREADS, 0, stream>>>(ts2, w.ntiles, totals + 1);
     scan_apply_kernel<<<dim3(w.ntiles, k), SC_THREADS, 0, stream>>>(of, os, n, w.ntiles, ts2);
-    pool_meta_kernel<<<1, 32, 0, stream>>>(totals, k, n, n_scenes, scene_count, idx_ptr, meta, status);
+    pool_meta_kernel<<<1, 32, 0, stream>>>(totals, k, n, n_scenes, scene_count, idx_ptr, meta, meta_host, status);
     count_launches(7);
     return check_launch("ptv3_pool_plan");
 }

@@ -732,8 +732,11 @@ class PointTransformerV3(PointModule):
         codes instead of deriving it from this batch's largest coordinate (needed
         when one logical batch is split over several processes).  ``offset_host``
         (the cumulative scene sizes as a Python list or CPU tensor) together with
-        ``sparse_shape`` and ``serialization_depth`` lets a caller that knows these
-        on the host skip the one device read at the start of the pass.  With
+        ``sparse_shape`` (largest grid coordinate per axis + 96) and
+        ``serialization_depth`` lets a caller that knows these on the host skip the one
+        device read at the start of the pass; a caller that streams batches from host
+        memory should do so, because that read is a small device-to-host copy which waits
+        behind any large copy the same engine is busy with (the previous batch's output).  With
         ``self.defer_status_check = True`` the device status word is not read at
         the end either; the caller checks ``point.check_status(force=True)`` when
         it next needs the host to wait.  (On the benchmark batch neither changes
@@ -750,6 +753,10 @@ class PointTransformerV3(PointModule):
         # -- planning phase: everything whose size depends on the data, so that all
         #    host reads happen here and the feature phase is queued without waiting
         point._ensure_grid_coord()
+        if "sparse_shape" in point.keys() and "_shape_pad" not in point.keys():
+            # a caller's shape is the largest grid coordinate + 96 (sparsify's default pad,
+            # model.py:162-164); the shapes of the coarse levels then follow without reading the device
+            point["_shape_pad"] = 96
         if "sparse_shape" not in point.keys() or depth is None or "_counts" not in point.keys():
             stats = torch.cat([point.grid_coord.max(0).values.to(torch.int64), point.offset.to(torch.int64)])
             stats = stats.tolist()                                     # one host read

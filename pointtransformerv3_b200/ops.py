@@ -4,6 +4,7 @@ Every wrapper allocates outputs and workspaces with torch, passes raw device
 pointers and the current CUDA stream, and raises on a non-zero status."""
 import ctypes
 import threading
+import time
 
 import torch
 
@@ -265,28 +266,49 @@ def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=
     perm = None
     if row_perm is not None:
         perm = (ctypes.c_int * k)(*[int(v) for v in row_perm])
+    # the sizes of the coarse level and the status word arrive in mapped host memory, written by
+    # the plan's last kernel; the host polls the "done" word behind them (a stream wait through
+    # the driver takes several times longer to notice the end of a kernel)
+    meta_host = _pinned(3 + n_scenes, torch.int64, "pool_plan.meta")
+    meta_host[-1] = 0
     _lib.check(lib.ptv3_pool_plan(_lib.ptr(code), _lib.ptr(order), _lib.ptr(grid_coord), _lib.ptr(batch),
                                   k, n, n_scenes, int(pooling_depth), perm, _lib.ptr(cluster),
                                   _lib.ptr(idx_ptr), _lib.ptr(head), _lib.ptr(pcode), _lib.ptr(porder),
                                   _lib.ptr(pinv), _lib.ptr(pgrid), _lib.ptr(pbatch), _lib.ptr(meta),
-                                  _lib.ptr(status), _lib.ptr(ws), nbytes, _lib.stream()),
+                                  ctypes.c_void_p(meta_host.data_ptr()), _lib.ptr(status), _lib.ptr(ws), nbytes,
+                                  _lib.stream()),
                "ptv3_pool_plan")
-    # the one sync: the cluster counts and the status word through pinned staging buffers
-    meta_host, status_host = _pinned(1 + n_scenes, torch.int64, "pool_plan.meta"), _pinned(1, torch.int32,
-                                                                                           "pool_plan.status")
-    meta_host.copy_(meta, non_blocking=True)
-    status_host.copy_(status, non_blocking=True)
-    torch.cuda.current_stream().synchronize()
-    host = meta_host.tolist()
-    if int(status_host[0]):
+    _wait_flag(meta_host)                          # the one wait
+    host = meta_host.tolist()[:-1]
+    if host[-1]:
         raise _lib.Ptv3Error("device status 0x%x (read after ptv3_pool_plan; the word is shared by "
-                             "every kernel queued with it)" % int(status_host[0]))
+                             "every kernel queued with it)" % host[-1])
+    host = host[:-1]
     m = host[0]
     # the k-row outputs are written packed (row stride m): views, no copies
     packed = lambda t: t.view(-1)[: k * m].view(k, m)
     return dict(cluster=cluster, idx_ptr=idx_ptr[: m + 1], head=head[:m],
                 code=packed(pcode), order=packed(porder), inverse=packed(pinv), grid_coord=pgrid[:m],
                 batch=pbatch[:m], counts=host[1:], m=m, offset=torch.cumsum(meta[1:], 0))
+
+
+POLL_SECONDS = 2.0      # how long a host thread polls a "done" word before it asks the driver
+
+
+def _wait_flag(buf):
+    """Waits until the last word of the pinned tensor ``buf`` is non-zero (stored by the last
+    kernel of a call).  Falls back to waiting for the stream, so a failed launch cannot hang
+    the host."""
+    flag = buf[-1:]
+    deadline = None
+    while int(flag) == 0:
+        if deadline is None:
+            deadline = time.monotonic() + POLL_SECONDS
+        elif time.monotonic() > deadline:
+            torch.cuda.current_stream().synchronize()
+            if int(flag) == 0:
+                raise _lib.Ptv3Error("the kernels of this call finished without reporting their result")
+            break
 
 
 _PINNED = {}

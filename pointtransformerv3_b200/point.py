@@ -14,10 +14,14 @@ def offset2bincount(offset):
 
 
 @torch.inference_mode()
-def offset2batch(offset):
-    """model.py:35-40."""
+def offset2batch(offset, n=None):
+    """model.py:35-40.  ``n``: the number of points when the caller knows it (the last
+    offset); repeat_interleave then does not have to read its output size from the device."""
     bincount = offset2bincount(offset)
-    return torch.arange(len(bincount), device=offset.device, dtype=torch.long).repeat_interleave(bincount)
+    ids = torch.arange(len(bincount), device=offset.device, dtype=torch.long)
+    if n is None:
+        return ids.repeat_interleave(bincount)
+    return ids.repeat_interleave(bincount, output_size=int(n))
 
 
 @torch.inference_mode()
@@ -76,7 +80,12 @@ class Point(AttrDict):
     def __init__(self, *args, **kwargs):
         super().__init__(*args, **kwargs)
         if "batch" not in self.keys() and "offset" in self.keys():
-            self["batch"] = offset2batch(self.offset)
+            n = None
+            for k in ("feat", "grid_coord", "coord"):      # any per-point tensor tells the size
+                if k in self.keys() and torch.is_tensor(self[k]):
+                    n = self[k].shape[0]
+                    break
+            self["batch"] = offset2batch(self.offset, n)
         elif "offset" not in self.keys() and "batch" in self.keys():
             self["offset"] = batch2offset(self.batch)
 

@@ -21,7 +21,7 @@ def voxelize(coord, feat, offset, grid_size, extra=None):
     scattering per-voxel results back to points.  ``extra``: optional dict of
     further per-point tensors to carry along.  One host read (the voxel count)."""
     offset = offset.to(torch.int64)
-    batch = offset2batch(offset)
+    batch = offset2batch(offset, coord.shape[0])
     grid, _ = ops.grid_coord(coord, grid_size)
     indices = torch.cat([batch.unsqueeze(-1).int(), grid], dim=1).contiguous()
     d = ops.voxel_dedup(indices, offset)
