@@ -66,4 +66,66 @@ __device__ __forceinline__ uint32_t exp2_bf16x2(uint32_t x)
     return y;
 }
 
+// Packed fp32 pairs (two floats in one 64-bit register, one instruction for both).
+__device__ __forceinline__ uint64_t pack2(float x, float y)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t r, float& x, float& y)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x), "=f"(y) : "l"(r));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
+{
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
+// Constants of the exponentials, packed once per thread.
+struct Exp2Const {
+    uint64_t log2e, magic, neg_magic, neg_one, c3, c2, c1, one;
+    __device__ __forceinline__ Exp2Const()
+    {
+        log2e = pack2(1.4426950408889634f, 1.4426950408889634f);
+        magic = pack2(12582912.f, 12582912.f);
+        neg_magic = pack2(-12582912.f, -12582912.f);
+        neg_one = pack2(-1.f, -1.f);
+        c3 = pack2(0.0555041086f, 0.0555041086f);
+        c2 = pack2(0.2402265070f, 0.2402265070f);
+        c1 = pack2(0.6931471806f, 0.6931471806f);
+        one = pack2(1.f, 1.f);
+    }
+};
+
+// 2^x for a pair on the FMA pipe: x = n + r with n integer (round to nearest, read off the low
+// mantissa bits after adding 1.5 * 2^23) and r in [-0.5, 0.5], 2^r by a cubic (relative error
+// 1e-4, far below the bf16 rounding that follows), n added to the exponent field.
+__device__ __forceinline__ uint32_t exp2_poly2_bf16(uint64_t x2, const Exp2Const& k)
+{
+    float x, y;
+    unpack2(x2, x, y);
+    x2 = pack2(fmaxf(x, -125.f), fmaxf(y, -125.f));
+    const uint64_t t2 = add2(x2, k.magic);
+    const uint64_t n2 = add2(t2, k.neg_magic);
+    const uint64_t r2 = fma2(n2, k.neg_one, x2);
+    uint64_t p2 = fma2(r2, k.c3, k.c2);
+    p2 = fma2(p2, r2, k.c1);
+    p2 = fma2(p2, r2, k.one);
+    float px, py, tx, ty;
+    unpack2(p2, px, py);
+    unpack2(t2, tx, ty);
+    px = __int_as_float(__float_as_int(px) + (__float_as_int(tx) << 23));
+    py = __int_as_float(__float_as_int(py) + (__float_as_int(ty) << 23));
+    return pack_bf16(px, py);
+}
+
 }  // namespace ptv3
