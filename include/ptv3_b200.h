@@ -356,10 +356,27 @@ int ptv3_mlp_fwd(const void* x, const void* fc1_weight, const void* fc1_bias, co
  *                        Replaces cpe.1 + cpe.2 + shortcut + norm1 (model.py:553-554,
  *                        589-592) and attn.proj + shortcut + norm2 (model.py:487, 594,
  *                        598-600).  sum_out may be NULL; it may alias residual.
- * ptv3_linear_supported() tells whether a shape is covered; other shapes use a
- * library GEMM followed by ptv3_add_layernorm_fwd.
+ * ptv3_linear_supported() tells whether a shape is covered; wider layers use
+ * ptv3_gemm_fwd followed by ptv3_add_layernorm_fwd.
  */
 int ptv3_linear_supported(int k, int n_out, int residual_mode, int dtype);
+/*
+ * Linear layer with streamed weights on the tcgen05 tensor cores, for the widths
+ * ptv3_linear_fwd does not take (bf16, k a multiple of 64, n_out a multiple of 128):
+ *   out = [residual +] act(x W^T + b),  act = exact GELU if `gelu` else identity
+ * with the roundings of the unfused sequence (the GEMM result is rounded to bf16
+ * before GELU / the residual sum, which is rounded again).
+ * Replaces nn.Linear in the blocks of the 256- and 512-channel levels (model.py:456,
+ * 487, 553), MLP.forward with its residual for 128 channels and more (model.py:510-516,
+ * 601-602: fc1 with gelu = 1, fc2 with the residual), and the pooling / unpooling
+ * projections (model.py:684, 726-735).
+ *   x  n x k;  weight  n_out x k (nn.Linear layout);  bias  n_out or NULL;
+ *   residual  n x n_out or NULL (may alias out);  all 16-byte aligned
+ * A wait that exceeds its bound sets PTV3_STATUS_WAIT_LIMIT in *status.
+ */
+int ptv3_gemm_supported(int k, int n_out, int dtype);
+int ptv3_gemm_fwd(const void* x, const void* weight, const void* bias, const void* residual, void* out,
+                  int64_t n, int k, int n_out, int gelu, int dtype, uint32_t* status, void* stream);
 int ptv3_linear_fwd(const void* x, const void* weight, const void* bias, void* out, int64_t n, int k,
                     int n_out, int dtype, uint32_t* status, void* stream);
 int ptv3_linear_ln_fwd(const void* x, const void* weight, const void* bias, const void* residual,
@@ -372,8 +389,10 @@ int ptv3_linear_ln_fwd(const void* x, const void* weight, const void* bias, cons
  * pre-norm, bf16): xCPE convolution + Linear + LayerNorm, attention with its two
  * Linear layers, MLP, the three residual additions.  The same kernels as the
  * single-operator entry points, queued from C++ so that a block costs the host
- * one call; channel widths outside the tcgen05 kernels' range take their Linear
- * layers from cuBLASLt.  All pointers are device pointers except the struct.
+ * one call; widths up to 128 use ptv3_linear_ln_fwd / ptv3_linear_fwd (and ptv3_mlp_fwd
+ * up to 64), wider ones ptv3_gemm_fwd with ptv3_add_layernorm_fwd; ptv3_block_supported
+ * tells whether every layer of a block has a kernel.  All pointers are device pointers
+ * except the struct.
  */
 typedef struct ptv3_block_args {
     int64_t n;                      /* voxels of the level */
@@ -452,25 +471,29 @@ int ptv3_seg_head_fwd(const void* feat, const void* weight, const void* bias, vo
                       int64_t n, int channels, int classes, int dtype, void* stream);
 
 /*
- * Stage transitions in one call each (bf16): the Linear projection(s) by cuBLASLt,
- * then the kernel of ptv3_pool_fwd / ptv3_unpool_fwd with the same arguments.
+ * Stage transitions in one call each (bf16): the Linear projection(s) on the tensor-core
+ * Linear kernels (ptv3_linear_fwd or ptv3_gemm_fwd, whichever takes the shape;
+ * ptv3_pool_stage_supported tells whether one does), then the kernel of ptv3_pool_fwd /
+ * ptv3_unpool_fwd with the same arguments.
  *   ptv3_pool_stage_fwd     SerializedPooling: proj + segment reduction + BN + GELU
  *                           (model.py:684-689, 707-710); x is n x c_in, out m x c_out
  *   ptv3_unpool_stage_fwd   SerializedUnpooling: proj and proj_skip + BN + GELU + gather-add
  *                           (model.py:726-735, 744-746); skip_feat n x c_skip, child_feat m x c_child
- * Weights in nn.Linear layout (c_out x c_in), biases required.
+ * Weights in nn.Linear layout (c_out x c_in), biases required.  status: one uint32, OR-ed
+ * with PTV3_STATUS_WAIT_LIMIT when a bounded wait of the Linear kernels ran out.
  */
+int ptv3_pool_stage_supported(int c_in, int c_out, int dtype);
 size_t ptv3_pool_stage_workspace_bytes(int64_t n, int c_out);
 int ptv3_pool_stage_fwd(const void* x, const void* weight, const void* bias, const float* coord,
                         const int64_t* indices, const int64_t* idx_ptr, int64_t n, int64_t m, int c_in, int c_out,
                         const float* bn_scale, const float* bn_shift, void* out, float* coord_out, int reduce,
-                        int dtype, void* workspace, size_t workspace_bytes, void* stream);
+                        int dtype, uint32_t* status, void* workspace, size_t workspace_bytes, void* stream);
 size_t ptv3_unpool_stage_workspace_bytes(int64_t n, int64_t m, int c_out);
 int ptv3_unpool_stage_fwd(const void* skip_feat, const void* child_feat, const void* w_skip, const void* b_skip,
                           const void* w_child, const void* b_child, const int64_t* cluster, int64_t n, int64_t m,
                           int c_skip, int c_child, int c_out, const float* skip_scale, const float* skip_shift,
                           const float* child_scale, const float* child_shift, void* out, void* skip_act, int dtype,
-                          void* workspace, size_t workspace_bytes, void* stream);
+                          uint32_t* status, void* workspace, size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -68,6 +68,8 @@ SIGNATURES = {
     "ptv3_add_layernorm_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_f32, c_ptr,
                                        c_i64, c_int, c_int, c_ptr]),
     "ptv3_linear_supported": (c_int, [c_int, c_int, c_int, c_int]),
+    "ptv3_gemm_supported": (c_int, [c_int, c_int, c_int]),
+    "ptv3_gemm_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int, c_int, c_ptr, c_ptr]),
     "ptv3_linear_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int, c_ptr, c_ptr]),
     "ptv3_linear_ln_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_f32, c_ptr, c_ptr, c_ptr, c_f32,
                                    c_ptr, c_i64, c_int, c_int, c_ptr, c_ptr]),
@@ -78,12 +80,13 @@ SIGNATURES = {
     "ptv3_voxel_dedup_workspace_bytes": (c_sz, [c_i64]),
     "ptv3_voxel_dedup": (c_int, [c_ptr, c_i64, c_ptr, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_seg_head_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int, c_ptr]),
+    "ptv3_pool_stage_supported": (c_int, [c_int, c_int, c_int]),
     "ptv3_pool_stage_workspace_bytes": (c_sz, [c_i64, c_int]),
     "ptv3_pool_stage_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_int, c_int, c_ptr, c_ptr,
-                                    c_ptr, c_ptr, c_int, c_int, c_ptr, c_sz, c_ptr]),
+                                    c_ptr, c_ptr, c_int, c_int, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_unpool_stage_workspace_bytes": (c_sz, [c_i64, c_i64, c_int]),
     "ptv3_unpool_stage_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_i64, c_int, c_int,
-                                      c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_sz, c_ptr]),
+                                      c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_block_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "ptv3_block_workspace_bytes": (c_sz, [ctypes.POINTER(BlockArgs)]),
     "ptv3_block_fwd": (c_int, [ctypes.POINTER(BlockArgs), c_ptr]),

@@ -396,8 +396,10 @@ class Block(PointModule):
             feat, normed = ops.linear_ln(x, attn.proj.weight, attn.proj.bias, feat, None, self.norm2[0], status)
             point.check_status("tcgen05 linear layers")
         else:
-            feat, normed = ops.add_layernorm(lin(x), shortcut, self.cpe[2], self.norm1[0])
-            x = attn.attend(point, normed)
+            # wide channels: the streamed-weight tensor-core Linear (bf16) or torch's (fp32), with
+            # the LayerNorm / residual glue in the fused row kernel
+            feat, normed = ops.add_layernorm(_linear_op(x, lin, status), shortcut, self.cpe[2], self.norm1[0])
+            x = _linear_op(attn.core(point, _linear_op(normed, attn.qkv, status)), attn.proj, status)
             feat, normed = ops.add_layernorm(x, feat, None, self.norm2[0])
         mlp = self.mlp[0]
         if (mlp.fc1.bias is not None and mlp.fc2.bias is not None
@@ -407,6 +409,13 @@ class Block(PointModule):
             feat = ops.mlp(normed, mlp.fc1.weight, mlp.fc1.bias, mlp.fc2.weight, mlp.fc2.bias, feat,
                            point.device_status())
             point.check_status("ptv3_mlp_fwd")
+        elif (mlp.fc1.bias is not None and mlp.fc2.bias is not None and normed.dtype == torch.bfloat16
+              and ops.gemm_supported(mlp.fc1.in_features, mlp.fc1.out_features, normed.dtype)
+              and ops.gemm_supported(mlp.fc2.in_features, mlp.fc2.out_features, normed.dtype)):
+            # bias + GELU and bias + residual in the epilogues of the two Linear kernels
+            hidden = ops.gemm(normed, mlp.fc1.weight, mlp.fc1.bias, None, True, status)
+            feat = ops.gemm(hidden, mlp.fc2.weight, mlp.fc2.bias, feat, False, status)
+            point.check_status("ptv3_gemm_fwd")
         else:
             x = mlp(normed)
             feat, _ = ops.add_layernorm(x, feat, None, None)
@@ -508,10 +517,11 @@ class SerializedPooling(PointModule):
             # projection and reduction queued by one C call
             feat, coord = ops.pool_stage(point.feat, self.proj.weight, self.proj.bias, src_coord,
                                          point.serialized_order[0], child.pop("_idx_ptr"), scale, shift,
-                                         self.reduce)
+                                         self.reduce, point.device_status())
+            point.check_status("ptv3_pool_stage_fwd")
         else:
-            feat, coord = ops.pool(self.proj(point.feat), src_coord, point.serialized_order[0],
-                                   child.pop("_idx_ptr"), scale, shift, self.reduce)
+            feat, coord = ops.pool(_linear_op(point.feat, self.proj, point.device_status()), src_coord,
+                                   point.serialized_order[0], child.pop("_idx_ptr"), scale, shift, self.reduce)
         cluster = child.pop("_cluster")
         child["feat"] = feat
         if coord is not None:
@@ -571,10 +581,11 @@ class SerializedUnpooling(PointModule):
                 # both projections and the gather-add queued by one C call
                 out, skip_act = ops.unpool_stage(parent.feat, point.feat, self.proj_skip[0].weight,
                                                  self.proj_skip[0].bias, self.proj[0].weight, self.proj[0].bias,
-                                                 inverse, ss, sb, cs, cb)
+                                                 inverse, ss, sb, cs, cb, parent.device_status())
+                parent.check_status("ptv3_unpool_stage_fwd")
             else:
-                child_lin = self.proj[0](point.feat)
-                skip_lin = self.proj_skip[0](parent.feat)
+                child_lin = _linear_op(point.feat, self.proj[0], parent.device_status())
+                skip_lin = _linear_op(parent.feat, self.proj_skip[0], parent.device_status())
                 out, skip_act = ops.unpool(skip_lin, child_lin, inverse, ss, sb, cs, cb)
             # the parent's sparse tensor keeps the skip branch alone: the reference
             # adds the up-sampled features to `feat` only (model.py:746), and the next
@@ -883,18 +894,27 @@ class SegHead(PointModule):
         return point
 
 
-SINGLE_CALL_MAX_ROWS = 131072
+def _linear_op(x, linear, status):
+    """``linear(x)`` for an nn.Linear: on the tensor-core Linear kernels of the library where
+    one takes the shape (bf16), else torch's own (fp32, unusual widths)."""
+    if (type(linear) is nn.Linear and x.dtype == torch.bfloat16 and linear.weight.dtype == torch.bfloat16
+            and x.dim() == 2):
+        k, n_out = linear.in_features, linear.out_features
+        if ops.gemm_supported(k, n_out, x.dtype):
+            return ops.gemm(x, linear.weight, linear.bias, None, False, status)
+        if linear.bias is not None and ops.linear_supported(k, n_out, False, x.dtype):
+            return ops.linear(x, linear.weight, linear.bias, status)
+    return linear(x)
 
 
 def _single_call_ok(feat, linear):
     """Whether a stage transition can go through its one-call entry point: bf16 features and
-    parameters, a bias, channel counts the library GEMM takes, no per-operator timing."""
-    # (levels with many rows are GPU-bound and keep torch's GEMM call, which picks the faster
-    # library kernel there; the one-call path is for the host-paced coarse levels)
-    return (ops.TIMERS is None and feat.shape[0] <= SINGLE_CALL_MAX_ROWS and feat.dtype == torch.bfloat16
-            and type(linear) is nn.Linear
+    parameters, a bias, a projection one of the tensor-core Linear kernels takes, no
+    per-operator timing."""
+    return (ops.TIMERS is None and feat.dtype == torch.bfloat16 and type(linear) is nn.Linear
             and linear.bias is not None and linear.weight.dtype == torch.bfloat16
-            and linear.weight.is_contiguous() and linear.in_features % 8 == 0 and linear.out_features % 8 == 0)
+            and linear.weight.is_contiguous()
+            and ops.pool_stage_supported(linear.in_features, linear.out_features, feat.dtype))
 
 
 def _record_stream(obj, stream):

@@ -512,6 +512,34 @@ def linear(x, weight, bias, status=None):
     return out
 
 
+def gemm_supported(k, n_out, dtype):
+    return dtype in _lib.DTYPE_IDS and bool(_lib.load().ptv3_gemm_supported(int(k), int(n_out), _lib.DTYPE_IDS[dtype]))
+
+
+def gemm(x, weight, bias=None, residual=None, gelu=False, status=None):
+    """out = [residual +] act(x W^T + b) with streamed weights (see ptv3_gemm_fwd)."""
+    _lib.require_cuda(x, weight, bias, residual)
+    lib = _lib.load()
+    x = x.contiguous()
+    n, k = x.shape
+    n_out = weight.shape[0]
+    out = torch.empty((n, n_out), dtype=x.dtype, device=x.device)
+    if residual is not None:
+        residual = residual.contiguous()
+        if residual.shape != out.shape or residual.dtype != x.dtype:
+            raise ValueError("residual must be (n, n_out) in the feature dtype")
+    own = status is None
+    if own:
+        status = new_status(x.device)
+    with timed("gemm", 2.0 * n * k * n_out):
+        _lib.check(lib.ptv3_gemm_fwd(_lib.ptr(x), _lib.ptr(weight.contiguous()), _lib.ptr(bias), _lib.ptr(residual),
+                                     _lib.ptr(out), n, k, n_out, int(bool(gelu)), _lib.dtype_id(x), _lib.ptr(status),
+                                     _lib.stream()), "ptv3_gemm_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_gemm_fwd")
+    return out
+
+
 def linear_ln(x, weight, bias, residual, ln1, ln2, status=None, want_sum=True):
     """(sum, normed) with y = x W^T + b, sum = residual + LN1(y) (or + y), normed = LN2(sum)."""
     _lib.require_cuda(x, weight, bias, residual)
@@ -639,7 +667,13 @@ def seg_head(feat, weight, bias=None, want_logits=True, want_labels=True):
     return logits, labels
 
 
-def pool_stage(x, weight, bias, coord, indices, idx_ptr, bn_scale=None, bn_shift=None, reduce="max"):
+def pool_stage_supported(c_in, c_out, dtype):
+    """Whether a projection c_in -> c_out can go through the one-call stage transitions."""
+    return dtype in _lib.DTYPE_IDS and bool(
+        _lib.load().ptv3_pool_stage_supported(int(c_in), int(c_out), _lib.DTYPE_IDS[dtype]))
+
+
+def pool_stage(x, weight, bias, coord, indices, idx_ptr, bn_scale=None, bn_shift=None, reduce="max", status=None):
     """SerializedPooling's feature side in one call (bf16): proj(x), segment reduction,
     BN + GELU, mean coordinate.  Returns (pooled feat (M, C_out), pooled coord or None)."""
     _lib.require_cuda(x, weight, bias, indices, idx_ptr)
@@ -655,17 +689,23 @@ def pool_stage(x, weight, bias, coord, indices, idx_ptr, bn_scale=None, bn_shift
         cout_coord = torch.empty((m, 3), dtype=torch.float32, device=x.device)
     nbytes = lib.ptv3_pool_stage_workspace_bytes(n, cout)
     ws = _lib.workspace(nbytes, x.device)
+    own = status is None
+    if own:
+        status = new_status(x.device)
     with timed("pool_stage", 2.0 * n * cin * cout):
         _lib.check(lib.ptv3_pool_stage_fwd(_lib.ptr(x), _lib.ptr(weight), _lib.ptr(bias), _lib.ptr(coord),
                                            _lib.ptr(indices), _lib.ptr(idx_ptr), n, m, cin, cout,
                                            _lib.ptr(bn_scale), _lib.ptr(bn_shift), _lib.ptr(out),
-                                           _lib.ptr(cout_coord), REDUCE_IDS[reduce], _lib.dtype_id(x), _lib.ptr(ws),
-                                           nbytes, _lib.stream()), "ptv3_pool_stage_fwd")
+                                           _lib.ptr(cout_coord), REDUCE_IDS[reduce], _lib.dtype_id(x),
+                                           _lib.ptr(status), _lib.ptr(ws), nbytes, _lib.stream()),
+                   "ptv3_pool_stage_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_pool_stage_fwd")
     return out, cout_coord
 
 
 def unpool_stage(skip_feat, child_feat, w_skip, b_skip, w_child, b_child, cluster, skip_scale, skip_shift,
-                 child_scale, child_shift):
+                 child_scale, child_shift, status=None):
     """SerializedUnpooling in one call (bf16); returns (out, skip_act) as ops.unpool does."""
     _lib.require_cuda(skip_feat, child_feat, cluster)
     lib = _lib.load()
@@ -677,11 +717,17 @@ def unpool_stage(skip_feat, child_feat, w_skip, b_skip, w_child, b_child, cluste
     act = torch.empty_like(out)
     nbytes = lib.ptv3_unpool_stage_workspace_bytes(n, m, cout)
     ws = _lib.workspace(nbytes, skip_feat.device)
+    own = status is None
+    if own:
+        status = new_status(skip_feat.device)
     with timed("unpool_stage", 2.0 * cout * (n * cs + m * cc)):
         _lib.check(lib.ptv3_unpool_stage_fwd(_lib.ptr(skip_feat), _lib.ptr(child_feat), _lib.ptr(w_skip),
                                              _lib.ptr(b_skip), _lib.ptr(w_child), _lib.ptr(b_child),
                                              _lib.ptr(cluster), n, m, cs, cc, cout, _lib.ptr(skip_scale),
                                              _lib.ptr(skip_shift), _lib.ptr(child_scale), _lib.ptr(child_shift),
-                                             _lib.ptr(out), _lib.ptr(act), _lib.dtype_id(skip_feat), _lib.ptr(ws),
-                                             nbytes, _lib.stream()), "ptv3_unpool_stage_fwd")
+                                             _lib.ptr(out), _lib.ptr(act), _lib.dtype_id(skip_feat),
+                                             _lib.ptr(status), _lib.ptr(ws), nbytes, _lib.stream()),
+                   "ptv3_unpool_stage_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_unpool_stage_fwd")
     return out, act

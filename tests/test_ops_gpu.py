@@ -432,6 +432,44 @@ def test_linear_tcgen05(k, n_out, n):
     assert rel_l2(got, F.linear(x.float(), w.float(), b.float())) < 5e-3
 
 
+@pytest.mark.parametrize("n,k,n_out,gelu,res", [(3000, 256, 768, False, False), (2111, 256, 256, False, True),
+                                                 (7000, 128, 512, True, False), (7000, 512, 128, False, True),
+                                                 (500, 512, 1536, False, False), (129, 2048, 512, False, True),
+                                                 (1, 64, 128, True, True), (2049, 1024, 256, False, False)])
+def test_gemm_tcgen05(n, k, n_out, gelu, res):
+    """The streamed-weight Linear kernel against torch on CPU with the same roundings (GEMM result
+    rounded to bf16, then GELU / residual sum rounded again)."""
+    g = torch.Generator().manual_seed(n + k + n_out)
+    x = torch.randn(n, k, generator=g).bfloat16()
+    w = (torch.randn(n_out, k, generator=g) / k ** 0.5).bfloat16()
+    b = (0.1 * torch.randn(n_out, generator=g)).bfloat16()
+    r = torch.randn(n, n_out, generator=g).bfloat16() if res else None
+    assert ops.gemm_supported(k, n_out, torch.bfloat16)
+    got = ops.gemm(x.cuda(), w.cuda(), b.cuda(), None if r is None else r.cuda(), gelu)
+    ref32 = F.linear(x.float(), w.float(), b.float())
+    ref = ref32.bfloat16()
+    if gelu:
+        ref = F.gelu(ref.float()).bfloat16()
+        ref32 = F.gelu(ref32)
+    if res:
+        ref = (ref.float() + r.float()).bfloat16()
+        ref32 = ref32 + r.float()
+    assert_close(got, ref, what="gemm", **TOL[torch.bfloat16])
+    assert rel_l2(got, ref32) < 5e-3
+    # without a bias
+    got = ops.gemm(x.cuda(), w.cuda(), None, None, False)
+    assert_close(got, F.linear(x.float(), w.float()).bfloat16(), what="gemm without bias", **TOL[torch.bfloat16])
+
+
+def test_gemm_rejects_unsupported_shapes():
+    from pointtransformerv3_b200 import _lib
+    x = torch.zeros(10, 96, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(128, 96, dtype=torch.bfloat16, device="cuda")
+    assert not ops.gemm_supported(96, 128, torch.bfloat16)
+    with pytest.raises(_lib.Ptv3Error):
+        ops.gemm(x, w)
+
+
 @pytest.mark.parametrize("C", [32, 64, 128])
 @pytest.mark.parametrize("with_ln1", [True, False])
 def test_linear_ln_tcgen05(C, with_ln1):
