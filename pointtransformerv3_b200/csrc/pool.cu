@@ -17,8 +17,14 @@
 
 namespace ptv3 {
 
-__device__ __forceinline__ float gelu_exact(float x)
+// GELU in its erf form.  fp32 features take the library erff; bf16 features the tanh-based
+// form (fit + hardware tanh, relative error ~5e-4, below the bf16 rounding that follows),
+// which costs a quarter of the instructions: with erff these kernels are bound by
+// arithmetic, not by memory.
+template <typename T>
+__device__ __forceinline__ float gelu_for(float x)
 {
+    if (sizeof(T) == 2) return gelu_tanh_erf(x);
     return 0.5f * x * (1.f + erff(x * 0.70710678118654752440f));
 }
 
@@ -26,7 +32,7 @@ __device__ __forceinline__ float gelu_exact(float x)
 // lanes of a group also average the coordinates.  C must be a multiple of Vec<T>::N.
 // REDUCE: 0 max, 1 min, 2 sum, 3 mean (torch_scatter.segment_csr's reduce argument)
 template <typename T, int LANES, int REDUCE>
-__global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x, const float* __restrict__ coord,
+__global__ void __launch_bounds__(256, 4) pool_max_kernel(const T* __restrict__ x, const float* __restrict__ coord,
                                                        const int64_t* __restrict__ indices,
                                                        const int64_t* __restrict__ idx_ptr, int64_t m, int C,
                                                        const float* __restrict__ scale,
@@ -38,33 +44,52 @@ __global__ void __launch_bounds__(256) pool_max_kernel(const T* __restrict__ x, 
     const int64_t c = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) / LANES;
     if (c >= m) return;
     const int64_t lo = idx_ptr[c], hi = idx_ptr[c + 1];
+    constexpr int CHUNK = 4;     // members fetched together (a stride-2 cluster has 4 on average, at most 8)
+    float cacc = 0.f;
     for (int ch = sub * V::N; ch < C; ch += LANES * V::N) {
         float best[V::N];
 #pragma unroll
         for (int i = 0; i < V::N; ++i) best[i] = REDUCE == 0 ? -INFINITY : (REDUCE == 1 ? INFINITY : 0.f);
-        for (int64_t j = lo; j < hi; ++j) {
-            const int64_t p = indices[j];
-            const typename V::Raw raw = *reinterpret_cast<const typename V::Raw*>(x + p * C + ch);
-            float f[V::N];
-            V::unpack(raw, f);
+        for (int64_t j0 = lo; j0 < hi; j0 += CHUNK) {
+            // the member indices first, then all their rows: independent loads, one latency each
+            int64_t p[CHUNK];
 #pragma unroll
-            for (int i = 0; i < V::N; ++i)
-                best[i] = REDUCE == 0 ? fmaxf(best[i], f[i]) : (REDUCE == 1 ? fminf(best[i], f[i]) : best[i] + f[i]);
+            for (int k = 0; k < CHUNK; ++k) p[k] = j0 + k < hi ? indices[j0 + k] : -1;
+            typename V::Raw raw[CHUNK];
+#pragma unroll
+            for (int k = 0; k < CHUNK; ++k)
+                if (p[k] >= 0) raw[k] = *reinterpret_cast<const typename V::Raw*>(x + p[k] * C + ch);
+            if (coord_out && sub < 3 && ch == sub * V::N) {
+#pragma unroll
+                for (int k = 0; k < CHUNK; ++k)
+                    if (p[k] >= 0) cacc += coord[3 * p[k] + sub];
+            }
+#pragma unroll
+            for (int k = 0; k < CHUNK; ++k) {
+                if (p[k] < 0) continue;
+                float f[V::N];
+                V::unpack(raw[k], f);
+#pragma unroll
+                for (int i = 0; i < V::N; ++i)
+                    best[i] = REDUCE == 0 ? fmaxf(best[i], f[i])
+                                          : (REDUCE == 1 ? fminf(best[i], f[i]) : best[i] + f[i]);
+            }
         }
 #pragma unroll
         for (int i = 0; i < V::N; ++i) {
             float v = best[i];
             if (REDUCE == 3) v = v / (float)(hi - lo);
             if (REDUCE >= 2) v = to_f<T>(from_f<T>(v));   // the reduction's output is rounded before the norm
-            if (scale) v = gelu_exact(fmaf(v, scale[ch + i], shift[ch + i]));
+            if (scale) v = gelu_for<T>(fmaf(v, scale[ch + i], shift[ch + i]));
             best[i] = v;
         }
         *reinterpret_cast<typename V::Raw*>(out + c * C + ch) = V::pack(best);
     }
     if (coord_out && sub < 3) {
-        float acc = 0.f;
-        for (int64_t j = lo; j < hi; ++j) acc += coord[3 * indices[j] + sub];
-        coord_out[3 * c + sub] = acc / (float)(hi - lo);
+        if (sub * V::N >= C) {     // fewer channel groups than coordinate lanes: not reached above
+            for (int64_t j = lo; j < hi; ++j) cacc += coord[3 * indices[j] + sub];
+        }
+        coord_out[3 * c + sub] = cacc / (float)(hi - lo);
     }
 }
 
@@ -97,13 +122,22 @@ __global__ void __launch_bounds__(256) unpool_kernel(const T* __restrict__ skip,
         float a[V::N], b[V::N], o[V::N];
         V::unpack(*reinterpret_cast<const typename V::Raw*>(skip + i * C + ch), a);
         V::unpack(*reinterpret_cast<const typename V::Raw*>(child + cl * C + ch), b);
+        // per-channel parameters with 16-byte loads (ch is a multiple of 4)
+        float ss[V::N], sh[V::N], cs[V::N], csh[V::N];
+#pragma unroll
+        for (int k = 0; k < V::N; k += 4) {
+            *reinterpret_cast<float4*>(ss + k) = *reinterpret_cast<const float4*>(s_scale + ch + k);
+            *reinterpret_cast<float4*>(sh + k) = *reinterpret_cast<const float4*>(s_shift + ch + k);
+            *reinterpret_cast<float4*>(cs + k) = *reinterpret_cast<const float4*>(c_scale + ch + k);
+            *reinterpret_cast<float4*>(csh + k) = *reinterpret_cast<const float4*>(c_shift + ch + k);
+        }
 #pragma unroll
         for (int k = 0; k < V::N; ++k) {
-            a[k] = gelu_exact(fmaf(a[k], s_scale[ch + k], s_shift[ch + k]));
+            a[k] = gelu_for<T>(fmaf(a[k], ss[k], sh[k]));
             // both branches are rounded to the element type before the sum, as
             // two separate modules would
             a[k] = to_f<T>(from_f<T>(a[k]));
-            const float bb = to_f<T>(from_f<T>(gelu_exact(fmaf(b[k], c_scale[ch + k], c_shift[ch + k]))));
+            const float bb = to_f<T>(from_f<T>(gelu_for<T>(fmaf(b[k], cs[k], csh[k]))));
             o[k] = a[k] + bb;
         }
         *reinterpret_cast<typename V::Raw*>(out + i * C + ch) = V::pack(o);
