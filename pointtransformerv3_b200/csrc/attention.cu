@@ -189,7 +189,7 @@ static int attention_impl(const void* qkv, const int64_t* order, const int64_t* 
     PTV3_REQUIRE(algo >= 0 && algo <= 4, PTV3_ERR_INVALID_ARGUMENT, "ptv3_attention_fwd: algo %d", algo);
     const bool mma_ok = rpe.grid_coord == nullptr && dtype == PTV3_DTYPE_BF16 &&
                         attn_mma_supported(channels, heads, max_seqlen) &&
-                        n_seq <= 2147483647 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)out & 3) == 0;
+                        n <= 2147483647ll && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)out & 3) == 0;
     const bool tc05_ok = mma_ok && status != nullptr && attn_tc05_supported(channels, heads, max_seqlen) &&
                          ((uintptr_t)out & 15) == 0;
     PTV3_REQUIRE(algo != 4 || tc05_ok, PTV3_ERR_UNSUPPORTED,

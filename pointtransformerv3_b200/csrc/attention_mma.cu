@@ -52,6 +52,10 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* Ks = smem;
     unsigned char* Vs = smem + (size_t)lpad_max * 32;
+    // point row of every padded row of the sequence, negated - 1 where the padded row does not own
+    // its point (borrowed rows): the gather walks pad -> order for every row anyway, and the query
+    // tiles then need one dependent load instead of three
+    int32_t* src_s = reinterpret_cast<int32_t*>(smem + (size_t)lpad_max * 64);
 
     // heads and query slices vary fastest over the grid (blockIdx.x = slice * heads + head): the
     // CTAs of one patch run together, so the rows they all gather from (a row holds every head's
@@ -82,7 +86,9 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
         const uint32_t k0 = smem_u32(Ks) + kv_offset(r, 0), k1 = smem_u32(Ks) + kv_offset(r, 1);
         const uint32_t v0 = smem_u32(Vs) + kv_offset(r, 0), v1 = smem_u32(Vs) + kv_offset(r, 1);
         if (r < L) {
-            const int64_t src = order[pad[start + r]];
+            const int64_t pd = pad[start + r];
+            const int64_t src = order[pd];
+            src_s[r] = unpad[pd] == start + r ? (int32_t)src : -(int32_t)src - 1;
             const __nv_bfloat16* kp = qkv + src * row_stride + C + h * AM_D;
             cp_async16(k0, kp);
             cp_async16(k1, kp + 8);
@@ -107,32 +113,32 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     const uint32_t ks_base = smem_u32(Ks), vs_base = smem_u32(Vs);
     const float sl2 = AM_LOG2E;
 
+    // query rows of a warp's tile, fetched one tile ahead (the row numbers are in shared memory,
+    // so this is a single load per row)
+    auto fetch_q = [&](int tile, uint32_t (&q)[4]) {
+        const int r0 = tile * 16 + g, r1 = r0 + 8;
+        q[0] = q[1] = q[2] = q[3] = 0u;
+        if (tile < tile_hi && r0 < L) {
+            const int32_t e = src_s[r0];
+            const uint32_t* qp = reinterpret_cast<const uint32_t*>(qkv + (int64_t)(e >= 0 ? e : -(e + 1)) * row_stride + h * AM_D);
+            q[0] = qp[t];
+            q[2] = qp[4 + t];
+        }
+        if (tile < tile_hi && r1 < L) {
+            const int32_t e = src_s[r1];
+            const uint32_t* qp = reinterpret_cast<const uint32_t*>(qkv + (int64_t)(e >= 0 ? e : -(e + 1)) * row_stride + h * AM_D);
+            q[1] = qp[t];
+            q[3] = qp[4 + t];
+        }
+    };
+    uint32_t qn[4];
+    fetch_q(tile_lo + warp, qn);
     for (int tile = tile_lo + warp; tile < tile_hi; tile += AM_WARPS) {
         const int r0 = tile * 16 + g, r1 = r0 + 8;
         const bool ok0 = r0 < L, ok1 = r1 < L;
-        int64_t src0 = 0, src1 = 0;
-        bool own0 = false, own1 = false;
-        if (ok0) {
-            const int64_t pd = pad[start + r0];
-            src0 = order[pd];
-            own0 = unpad[pd] == start + r0;
-        }
-        if (ok1) {
-            const int64_t pd = pad[start + r1];
-            src1 = order[pd];
-            own1 = unpad[pd] == start + r1;
-        }
-        uint32_t qa[4] = {0u, 0u, 0u, 0u};
-        if (ok0) {
-            const uint32_t* qp = reinterpret_cast<const uint32_t*>(qkv + src0 * row_stride + h * AM_D);
-            qa[0] = scale_bf16x2(qp[t], scale);
-            qa[2] = scale_bf16x2(qp[4 + t], scale);
-        }
-        if (ok1) {
-            const uint32_t* qp = reinterpret_cast<const uint32_t*>(qkv + src1 * row_stride + h * AM_D);
-            qa[1] = scale_bf16x2(qp[t], scale);
-            qa[3] = scale_bf16x2(qp[4 + t], scale);
-        }
+        const uint32_t qa[4] = {scale_bf16x2(qn[0], scale), scale_bf16x2(qn[1], scale), scale_bf16x2(qn[2], scale),
+                                scale_bf16x2(qn[3], scale)};
+        fetch_q(tile + AM_WARPS, qn);
         float m0 = -INFINITY, m1 = -INFINITY, l0, l1;
         float o[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
         float osum[4] = {0.f, 0.f, 0.f, 0.f};   // row sums of the rounded probabilities: a ones column of V
@@ -221,15 +227,16 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
         }
         l0 = osum[0];
         l1 = osum[2];
-        if (ok0 && own0) {
+        const int32_t e0 = ok0 ? src_s[r0] : -1, e1 = ok1 ? src_s[r1] : -1;     // >= 0: the row owns its point
+        if (e0 >= 0) {
             const float inv = 1.f / l0;
-            uint32_t* op = reinterpret_cast<uint32_t*>(out + src0 * (int64_t)C + h * AM_D);
+            uint32_t* op = reinterpret_cast<uint32_t*>(out + e0 * (int64_t)C + h * AM_D);
             op[t] = pack_bf16(o[0][0] * inv, o[0][1] * inv);
             op[4 + t] = pack_bf16(o[1][0] * inv, o[1][1] * inv);
         }
-        if (ok1 && own1) {
+        if (e1 >= 0) {
             const float inv = 1.f / l1;
-            uint32_t* op = reinterpret_cast<uint32_t*>(out + src1 * (int64_t)C + h * AM_D);
+            uint32_t* op = reinterpret_cast<uint32_t*>(out + e1 * (int64_t)C + h * AM_D);
             op[t] = pack_bf16(o[0][2] * inv, o[0][3] * inv);
             op[4 + t] = pack_bf16(o[1][2] * inv, o[1][3] * inv);
         }
@@ -247,10 +254,10 @@ int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, c
                     bool packed_exp, uint32_t* status, cudaStream_t stream)
 {
     const int lpad = (max_seqlen + AM_KC - 1) / AM_KC * AM_KC;
-    const size_t smem = (size_t)lpad * 64;
+    const size_t smem = (size_t)lpad * 68;      // K, V and the row numbers
     // per device and cheap, so it is simply repeated on every call
     auto kern = packed_exp ? attn_mma_d16_kernel<true> : attn_mma_d16_kernel<false>;
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_MMA_MAX_SEQLEN * 64) !=
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ATTN_MMA_MAX_SEQLEN * 68) !=
         cudaSuccess)
         return check_launch("ptv3_attention_fwd: shared memory attribute");
     // slice the queries of a sequence over several CTAs when there are few (sequence, head) pairs
