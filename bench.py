@@ -43,9 +43,8 @@ CPU_SAMPLE_VOXELS = 100_000
 LIDAR_SCENES = 16
 LIDAR_GRID = 0.05
 # DRAM read + write bytes per row and channel of one attention launch (ncu, dram__bytes_read.sum +
-# dram__bytes_write.sum of a single launch on 240 640 rows x 64 channels gathered through a random
-# permutation, the least local case)
-ATTENTION_DRAM_BYTES_PER_ROW_CHANNEL = 10.74
+# dram__bytes_write.sum of a single launch on 407 552 padded rows x 64 channels: 166.2 + 34.5 MB)
+ATTENTION_DRAM_BYTES_PER_ROW_CHANNEL = 7.70
 
 
 def workload_config(n_gpus, gather=False):
@@ -667,6 +666,20 @@ def run_operator_case(args):
                    roofline_qkv={"kernel": "linear_tc05_kernel<64> (plain mode)", "bound": "hbm",
                                  "achieved": qkv_b / t_qkv / 1e6, "peak": hbm, "unit": "GB/s",
                                  "frac": qkv_b / t_qkv / 1e6 / hbm})
+    elif args.case == "gemm":
+        # the streamed-weight Linear kernel on the shapes of the wide levels (rows x k -> n_out)
+        n, k, n_out = args.points or 7808, 256, 768
+        g = torch.Generator().manual_seed(0)
+        x = torch.randn(n, k, generator=g).bfloat16().to(dev)
+        w = (torch.randn(n_out, k, generator=g) / k ** 0.5).bfloat16().to(dev)
+        b = torch.zeros(n_out).bfloat16().to(dev)
+        st = ops.new_status(dev)
+        t = _time_device(lambda: ops.gemm(x, w, b, None, False, st), args.steps, args.warmup, flush)
+        flops = 2.0 * n * k * n_out
+        out.update(config={"workload": "Linear %d -> %d with streamed weights, bf16" % (k, n_out), "rows": n},
+                   metric="gemm_rows_per_sec", unit="rows/s", value=n / (t * 1e-3), ms=t,
+                   roofline={"kernel": "gemm_tc05_kernel", "bound": "tensor", "achieved": flops / t / 1e9,
+                             "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e9 / tf, "traffic": None})
     elif args.case == "seghead":
         n, c, k = args.points or 407_000, 64, 20
         g = torch.Generator().manual_seed(0)
@@ -745,7 +758,7 @@ def main():
     ap.add_argument("--no-lidar", action="store_true", help="skip the sharded LiDAR-like batch (\"lidar16\")")
     ap.add_argument("--gather-outputs", action="store_true",
                     help="N > 1: all-gather the output features over NCCL inside every step")
-    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "linear", "pooling", "seghead"],
+    ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "linear", "gemm", "pooling", "seghead"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
     ap.add_argument("--algo", type=int, default=0, help="--case attention: algo of ptv3_attention_fwd (4 = tcgen05)")
