@@ -40,17 +40,20 @@
 // columns of its S; O|l in 96..127).
 // Every mbarrier wait is bounded; a wait that runs out sets PTV3_STATUS_WAIT_LIMIT.
 //
-// Measured on B200 (240 000 points, C = 64, 4 heads): 0.45 ms against 0.32 ms of the mma.sync
+// Measured on B200 (240 000 points, C = 64, 4 heads): 0.41 ms against 0.31 ms of the mma.sync
 // kernel (attention_mma.cu), which therefore stays the automatic choice.  Cycle stamps of one
 // group against its issuer show what bounds this kernel: a key block takes a group ~2400
 // cycles whatever the softmax does (all exponentials on the exponential unit, three of eight
 // on the FMA pipe, or none at all), and the next S is seen one block period after the product
-// that makes it was issued.  The period is the tensor pipe working through the 16 products of
-// a round of the four groups (3 x P V' + 1 x Q K^T each): at head dimension 16 every product is
-// tiny (128 x 32 x 16 or 128 x 48 x 16), K is 16 per instruction by the instruction set, so
-// a (patch, head) pair needs ~690 of them at ~150 cycles each, whatever their size; the pipe's
-// time goes to per-instruction overhead, not to arithmetic (~10 % of its rate).  The mma.sync
-// kernel pays for its products with issue slots of the CUDA cores instead, which it has.
+// that makes it was issued.  The period is the asynchronous tensor path working through the
+// 16 products of a round of the four groups (3 x P V' + 1 x Q K^T each): at head dimension 16
+// every product is tiny (128 x 32 x 16 or 128 x 48 x 16), K is 16 per instruction by the
+// instruction set, so a (patch, head) pair needs ~690 of them at ~150 cycles each, whatever
+// their size.  The arithmetic is not what takes the time: the profiler shows the tensor pipe
+// 12 % active, the exponential unit 41 % and instruction issue 65 %; the time goes to the
+// latency of each product through that path (issue, operand fetch from shared and tensor
+// memory, commit), which at this size is not hidden by the next product.  The mma.sync kernel
+// pays for its products with issue slots of the CUDA cores instead, which it has.
 // Earlier forms of this kernel (scores read back every block with the output in registers;
 // two passes with the exact maximum first; one score buffer) all ran at 0.42-0.49 ms for
 // the same reason.
