@@ -571,7 +571,7 @@ def run_operator_case(args):
                              "bound": "tensor", "achieved": flops / t / 1e9,
                              "peak": tf, "unit": "TFLOP/s", "frac": flops / t / 1e9 / tf, "traffic": None})
     elif args.case == "conv":
-        c = 128
+        c = args.channels or 128
         coord, gc = synthetic.indoor_scene(0, args.points or 80_000, GRID)
         n = gc.shape[0]
         ind = torch.cat([torch.zeros(n, 1, dtype=torch.int32), gc], 1).contiguous().to(dev)
@@ -585,13 +585,17 @@ def run_operator_case(args):
         nbr = ops.kmap_build(ind, 3)
         pairs = int((nbr >= 0).sum())
         nbr = nbr.index_select(1, order[0])
-        t = _time_device(lambda: ops.subm_conv(feat, nbr, w, b, row_order=order[0]), args.steps, args.warmup,
-                         flush)
+        status = ops.new_status(dev)
+        t = _time_device(lambda: ops.subm_conv(feat, nbr, w, b, algo=args.algo, row_order=order[0], status=status),
+                         args.steps, args.warmup, flush)
+        if int(status.item()):
+            raise SystemExit("device status 0x%x" % int(status.item()))
         flops = 2.0 * pairs * c * c
-        out.update(config={"workload": "SubMConv3d 3x3x3, C=128, bf16, one indoor scene", "voxels": n,
-                           "pairs": pairs},
+        out.update(config={"workload": "SubMConv3d 3x3x3, C=%d, bf16, one indoor scene" % c, "voxels": n,
+                           "pairs": pairs, "algo": args.algo},
                    metric="conv_voxels_per_sec", unit="voxels/s", value=n / (t * 1e-3), ms=t, kmap_ms=t_map,
-                   roofline={"kernel": "conv_mma_kernel", "bound": "tensor", "achieved": flops / t / 1e9,
+                   roofline={"kernel": "conv_mma_kernel" if args.algo == 2 else "conv_tc05_kernel",
+                             "bound": "tensor", "achieved": flops / t / 1e9,
                              "peak": tf, "unit": "TFLOP/s (useful FLOPs: 2 x pairs x C^2)",
                              "frac": flops / t / 1e9 / tf, "traffic": None},
                    roofline_kmap={"kernel": "km_insert + km_probe", "bound": "hbm",
@@ -761,7 +765,10 @@ def main():
     ap.add_argument("--case", default="forward", choices=["forward", "serialization", "voxelize", "attention", "conv", "stem", "mlp", "linear", "gemm", "pooling", "seghead"],
                     help="forward = the headline workload; the others time one operator of the path")
     ap.add_argument("--points", type=int, default=0, help="size override for the single-operator cases")
-    ap.add_argument("--algo", type=int, default=0, help="--case attention: algo of ptv3_attention_fwd (4 = tcgen05)")
+    ap.add_argument("--algo", type=int, default=0,
+                    help="--case attention: algo of ptv3_attention_fwd (4 = tcgen05); --case conv: algo of "
+                         "ptv3_subm_conv_fwd (2 = mma.sync, 3 = tcgen05)")
+    ap.add_argument("--channels", type=int, default=0, help="--case conv: channel count (default 128)")
     args = ap.parse_args()
     if args.case != "forward":
         run_operator_case(args)

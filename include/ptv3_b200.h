@@ -209,11 +209,17 @@ int ptv3_kmap_build_static(const int32_t* indices, int64_t n, int ksize, int32_t
  *               spatially compact).  When given, column j of nbr must describe
  *               voxel row_order[j], i.e. nbr = kernel_map[:, row_order]; the
  *               result is the same as without it
- *   algo        0 = automatic, 1 = CUDA-core path, 2 = tensor-core path
+ *   algo        0 = automatic, 1 = CUDA-core path, 2 = mma.sync tensor-core path,
+ *               3 = tcgen05 path (bf16, at most 27 offsets, channels 32 -> 32 or
+ *               multiples of 64; accumulates every offset of a tile in tensor memory
+ *               in a fixed order, so the result is the same bit for bit on every run)
+ *   status      one device word, zeroed by the caller; the tcgen05 path sets
+ *               PTV3_STATUS_WAIT_LIMIT in it if a device wait runs out.  May be NULL,
+ *               in which case the tcgen05 path is not used
  */
 int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight, const void* bias,
                        void* out, const int64_t* row_order, int64_t n, int c_in, int c_out,
-                       int kernel_volume, int dtype, int algo, void* stream);
+                       int kernel_volume, int dtype, int algo, uint32_t* status, void* stream);
 
 /*
  * Pair-list form of the submanifold convolution, for levels with few voxels and

@@ -51,7 +51,7 @@ SIGNATURES = {
     "ptv3_kmap_static_max_voxels": (c_i64, []),
     "ptv3_kmap_build_static": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr]),
     "ptv3_subm_conv_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int,
-                                   c_int, c_int, c_ptr]),
+                                   c_int, c_int, c_ptr, c_ptr]),
     "ptv3_conv_pairs_workspace_bytes": (c_sz, [c_i64, c_int]),
     "ptv3_conv_pairs_build": (c_int, [c_ptr, c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_subm_conv_pairs_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_sz,

@@ -118,7 +118,7 @@ extern "C" int ptv3_block_fwd(const ptv3_block_args* a, void* stream_)
                                       dt, stream_));
     else
         STEP(ptv3_subm_conv_fwd(a->conv_in, a->nbr, a->conv_weight, a->conv_bias, b.x, a->row_order, n, C, C, 27,
-                                dt, 0, stream_));
+                                dt, 0, a->status, stream_));
 
     const bool tc_lin = ptv3_linear_supported(C, C, 1, dt) && ptv3_linear_supported(C, 3 * C, 0, dt);
     if (tc_lin) {

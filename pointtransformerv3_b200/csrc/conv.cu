@@ -121,7 +121,7 @@ static int launch_conv_fma(const void* feat, const int32_t* nbr, const void* wei
 extern "C" int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const void* weight,
                                   const void* bias, void* out, const int64_t* row_order, int64_t n,
                                   int c_in, int c_out, int kernel_volume, int dtype, int algo,
-                                  void* stream)
+                                  uint32_t* status, void* stream)
 {
     using namespace ptv3;
     PTV3_REQUIRE(n >= 0 && c_in >= 1 && c_out >= 1 && kernel_volume >= 1, PTV3_ERR_INVALID_ARGUMENT,
@@ -131,13 +131,24 @@ extern "C" int ptv3_subm_conv_fwd(const void* feat, const int32_t* nbr, const vo
     if (n == 0) return PTV3_OK;
     PTV3_REQUIRE(feat && nbr && weight && out, PTV3_ERR_INVALID_ARGUMENT,
                  "ptv3_subm_conv_fwd: null pointer");
-    PTV3_REQUIRE(algo >= 0 && algo <= 2, PTV3_ERR_INVALID_ARGUMENT, "ptv3_subm_conv_fwd: algo %d", algo);
+    PTV3_REQUIRE(algo >= 0 && algo <= 3, PTV3_ERR_INVALID_ARGUMENT, "ptv3_subm_conv_fwd: algo %d", algo);
     const bool mma_ok = dtype == PTV3_DTYPE_BF16 && conv_mma_supported(c_in, c_out, kernel_volume) &&
                         ((uintptr_t)feat & 15) == 0 && ((uintptr_t)weight & 15) == 0 &&
                         ((uintptr_t)out & 3) == 0;
     PTV3_REQUIRE(algo != 2 || mma_ok, PTV3_ERR_UNSUPPORTED,
                  "ptv3_subm_conv_fwd: the tensor-core path needs bf16, <= 27 offsets, channels 32->32 or "
                  "C_in %% 64 == 0 with C_out 64 or a multiple of 128, and 16-byte aligned tensors");
+    const bool tc_ok = dtype == PTV3_DTYPE_BF16 && conv_tc05_supported(c_in, c_out, kernel_volume) && status &&
+                       n < (1ll << 31) && ((uintptr_t)feat & 15) == 0 && ((uintptr_t)weight & 15) == 0 &&
+                       ((uintptr_t)out & 15) == 0;
+    PTV3_REQUIRE(algo != 3 || tc_ok, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_subm_conv_fwd: the tcgen05 path needs bf16, <= 27 offsets, channels 32->32 or multiples of "
+                 "64, a status word and 16-byte aligned tensors");
+    // automatic choice: tensor memory for 64 channels and more; at 32 channels a stage of the tcgen05
+    // pipeline is too small for its fixed cost and the mma.sync kernel is faster
+    if (tc_ok && (algo == 3 || (algo == 0 && c_in >= 64)))
+        return launch_conv_tc05(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kernel_volume, status,
+                                (cudaStream_t)stream);
     if (mma_ok && algo != 1)
         return launch_conv_mma(feat, nbr, weight, bias, out, row_order, n, c_in, c_out, kernel_volume,
                                (cudaStream_t)stream);

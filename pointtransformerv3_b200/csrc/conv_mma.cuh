@@ -1,4 +1,4 @@
-// Launcher of the tensor-core submanifold convolution path (conv_mma.cu).
+// Launchers of the tensor-core submanifold convolution paths (conv_mma.cu, conv_tc05.cu).
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -12,6 +12,13 @@ bool conv_mma_supported(int c_in, int c_out, int kernel_volume);
 int launch_conv_mma(const void* feat, const int32_t* nbr, const void* weight, const void* bias,
                     void* out, const int64_t* row_order, int64_t n, int c_in, int c_out,
                     int kernel_volume, cudaStream_t stream);
+
+// tcgen05 form (conv_tc05.cu): same operands, accumulator in tensor memory; `status` receives
+// PTV3_STATUS_WAIT_LIMIT if a device wait runs out.
+bool conv_tc05_supported(int c_in, int c_out, int kernel_volume);
+int launch_conv_tc05(const void* feat, const int32_t* nbr, const void* weight, const void* bias, void* out,
+                     const int64_t* row_order, int64_t n, int c_in, int c_out, int kernel_volume,
+                     uint32_t* status, cudaStream_t stream);
 
 // Pair-list form (coarse levels): pairs sorted by kernel offset, 128-pair tiles,
 // atomic fixed-point accumulation into acc (n x c_out 64-bit integers of workspace), then

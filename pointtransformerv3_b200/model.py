@@ -786,6 +786,7 @@ class PointTransformerV3(PointModule):
         #    level s + 2 while stage s runs), so that their host reads never wait behind, and
         #    never hold up, the feature kernels.
         main = torch.cuda.current_stream()
+        feat_dtype = point.feat.dtype
         point["_sparse_indices"] = point._sparse_indices()
         serialized = torch.cuda.Event()
         serialized.record(main)
@@ -796,7 +797,7 @@ class PointTransformerV3(PointModule):
         with torch.cuda.stream(side):
             kmaps0 = spconv.prebuild_kernel_map(
                 point["_sparse_indices"], point.serialized_order[0], 3, status,
-                with_pairs=point.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
+                with_pairs=_stage_uses_pairs(self.enc._modules.get("enc0"), point.batch.shape[0], feat_dtype))
         _record_stream(kmaps0, main)
         point["_prebuilt_kmaps"] = kmaps0
         events = {0: torch.cuda.Event()}
@@ -824,7 +825,7 @@ class PointTransformerV3(PointModule):
                     child["_sparse_indices"] = child._sparse_indices()
                     child["_prebuilt_kmaps"] = spconv.prebuild_kernel_map(
                         child["_sparse_indices"], child.serialized_order[0], 3, status,
-                        with_pairs=child.batch.shape[0] <= spconv.PAIR_PATH_MAX_VOXELS)
+                        with_pairs=_stage_uses_pairs(stage, child.batch.shape[0], feat_dtype))
                     # ... and the patch layout of the stage's attention blocks
                     for m in stage:
                         if isinstance(m, Block) and m.attn.enable_flash:
@@ -905,6 +906,17 @@ def _linear_op(x, linear, status):
         if linear.bias is not None and ops.linear_supported(k, n_out, False, x.dtype):
             return ops.linear(x, linear.weight, linear.bias, status)
     return linear(x)
+
+
+def _stage_uses_pairs(stage, n, dtype):
+    """Whether the 3x3x3 convolutions of the stage's blocks will ask for the pair list of this level
+    (it is then made ahead of time with the kernel map; otherwise a convolution that wants one
+    builds it when it runs)."""
+    for m in (stage or []):
+        if isinstance(m, Block):
+            conv = m.cpe[0]
+            return spconv.uses_pair_path(n, conv.in_channels, conv.out_channels, dtype, conv.kernel_size)
+    return False
 
 
 def _single_call_ok(feat, linear):

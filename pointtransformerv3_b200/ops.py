@@ -214,9 +214,11 @@ def kmap_build(indices, ksize, status=None):
     return nbr
 
 
-def subm_conv(feat, nbr, weight, bias=None, algo=0, row_order=None):
+def subm_conv(feat, nbr, weight, bias=None, algo=0, row_order=None, status=None):
     """feat (N,Cin), nbr (k^3,N) int32, weight (Cout,k,k,k,Cin) -> (N,Cout).
-    row_order: optional (N,) int64 permutation used to group voxels into tiles."""
+    row_order: optional (N,) int64 permutation used to group voxels into tiles.
+    status: device status word of the caller (read later); without one a fresh word
+    is made and checked here (one host sync)."""
     _lib.require_cuda(feat, nbr, weight, bias)
     lib = _lib.load()
     feat = feat.contiguous()
@@ -229,11 +231,16 @@ def subm_conv(feat, nbr, weight, bias=None, algo=0, row_order=None):
     if bias is not None and bias.dtype != feat.dtype:
         raise ValueError("bias dtype %s != feature dtype %s" % (bias.dtype, feat.dtype))
     out = torch.empty((n, cout), dtype=feat.dtype, device=feat.device)
+    own = status is None
+    if own:
+        status = new_status(feat.device)
     with timed("subm_conv_k%d" % round(kvol ** (1 / 3)), 2.0 * n * kvol * cin * cout):
         _lib.check(lib.ptv3_subm_conv_fwd(_lib.ptr(feat), _lib.ptr(nbr), _lib.ptr(weight.contiguous()),
                                           _lib.ptr(bias), _lib.ptr(out), _lib.ptr(row_order), n, cin, cout, kvol,
-                                          _lib.dtype_id(feat), int(algo), _lib.stream()),
+                                          _lib.dtype_id(feat), int(algo), _lib.ptr(status), _lib.stream()),
                    "ptv3_subm_conv_fwd")
+    if own:
+        _lib.raise_on_status(status, "ptv3_subm_conv_fwd")
     return out
 
 

@@ -10,9 +10,18 @@ import torch.nn as nn
 from . import ops
 
 
-# largest level handled by the pair-list convolution (its fp32 accumulation buffer
-# and pair arrays stay small, and above this size output-stationary tiles win)
+# The pair-list convolution multiplies only the (input, output) pairs that exist, 128 pairs of one
+# offset at a time, so a slice of the weights serves 128 useful rows; an output-stationary tile of a
+# coarse level uses it for the ~40 voxels of its 128 that have that neighbour.  That pays when the
+# weights are the bulk of the traffic: few voxels and very wide channels.
 PAIR_PATH_MAX_VOXELS = 65536
+PAIR_PATH_MIN_CHANNELS = 512
+
+
+def uses_pair_path(n, in_channels, out_channels, dtype, kernel_size=3):
+    """Whether a 3x3x3 convolution of this shape runs on the pair list (else on the kernel map)."""
+    return (dtype == torch.bfloat16 and kernel_size == 3 and n <= PAIR_PATH_MAX_VOXELS
+            and in_channels >= PAIR_PATH_MIN_CHANNELS and in_channels % 64 == 0 and out_channels % 128 == 0)
 
 
 class SparseConvTensor:
@@ -132,16 +141,16 @@ class SubMConv3d(SparseModule):
         geo = self.geometry(x)
         if "pair_in" in geo:
             return x.replace_feature(ops.subm_conv_pairs(x.features, geo, self.weight, self.bias))
-        return x.replace_feature(ops.subm_conv(x.features, geo["nbr"], self.weight, self.bias,
-                                               row_order=geo["row_order"]))
+        out = ops.subm_conv(x.features, geo["nbr"], self.weight, self.bias, row_order=geo["row_order"],
+                            status=x.status if x.defer_status else None)
+        return x.replace_feature(out)
 
     def geometry(self, x):
         """The index structure this convolution runs on for the sparse tensor ``x``:
-        the pair list on coarse levels (few voxels, wide channels: only the pairs
-        that exist are multiplied), else dict(nbr, row_order) of the kernel map."""
-        n = x.features.shape[0]
-        if (x.features.dtype == torch.bfloat16 and self.kernel_size == 3 and n <= PAIR_PATH_MAX_VOXELS
-                and self.in_channels % 64 == 0 and self.out_channels % 128 == 0 and self.in_channels >= 128):
+        the pair list on the coarsest levels (few voxels, very wide channels: only the
+        pairs that exist are multiplied), else dict(nbr, row_order) of the kernel map."""
+        if uses_pair_path(x.features.shape[0], self.in_channels, self.out_channels, x.features.dtype,
+                          self.kernel_size):
             return x.pair_list(self.kernel_size, self.indice_key)
         nbr, row_order = x.kernel_map(self.kernel_size, self.indice_key)
         return {"nbr": nbr, "row_order": row_order}

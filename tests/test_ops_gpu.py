@@ -309,6 +309,42 @@ def test_subm_conv_tensor_core_path(c, permuted):
     assert rel_l2(got, ref) < 4e-3
 
 
+@pytest.mark.parametrize("permuted", [False, True])
+@pytest.mark.parametrize("cin,cout,shift", [(32, 32, 0), (64, 64, 0), (128, 128, 1), (256, 256, 2), (512, 512, 3),
+                                            (64, 192, 1)])
+def test_subm_conv_tcgen05_path(cin, cout, shift, permuted):
+    """bf16 convolution with the accumulator in tensor memory against the fp32 oracle and the
+    mma.sync path, on a fine level and on coarsened ones (denser neighbourhoods), sizes that are not
+    multiples of the tile, and twice for bit-identical results."""
+    data = small_batch([6000, 2500], 8 + shift)
+    batch = O.offset_to_batch(data["offset"])
+    ind = O.sparse_indices(batch, data["grid_coord"] >> shift)
+    ind = torch.unique(ind, dim=0)
+    n = ind.shape[0]
+    g = torch.Generator().manual_seed(cin + cout)
+    feat = torch.randn(n, cin, generator=g).bfloat16()
+    w = (torch.randn(cout, 3, 3, 3, cin, generator=g) / (9 * cin) ** 0.5).bfloat16()
+    b = (torch.randn(cout, generator=g) * 0.1).bfloat16()
+    ref = O.subm_conv(feat.float(), O.kernel_map(ind, 3), w.float(), b.float())
+    nbr = ops.kmap_build(ind.cuda(), 3)
+    row_order = None
+    if permuted:
+        code, order, inverse, depth = O.serialization(ind[:, 1:], ind[:, 0].long(), ["z"])
+        row_order = order[0].cuda()
+        nbr = nbr.index_select(1, row_order)
+    got = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=3, row_order=row_order)
+    again = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=3, row_order=row_order)
+    assert torch.equal(got, again)
+    assert_close(got, ref, what="tcgen05 conv vs fp32 oracle", **TOL[torch.bfloat16])
+    assert rel_l2(got, ref) < 4e-3
+    if cin == cout:
+        base = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=2, row_order=row_order)
+        assert_close(got, base, atol=1e-2, rtol=1e-2, what="tcgen05 vs mma.sync conv")
+    nb = ops.subm_conv(feat.cuda(), nbr, w.cuda(), None, algo=3, row_order=row_order)
+    assert_close(nb, O.subm_conv(feat.float(), O.kernel_map(ind, 3), w.float(), None), what="no bias",
+                 **TOL[torch.bfloat16])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("C", [32, 48, 64, 128, 256, 512])
 def test_add_layernorm(C, dtype):
