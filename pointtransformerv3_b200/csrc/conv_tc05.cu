@@ -48,12 +48,6 @@ struct ConvTcArgs {
     uint32_t* status;
 };
 
-// 16-byte copy that writes zeros when `valid` is false (nothing is read then)
-__device__ __forceinline__ void cp_async16_zfill(uint32_t saddr, const void* gptr, bool valid)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(saddr), "l"(gptr), "r"(valid ? 16 : 0));
-}
-
 template <int BN, int KC, int STAGES, int LAGW>
 __global__ void __launch_bounds__(CT_THREADS) conv_tc05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                const ConvTcArgs a)

@@ -17,6 +17,7 @@
 // pass that forms it and the pass that normalises it.  Every intermediate the unfused
 // sequence would round to bf16 is rounded at the same place.  Waits are bounded.
 #include "common.cuh"
+#include "mma_util.cuh"
 #include "tc05.cuh"
 #include "vec.cuh"
 
@@ -38,12 +39,37 @@ struct LinearArgs {
     int64_t n;
     int n_out;
     int groups;       // 128-thread groups that work (1..4)
+    int nacc;         // accumulators per group in tensor memory (2 where 2 x groups x columns fit in 512)
     int w_box_rows;   // rows per TMA box of W
     int residual_mode;
     uint32_t* status;
 };
 
 __device__ __forceinline__ float lin_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// ---- pairs of floats in one 64-bit register (low word = first of the pair) ------------------------
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+// a bf16x2 word as a pair of floats
+__device__ __forceinline__ uint64_t unpack_bf16x2(uint32_t w) { return pack2u(w << 16, w & 0xffff0000u); }
+// both floats rounded to bf16 (round to nearest even); `packed` receives the bf16x2 word
+__device__ __forceinline__ uint64_t round2(uint64_t v, uint32_t& packed)
+{
+    float lo, hi;
+    unpack2(v, lo, hi);
+    packed = pack_bf16(lo, hi);
+    return unpack_bf16x2(packed);
+}
+__device__ __forceinline__ float hsum2(uint64_t v)
+{
+    float lo, hi;
+    unpack2(v, lo, hi);
+    return lo + hi;
+}
 
 // Staging tile of a group: 128 rows x 64 bf16 columns, rows 144 bytes apart, so that
 // both the row-per-thread accesses of the epilogue and the coalesced copies to and
@@ -98,16 +124,17 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
     float* par = reinterpret_cast<float*>(smem + off_par);
     float *bias_s = par, *g1 = par + n_out, *b1 = par + 2 * n_out, *g2 = par + 3 * n_out, *b2 = par + 4 * n_out;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off_bar);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5;
     const int g = tid >> 7, t = tid & 127;
     const uint32_t wbar = sbase + off_bar;
-    const uint32_t xbar0 = wbar + 8 * (1 + 2 * g), mbar = wbar + 8 * (9 + g);   // xbar0 + 8: second x buffer
+    // xbar0 + 8: second x buffer; mbar0 + 8: second accumulator
+    const uint32_t xbar0 = wbar + 8 * (1 + 2 * g), mbar0 = wbar + 8 * (9 + 2 * g);
 
     if (tid == 0) {
-        for (int i = 0; i < 13; ++i) mbar_init(wbar + 8 * i, 1);
+        for (int i = 0; i < 17; ++i) mbar_init(wbar + 8 * i, 1);
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_x);
@@ -120,7 +147,7 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
         g2[i] = a.ln2_w ? __bfloat162float(a.ln2_w[i]) : 1.f;
         b2[i] = a.ln2_b ? __bfloat162float(a.ln2_b[i]) : 0.f;
     }
-    if (warp == 0) tmem_alloc(sbase + off_bar + 104, 512);
+    if (warp == 0) tmem_alloc(sbase + off_bar + 136, 512);
     fence_before_sync();
     __syncthreads();
     fence_after_sync();
@@ -137,8 +164,12 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
     // columns of tensor memory per group: n_out rounded up to 32, groups side by side
     const int tm_cols = (n_out + 31) / 32 * 32;
     const uint32_t tm_lane = (uint32_t)((warp & 3) * 32) << 16;
-    const uint32_t tm_acc = tmem_base + tm_lane + g * tm_cols;
-    const uint32_t tm_acc_mma = tmem_base + g * tm_cols;
+    // two accumulators per group where tensor memory has room (a.nacc == 2): the product of the next
+    // tile is issued before this tile's epilogue starts, so no tile waits for its product
+    const int nacc = a.nacc;
+    const uint32_t tm_acc_step = (uint32_t)(a.groups * tm_cols);
+    const uint32_t tm_acc0 = tmem_base + tm_lane + g * tm_cols;
+    const uint32_t tm_acc_mma0 = tmem_base + g * tm_cols;
     const uint32_t xs0 = sbase + off_x + 2 * g * X_BYTES;   // two x buffers
     unsigned char* stage = smem + off_stage + g * LIN_STAGE_BYTES;
     unsigned char* my_row = stage + t * LIN_STAGE_ROW;
@@ -147,7 +178,7 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
     // one MMA covers at most 256 output columns
     const int n_half = n_out > 256 ? n_out / 2 : n_out;
     const uint32_t idesc = umma_idesc_bf16(128, n_half);
-    uint32_t xph[2] = {0, 0}, mph = 0;
+    uint32_t xph[2] = {0, 0};
     const float inv_c = 1.f / (float)n_out;
     const int nchunks = n_out / 32;
 
@@ -170,34 +201,83 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                 for (int b = 0; b < n_out * 2; b += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"(p + b));
             }
         };
-        if (t == 0 && tile0 < ntiles) load_x(tile0, 0);
-        prefetch_residual(tile0);
-        int buf = 0;
-        for (int64_t tile = tile0; tile < ntiles; tile += tile_step, buf ^= 1) {
-            const int64_t row0 = tile * 128;
-            const uint32_t xs = xs0 + buf * X_BYTES;
-            ok &= mbar_wait(xbar0 + 8 * buf, xph[buf], abort);
-            xph[buf] ^= 1;
-            prefetch_residual(tile + tile_step);
-            if (t == 0) {
-                // the other buffer was consumed by the previous tile's MMAs, which have completed:
-                // fetch the next tile into it while this tile is multiplied and written out
-                if (tile + tile_step < ntiles) load_x(tile + tile_step, buf ^ 1);
-                fence_after_sync();
-                for (int h = 0; h < n_out; h += n_half) {
-#pragma unroll
-                    for (int k = 0; k < K / 16; ++k) {
-                        const int kb = (k * 16) / KCOLS, kk = (k * 16) % KCOLS;
-                        const uint64_t da = umma_desc_kmajor(xs + kb * X_BLOCK + kk * 2, SW);
-                        const uint64_t db = umma_desc_kmajor(sbase + kb * w_block + h * SW + kk * 2, SW);
-                        umma_bf16(tm_acc_mma + h, da, db, idesc, k > 0);
-                    }
-                }
-                umma_commit(mbar);
-            }
-            ok &= mbar_wait(mbar, mph, abort);
-            mph ^= 1;
+        // t == 0 only: the product of the x tile in buffer xb into accumulator acc
+        auto issue_mma = [&](int xb, int acc) {
+            const uint32_t xs = xs0 + xb * X_BYTES;
             fence_after_sync();
+            for (int h = 0; h < n_out; h += n_half) {
+#pragma unroll
+                for (int k = 0; k < K / 16; ++k) {
+                    const int kb = (k * 16) / KCOLS, kk = (k * 16) % KCOLS;
+                    const uint64_t da = umma_desc_kmajor(xs + kb * X_BLOCK + kk * 2, SW);
+                    const uint64_t db = umma_desc_kmajor(sbase + kb * w_block + h * SW + kk * 2, SW);
+                    umma_bf16(tm_acc_mma0 + acc * tm_acc_step + h, da, db, idesc, k > 0);
+                }
+            }
+            umma_commit(mbar0 + 8 * acc);
+        };
+        // residual slab 0 of a tile into the staging tile, asynchronously (the staging tile is free
+        // from the end of one tile to the residual pass of the next)
+        auto fetch_residual = [&](int64_t row0) {
+            if (!a.residual_mode) return;
+            if (n_out >= 64) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+                    const bool in = row0 + r < a.n;
+                    cp_async16_zfill(smem_u32_generic(stage + r * LIN_STAGE_ROW + c * 16),
+                                     a.residual + (in ? row0 + r : 0) * n_out + c * 8, in);
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                    const bool in = row0 + r < a.n;
+                    cp_async16_zfill(smem_u32_generic(stage + r * LIN_STAGE_ROW + c * 16),
+                                     a.residual + (in ? row0 + r : 0) * n_out + c * 8, in);
+                }
+            }
+            cp_async_commit();
+        };
+        if (t == 0 && tile0 < ntiles) {
+            load_x(tile0, 0);
+            if (nacc == 2) {
+                ok &= mbar_wait(xbar0, xph[0], abort);
+                xph[0] ^= 1;
+                issue_mma(0, 0);
+                if (tile0 + tile_step < ntiles) load_x(tile0 + tile_step, 1);
+            }
+        }
+        int j = 0;
+        for (int64_t tile = tile0; tile < ntiles; tile += tile_step, ++j) {
+            const int64_t row0 = tile * 128;
+            const int buf = j & 1, cur = nacc == 2 ? buf : 0;
+            fetch_residual(row0);
+            prefetch_residual(tile + tile_step);
+            if (nacc == 2) {
+                ok &= mbar_wait(mbar0 + 8 * cur, (j >> 1) & 1, abort);
+                if (t == 0 && tile + tile_step < ntiles) {
+                    // the next tile's product into the other accumulator (its epilogue ended with
+                    // the barrier that closed the previous tile), then the x tile after that into
+                    // the buffer this tile's product has finished with
+                    ok &= mbar_wait(xbar0 + 8 * (buf ^ 1), xph[buf ^ 1], abort);
+                    xph[buf ^ 1] ^= 1;
+                    issue_mma(buf ^ 1, buf ^ 1);
+                    if (tile + 2 * tile_step < ntiles) load_x(tile + 2 * tile_step, buf);
+                }
+            } else {
+                ok &= mbar_wait(xbar0 + 8 * buf, xph[buf], abort);
+                xph[buf] ^= 1;
+                if (t == 0) {
+                    // the other buffer was consumed by the previous tile's MMAs, which have completed:
+                    // fetch the next tile into it while this tile is multiplied and written out
+                    if (tile + tile_step < ntiles) load_x(tile + tile_step, buf ^ 1);
+                    issue_mma(buf, 0);
+                }
+                ok &= mbar_wait(mbar0, j & 1, abort);
+            }
+            fence_after_sync();
+            const uint32_t tm_acc = tm_acc0 + cur * tm_acc_step;
             const int64_t row = row0 + t;
             const bool live = row < a.n;
             if (!a.residual_mode) {
@@ -231,33 +311,49 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                     named_barrier(1 + g, 128);
                 }
             } else {
+                // The arithmetic below works on pairs of channels (fma.rn.f32x2 / add.rn.f32x2), reads the
+                // per-channel parameters two pairs at a time and converts to bf16 once per rounding
+                // (cvt.rn.bf16x2.f32; the rounded floats are the two halves of that word): the epilogue
+                // is bound by instruction issue, not by memory.
                 // ---- first LayerNorm (optional): statistics of y = round(acc + bias)
                 float mean1 = 0.f, rstd1 = 1.f;
                 if (a.ln1_w) {
                     // one pass with sums shifted by the row's first value (no cancellation)
-                    float sh = 0.f, s1 = 0.f, q1 = 0.f;
+                    float sh = 0.f;
+                    uint64_t nsh2 = 0, s1 = 0, q1 = 0;
                     for (int c = 0; c < nchunks; ++c) {
                         uint32_t v[32];
                         tmem_ld32(tm_acc + c * 32, v);
                         tmem_ld_wait();
-                        if (c == 0) sh = lin_round(__uint_as_float(v[0]) + bias_s[0]);
+                        if (c == 0) {
+                            sh = lin_round(__uint_as_float(v[0]) + bias_s[0]);
+                            nsh2 = pack2(-sh, -sh);
+                        }
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            const float d = lin_round(__uint_as_float(v[i]) + bias_s[c * 32 + i]) - sh;
-                            s1 += d;
-                            q1 = fmaf(d, d, q1);
+                        for (int i = 0; i < 32; i += 4) {
+                            const ulonglong2 bb = *reinterpret_cast<const ulonglong2*>(bias_s + c * 32 + i);
+                            uint32_t pk;
+                            const uint64_t d0 = add2(round2(add2(pack2u(v[i], v[i + 1]), bb.x), pk), nsh2);
+                            const uint64_t d1 = add2(round2(add2(pack2u(v[i + 2], v[i + 3]), bb.y), pk), nsh2);
+                            s1 = add2(s1, add2(d0, d1));
+                            q1 = fma2(d0, d0, q1);
+                            q1 = fma2(d1, d1, q1);
                         }
                     }
-                    const float md1 = s1 * inv_c;
+                    const float md1 = hsum2(s1) * inv_c;
                     mean1 = sh + md1;
-                    rstd1 = rsqrtf(fmaxf(q1 * inv_c - md1 * md1, 0.f) + a.eps1);
+                    rstd1 = rsqrtf(fmaxf(hsum2(q1) * inv_c - md1 * md1, 0.f) + a.eps1);
                 }
+                const uint64_t nmean1 = pack2(-mean1, -mean1), rs1 = pack2(rstd1, rstd1);
                 // ---- s = residual + t, stored and parked in tensor memory; shifted sums for LN2
-                float shift = 0.f, s2 = 0.f, q2 = 0.f;
+                float shift = 0.f;
+                uint64_t nshift2 = 0, s2p = 0, q2p = 0;
                 for (int sl = 0; sl < nslabs; ++sl) {
                     const int cw = min(64, n_out - sl * 64);
-                    // residual slab: coalesced into the staging tile
-                    if (cw == 64) {
+                    // residual slab: coalesced into the staging tile (slab 0 was asked for at the top)
+                    if (sl == 0) {
+                        cp_async_wait<0>();
+                    } else if (cw == 64) {
                         global_to_stage(stage, a.residual, row0, a.n, n_out, sl * 64, t);
                     } else {
 #pragma unroll
@@ -276,22 +372,42 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                         tmem_ld_wait();
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            float r[8], f[8];
-                            Vec<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(my_row + c * 64 + q * 16), r);
+                            const uint4 rr = *reinterpret_cast<const uint4*>(my_row + c * 64 + q * 16);
+                            const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+                            uint32_t ow[4];
+                            const int ch0 = sl * 64 + c * 32 + q * 8;
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int ch = sl * 64 + c * 32 + q * 8 + i;
-                                float y = lin_round(__uint_as_float(v[q * 8 + i]) + bias_s[ch]);
-                                if (a.ln1_w) y = lin_round(fmaf((y - mean1) * rstd1, g1[ch], b1[ch]));
-                                const float sv = lin_round(r[i] + y);
-                                if (ch == 0) shift = sv;
-                                const float d = sv - shift;
-                                s2 += d;
-                                q2 = fmaf(d, d, q2);
-                                f[i] = sv;
-                                v[q * 8 + i] = __float_as_uint(sv);
+                            for (int h = 0; h < 2; ++h) {
+                                const ulonglong2 bb = *reinterpret_cast<const ulonglong2*>(bias_s + ch0 + h * 4);
+                                ulonglong2 gg = {0, 0}, hh = {0, 0};
+                                if (a.ln1_w) {
+                                    gg = *reinterpret_cast<const ulonglong2*>(g1 + ch0 + h * 4);
+                                    hh = *reinterpret_cast<const ulonglong2*>(b1 + ch0 + h * 4);
+                                }
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const int i = q * 8 + h * 4 + e * 2;      // first of the two columns
+                                    uint32_t pk;
+                                    uint64_t y = round2(add2(pack2u(v[i], v[i + 1]), e ? bb.y : bb.x), pk);
+                                    if (a.ln1_w)
+                                        y = round2(fma2(fma2(add2(y, nmean1), rs1, 0ull), e ? gg.y : gg.x,
+                                                        e ? hh.y : hh.x), pk);
+                                    const uint64_t sv = round2(add2(unpack_bf16x2(rw[h * 2 + e]), y), pk);
+                                    ow[h * 2 + e] = pk;
+                                    if (sl == 0 && c == 0 && q == 0 && h == 0 && e == 0) {
+                                        float lo, hi;
+                                        unpack2(sv, lo, hi);
+                                        shift = lo;
+                                        nshift2 = pack2(-lo, -lo);
+                                    }
+                                    const uint64_t d = add2(sv, nshift2);
+                                    s2p = add2(s2p, d);
+                                    q2p = fma2(d, d, q2p);
+                                    v[i] = (uint32_t)sv;
+                                    v[i + 1] = (uint32_t)(sv >> 32);
+                                }
                             }
-                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = Vec<__nv_bfloat16>::pack(f);
+                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                         }
                         tmem_st32(tm_acc + sl * 64 + c * 32, v);
                     }
@@ -311,10 +427,12 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                     }
                     named_barrier(1 + g, 128);
                 }
+                const float s2 = hsum2(s2p), q2 = hsum2(q2p);
                 tmem_st_wait();
                 const float md = s2 * inv_c;                      // mean - shift
                 const float var = fmaxf(q2 * inv_c - md * md, 0.f);
                 const float mean2 = shift + md, rstd2 = rsqrtf(var + a.eps2);
+                const uint64_t nmean2 = pack2(-mean2, -mean2), rs2 = pack2(rstd2, rstd2);
                 for (int sl = 0; sl < nslabs; ++sl) {
                     const int cw = min(64, n_out - sl * 64);
                     for (int c = 0; c < cw / 32; ++c) {
@@ -323,13 +441,23 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                         tmem_ld_wait();
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            float f[8];
+                            uint32_t ow[4];
+                            const int ch0 = sl * 64 + c * 32 + q * 8;
 #pragma unroll
-                            for (int i = 0; i < 8; ++i) {
-                                const int ch = sl * 64 + c * 32 + q * 8 + i;
-                                f[i] = fmaf((__uint_as_float(v[q * 8 + i]) - mean2) * rstd2, g2[ch], b2[ch]);
+                            for (int h = 0; h < 2; ++h) {
+                                const ulonglong2 gg = *reinterpret_cast<const ulonglong2*>(g2 + ch0 + h * 4);
+                                const ulonglong2 hh = *reinterpret_cast<const ulonglong2*>(b2 + ch0 + h * 4);
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const int i = q * 8 + h * 4 + e * 2;
+                                    const uint64_t f = fma2(fma2(add2(pack2u(v[i], v[i + 1]), nmean2), rs2, 0ull),
+                                                            e ? gg.y : gg.x, e ? hh.y : hh.x);
+                                    float lo, hi;
+                                    unpack2(f, lo, hi);
+                                    ow[h * 2 + e] = pack_bf16(lo, hi);
+                                }
                             }
-                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = Vec<__nv_bfloat16>::pack(f);
+                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                         }
                     }
                     named_barrier(1 + g, 128);
@@ -373,16 +501,17 @@ static int launch_linear(const void* x, const void* w, LinearArgs a, int k, cuda
     if (groups > 4) groups = 4;
     // ... and as many as fit in shared memory next to the resident weights
     while (groups > 1 && (size_t)kb * a.n_out * sw + (size_t)groups * (2 * kb * 128 * sw + LIN_STAGE_BYTES) +
-                                 5 * (size_t)a.n_out * 4 + 128 + 1024 > 220 * 1024)
+                                 5 * (size_t)a.n_out * 4 + 160 + 1024 > 220 * 1024)
         --groups;
     a.groups = groups;
+    a.nacc = 2 * groups * tm_cols <= 512 ? 2 : 1;
     CUtensorMap mx, mw;
     int rc = make_tensor_map_bf16(&mx, x, (uint64_t)a.n, k, (uint64_t)k * 2, 128, kcols);
     if (rc) return rc;
     rc = make_tensor_map_bf16(&mw, w, a.n_out, k, (uint64_t)k * 2, a.w_box_rows, kcols);
     if (rc) return rc;
     const size_t smem = (size_t)kb * a.n_out * sw + (size_t)groups * (2 * kb * 128 * sw + LIN_STAGE_BYTES) +
-                        5 * (size_t)a.n_out * 4 + 128 + 1024;
+                        5 * (size_t)a.n_out * 4 + 160 + 1024;
     const size_t smem_req = smem < 120 * 1024 ? 120 * 1024 : smem;   // one CTA per SM (it takes all of tensor memory)
     const int64_t ntiles = (a.n + 127) / 128;
     int64_t grid = (ntiles + groups - 1) / groups;

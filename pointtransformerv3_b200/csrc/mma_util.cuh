@@ -14,6 +14,11 @@ __device__ __forceinline__ void cp_async16(uint32_t saddr, const void* gptr)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(saddr), "l"(gptr));
 }
+// 16-byte copy that writes zeros when `valid` is false (nothing is read then)
+__device__ __forceinline__ void cp_async16_zfill(uint32_t saddr, const void* gptr, bool valid)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(saddr), "l"(gptr), "r"(valid ? 16 : 0));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait()
