@@ -47,30 +47,6 @@ struct LinearArgs {
 
 __device__ __forceinline__ float lin_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-// ---- pairs of floats in one 64-bit register (low word = first of the pair) ------------------------
-__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi)
-{
-    uint64_t r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
-    return r;
-}
-// a bf16x2 word as a pair of floats
-__device__ __forceinline__ uint64_t unpack_bf16x2(uint32_t w) { return pack2u(w << 16, w & 0xffff0000u); }
-// both floats rounded to bf16 (round to nearest even); `packed` receives the bf16x2 word
-__device__ __forceinline__ uint64_t round2(uint64_t v, uint32_t& packed)
-{
-    float lo, hi;
-    unpack2(v, lo, hi);
-    packed = pack_bf16(lo, hi);
-    return unpack_bf16x2(packed);
-}
-__device__ __forceinline__ float hsum2(uint64_t v)
-{
-    float lo, hi;
-    unpack2(v, lo, hi);
-    return lo + hi;
-}
-
 // Staging tile of a group: 128 rows x 64 bf16 columns, rows 144 bytes apart, so that
 // both the row-per-thread accesses of the epilogue and the coalesced copies to and
 // from global memory (consecutive threads on consecutive 16-byte pieces) are free of

@@ -172,14 +172,25 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
                 tmem_ld_wait();
                 const float* bb = b1s + ch * Cfg::HC + cg * 32;
                 unsigned char* blk = hs_ptr + (cg >> 1) * Cfg::H_BLOCK + t * 128;
+                // pairs of channels: packed fp32 arithmetic, parameters two pairs per load
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    float f[8];
+                    uint32_t ow[4];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i)
-                        f[i] = gelu_tanh_erf(bf16_round(__uint_as_float(v[q * 8 + i]) + bb[q * 8 + i]));
+                    for (int h = 0; h < 2; ++h) {
+                        const ulonglong2 b2 = *reinterpret_cast<const ulonglong2*>(bb + q * 8 + h * 4);
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int i = q * 8 + h * 4 + e * 2;
+                            uint32_t pk;
+                            const uint64_t y = round2(add2(pack2u(v[i], v[i + 1]), e ? b2.y : b2.x), pk);
+                            float lo, hi;
+                            unpack2(gelu_tanh_erf2(y), lo, hi);
+                            ow[h * 2 + e] = pack_bf16(lo, hi);
+                        }
+                    }
                     const int c = (cg & 1) * 4 + q;
-                    *reinterpret_cast<uint4*>(blk + ((c ^ (t & 7)) << 4)) = Vec<__nv_bfloat16>::pack(f);
+                    *reinterpret_cast<uint4*>(blk + ((c ^ (t & 7)) << 4)) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                 }
             }
             fence_proxy_async();
@@ -218,13 +229,24 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
             tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-                float r[8], f[8];
                 unsigned char* slot = hs_ptr + t * 128 + (((cg * 4 + q) ^ (t & 7)) << 4);
-                Vec<__nv_bfloat16>::unpack(*reinterpret_cast<const uint4*>(slot), r);
+                const uint4 rr = *reinterpret_cast<const uint4*>(slot);
+                const uint32_t rw[4] = {rr.x, rr.y, rr.z, rr.w};
+                uint32_t ow[4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    f[i] = r[i] + bf16_round(__uint_as_float(v[q * 8 + i]) + b2s[cg * 32 + q * 8 + i]);
-                *reinterpret_cast<uint4*>(slot) = Vec<__nv_bfloat16>::pack(f);
+                for (int h = 0; h < 2; ++h) {
+                    const ulonglong2 b2 = *reinterpret_cast<const ulonglong2*>(b2s + cg * 32 + q * 8 + h * 4);
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int i = q * 8 + h * 4 + e * 2;
+                        uint32_t pk;
+                        const uint64_t y = round2(add2(pack2u(v[i], v[i + 1]), e ? b2.y : b2.x), pk);
+                        float lo, hi;
+                        unpack2(add2(unpack_bf16x2(rw[h * 2 + e]), y), lo, hi);
+                        ow[h * 2 + e] = pack_bf16(lo, hi);
+                    }
+                }
+                *reinterpret_cast<uint4*>(slot) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
             }
         }
         named_barrier(1 + g, 128);

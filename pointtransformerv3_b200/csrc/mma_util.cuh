@@ -95,6 +95,30 @@ __device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b)
     return d;
 }
 
+// a pair from two 32-bit words (low word = first of the pair)
+__device__ __forceinline__ uint64_t pack2u(uint32_t lo, uint32_t hi)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+// a bf16x2 word as a pair of floats
+__device__ __forceinline__ uint64_t unpack_bf16x2(uint32_t w) { return pack2u(w << 16, w & 0xffff0000u); }
+// both floats rounded to bf16 (round to nearest even); `packed` receives the bf16x2 word
+__device__ __forceinline__ uint64_t round2(uint64_t v, uint32_t& packed)
+{
+    float lo, hi;
+    unpack2(v, lo, hi);
+    packed = pack_bf16(lo, hi);
+    return unpack_bf16x2(packed);
+}
+__device__ __forceinline__ float hsum2(uint64_t v)
+{
+    float lo, hi;
+    unpack2(v, lo, hi);
+    return lo + hi;
+}
+
 // Constants of the exponentials, packed once per thread.
 struct Exp2Const {
     uint64_t log2e, magic, neg_magic, neg_one, c3, c2, c1, one;

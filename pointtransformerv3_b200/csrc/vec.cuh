@@ -1,5 +1,6 @@
 // 16-byte vector access to rows of fp32 / bf16 features.
 #pragma once
+#include "mma_util.cuh"
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
@@ -53,6 +54,21 @@ __device__ __forceinline__ float gelu_tanh_erf(float x)
     asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(p));
     const float hx = 0.5f * x;
     return fmaf(hx, th, hx);
+}
+// the same for a pair of values (packed fp32 arithmetic; the same operations in the same order)
+__device__ __forceinline__ uint64_t gelu_tanh_erf2(uint64_t x)
+{
+    const float c1 = 1.12812329f * 0.70710678f, c3 = 0.10414445f * 0.35355339f, c5 = -0.00181548f * 0.17677670f;
+    float a, b;
+    unpack2(fma2(x, x, 0ull), a, b);
+    const uint64_t x2 = pack2(fminf(a, 32.f), fminf(b, 32.f));
+    const uint64_t p = fma2(fma2(fma2(pack2(c5, c5), x2, pack2(c3, c3)), x2, pack2(c1, c1)), x, 0ull);
+    unpack2(p, a, b);
+    float ta, tb;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(ta) : "f"(a));
+    asm("tanh.approx.f32 %0, %1;" : "=f"(tb) : "f"(b));
+    const uint64_t hx = fma2(x, pack2(0.5f, 0.5f), 0ull);
+    return fma2(hx, pack2(ta, tb), hx);
 }
 
 }  // namespace ptv3
