@@ -749,10 +749,12 @@ class PointTransformerV3(PointModule):
         memory should do so, because that read is a small device-to-host copy which waits
         behind any large copy the same engine is busy with (the previous batch's output).  With
         ``self.defer_status_check = True`` the device status word is not read at
-        the end either; the caller checks ``point.check_status(force=True)`` when
-        it next needs the host to wait.  (On the benchmark batch neither changes
-        the throughput of back-to-back passes: measured 9.8 ms per step against
-        9.5-9.7 with the two host waits in place.)"""
+        the end either; the caller checks ``point.check_status(force=True)`` (or reads
+        ``point["_status"]`` together with the output) when it next needs the host to
+        wait.  Passes queued back to back then overlap: serialization and the pooling
+        plans of one pass run on the planning stream while the main stream still holds
+        the features of the pass before it (benchmark batch: 8.55 ms per pass with the
+        status read at the end of every pass, 8.2 ms with it deferred)."""
         point = Point(data_dict)
         depth = point.pop("serialization_depth", None)
         host_offset = point.pop("offset_host", None)
@@ -761,37 +763,43 @@ class PointTransformerV3(PointModule):
             point["_counts"] = [off[i + 1] - off[i] for i in range(len(off) - 1)]
         status = point.device_status()
         point["_defer_status"] = True
-        # -- planning phase: everything whose size depends on the data, so that all
-        #    host reads happen here and the feature phase is queued without waiting
-        point._ensure_grid_coord()
-        if "sparse_shape" in point.keys() and "_shape_pad" not in point.keys():
-            # a caller's shape is the largest grid coordinate + 96 (sparsify's default pad,
-            # model.py:162-164); the shapes of the coarse levels then follow without reading the device
-            point["_shape_pad"] = 96
-        if "sparse_shape" not in point.keys() or depth is None or "_counts" not in point.keys():
-            stats = torch.cat([point.grid_coord.max(0).values.to(torch.int64), point.offset.to(torch.int64)])
-            stats = stats.tolist()                                     # one host read
-            if depth is None:
-                depth = max(stats[:3]).bit_length()
-            if "sparse_shape" not in point.keys():
-                point["sparse_shape"] = [v + 96 for v in stats[:3]]
-                point["_shape_pad"] = 96
-            off = [0] + stats[3:]
-            point["_counts"] = [off[i + 1] - off[i] for i in range(len(off) - 1)]
-        point.serialization(order=self.order, depth=depth, shuffle_orders=self.shuffle_orders)
-        # -- Schedule.  The pooling plan of a coarser level needs only the codes of the level
-        #    above it; it has one host read (its size) and a few dozen small launches, which
-        #    run on a second, high-priority stream.  Plans are made two stages ahead of the
-        #    features (level 1 while the stem runs, level 2 while the first encoder stage runs,
-        #    level s + 2 while stage s runs), so that their host reads never wait behind, and
-        #    never hold up, the feature kernels.
-        main = torch.cuda.current_stream()
         feat_dtype = point.feat.dtype
-        point["_sparse_indices"] = point._sparse_indices()
-        serialized = torch.cuda.Event()
-        serialized.record(main)
+        # -- Schedule.  Serialization and the pooling plans need only coordinates.  They run on a
+        #    second, high-priority stream: a plan has one host read (its size) and a few dozen small
+        #    launches, and is made two stages ahead of the features (level 1 while the stem runs,
+        #    level s + 2 while stage s runs), so that the host reads never wait behind, and never hold
+        #    up, the feature kernels.  Nothing on that stream depends on the main stream beyond the
+        #    inputs, so with deferred status checks the planning of one pass runs while the main stream
+        #    still holds the features of the pass before it.
+        main = torch.cuda.current_stream()
         side = self._side_stream(main.device)
-        side.wait_event(serialized)
+        inputs_ready = torch.cuda.Event()
+        inputs_ready.record(main)
+        side.wait_event(inputs_ready)
+        with torch.cuda.stream(side):
+            # -- planning phase: everything whose size depends on the data, so that all
+            #    host reads happen here and the feature phase is queued without waiting
+            point._ensure_grid_coord()
+            if "sparse_shape" in point.keys() and "_shape_pad" not in point.keys():
+                # a caller's shape is the largest grid coordinate + 96 (sparsify's default pad,
+                # model.py:162-164); the shapes of the coarse levels then follow without reading the device
+                point["_shape_pad"] = 96
+            if "sparse_shape" not in point.keys() or depth is None or "_counts" not in point.keys():
+                stats = torch.cat([point.grid_coord.max(0).values.to(torch.int64), point.offset.to(torch.int64)])
+                stats = stats.tolist()                                     # one host read
+                if depth is None:
+                    depth = max(stats[:3]).bit_length()
+                if "sparse_shape" not in point.keys():
+                    point["sparse_shape"] = [v + 96 for v in stats[:3]]
+                    point["_shape_pad"] = 96
+                off = [0] + stats[3:]
+                point["_counts"] = [off[i + 1] - off[i] for i in range(len(off) - 1)]
+            point.serialization(order=self.order, depth=depth, shuffle_orders=self.shuffle_orders)
+            point["_sparse_indices"] = point._sparse_indices()
+        # what was made there is consumed (and later dropped) by work queued on the main stream
+        _record_stream(point, main)
+        serialized = torch.cuda.Event()
+        serialized.record(side)
         # the finest level's 3x3x3 kernel map is first needed after the stem: build it on the
         # second stream while the stem (which probes its own voxel index) runs on the first
         with torch.cuda.stream(side):
@@ -840,6 +848,7 @@ class PointTransformerV3(PointModule):
                 events[i].record(side)
                 plan_state["cursor"] = child
 
+        main.wait_event(serialized)
         point.sparsify()
         point = self.embedding(point)
         for i, stage in enumerate(stages):
