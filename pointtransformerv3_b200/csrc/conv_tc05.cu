@@ -14,11 +14,17 @@
 // through a ring of stages guarded by mbarriers.  When the last product has completed, warps 0..3
 // read the accumulator (thread = voxel), add the bias, round to bf16 and store their rows.
 //
-// The sum over offsets and input channels is taken in one fixed order inside one accumulator, so
-// the result is the same bit for bit on every run, on every level: no atomics, no pair lists, no
-// second pass.  Products with zero rows are not skipped (on coarse levels about two thirds of the
-// rows of an active offset are empty); with the tensor pipe that is cheaper than avoiding them:
-// the kernel's time goes to moving the neighbour rows and the weights from L2 to shared memory.
+// Two threads issue the products, taking the stages in turn, each into its own accumulator (one
+// thread can start a stage only every ~450 cycles: looking at a stage's barrier costs it as much as
+// issuing the stage's four products); the epilogue adds the two partial sums.  Every sum is taken
+// in one fixed order, so the result is the same bit for bit on every run, on every level: no
+// atomics, no pair lists, no second pass.  Products with zero rows are not skipped (on coarse
+// levels about two thirds of the rows of an active offset are empty): the tensor pipe has time to
+// spare.  What bounds the kernel is shared-memory bandwidth: a stage writes 32 KiB (128 gathered
+// rows and 128 weight rows of 128 bytes) and its four products read 32 KiB (a 128 x 128 x 16
+// product reads 8 KiB of operands, 128 bytes per cycle at the tensor pipe's full rate), 512 cycles
+// per stage at 128 bytes per cycle; measured: ~680.  Leaving out the gather copies or the weight
+// loads altogether changes the time by 10 % and 2 %.
 //
 // Replaces spconv.SubMConv3d.forward at model.py:546-552 for bf16.
 // Useful work: 2 . pairs . C_in . C_out FLOP.  Every mbarrier wait is bounded and reports through
@@ -35,7 +41,7 @@ using namespace tc05;
 constexpr int CT_TM = 128;         // voxels per tile
 constexpr int CT_MAX_KVOL = 27;
 constexpr int CT_GATHER_WARPS = 8;
-constexpr int CT_THREADS = (CT_GATHER_WARPS + 1) * 32;
+
 
 struct ConvTcArgs {
     const __nv_bfloat16* feat;
@@ -48,24 +54,28 @@ struct ConvTcArgs {
     uint32_t* status;
 };
 
-template <int BN, int KC, int STAGES, int LAGW>
-__global__ void __launch_bounds__(CT_THREADS) conv_tc05_kernel(const __grid_constant__ CUtensorMap map_w,
+template <int BN, int KC, int STAGES, int NI>
+__global__ void __launch_bounds__((CT_GATHER_WARPS + NI) * 32) conv_tc05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                const ConvTcArgs a)
 {
     constexpr int ROWB = KC * 2;                    // bytes per staged row: one swizzle span (128 or 64)
     constexpr int NCH = ROWB / 16;                  // 16-byte chunks per row
     constexpr int A_BYTES = CT_TM * ROWB, B_BYTES = BN * ROWB, STAGE_BYTES = A_BYTES + B_BYTES;
-    constexpr int TM_COLS = BN < 32 ? 32 : BN;
+    constexpr int CT_THREADS = (CT_GATHER_WARPS + NI) * 32;
+    // NI issuing threads, each with its own accumulator in tensor memory (columns rounded up to a power
+    // of two for the allocation).  A slot of the ring must always be consumed by the same issuer
+    // (STAGES a multiple of NI): an issuer that met a slot whose previous use another, slower issuer had
+    // not consumed yet would take the parity of that older phase for its own.
+    constexpr int TM_USED = NI * BN;
+    constexpr int TM_COLS = TM_USED <= 32 ? 32 : TM_USED <= 64 ? 64 : TM_USED <= 128 ? 128 : TM_USED <= 256 ? 256 : 512;
+    static_assert(TM_USED <= 512 && STAGES % NI == 0, "issuers and accumulators");
     static_assert(STAGE_BYTES % 1024 == 0 && A_BYTES % 1024 == 0, "operand tiles start on a swizzle atom");
-    // a warp that keeps one stage in flight while it fills the next hands over stage X only after it
-    // has found a free slot for its next stage; that slot must not depend on stage X itself
     // Warps that gather: at most one per stage of the ring.  A parity wait on an mbarrier can only tell
     // the current phase from the one before it, so a warp must never be two uses ahead of a slot: its
     // stages are NGW apart, and having been given a slot for stage X (stage X - STAGES consumed) it may
     // ask for the slot of stage X + NGW only if stage X + NGW - 2 STAGES is known to be consumed,
     // i.e. NGW <= STAGES (the products run in order).
     constexpr int NGW = STAGES < CT_GATHER_WARPS ? STAGES : CT_GATHER_WARPS;
-    static_assert(LAGW == 0 || (LAGW == 1 && STAGES > NGW), "stages per gathering warp");
 
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -93,7 +103,7 @@ __global__ void __launch_bounds__(CT_THREADS) conv_tc05_kernel(const __grid_cons
             mbar_init(full0 + 8 * s, 2);        // the gathering warp of the stage + its weight load
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accfull, 1);
+        mbar_init(accfull, NI);
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_w);
@@ -150,7 +160,6 @@ __global__ void __launch_bounds__(CT_THREADS) conv_tc05_kernel(const __grid_cons
         // issue, the proxy fence) and the latency of its copies overlap with the other warps' stages.
         constexpr int RPP = 32 / NCH;                     // rows per pass of the warp
         const int c = lane % NCH, rr = lane / NCH;        // this lane's chunk and first row
-        int prev = -1;
         for (int it = warp < NGW ? warp : nit; it < nit; it += NGW) {
             const int s = it % STAGES;
             if (lane == 0) {
@@ -180,27 +189,10 @@ __global__ void __launch_bounds__(CT_THREADS) conv_tc05_kernel(const __grid_cons
                 }
             }
             cp_async_commit();
-            if (LAGW == 0) {
-                cp_async_wait<0>();
-                fence_proxy_async();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_one(full0 + 8 * s);
-            } else {
-                if (prev >= 0) {
-                    // the stage before this one has landed: hand it to the tensor pipe
-                    cp_async_wait<1>();
-                    fence_proxy_async();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive_one(full0 + 8 * prev);
-                }
-                prev = s;
-            }
-        }
-        if (LAGW != 0) {
             cp_async_wait<0>();
             fence_proxy_async();
             __syncwarp();
-            if (lane == 0 && prev >= 0) mbar_arrive_one(full0 + 8 * prev);
+            if (lane == 0) mbar_arrive_one(full0 + 8 * s);
         }
 
         // ---- epilogue: thread = voxel ----------------------------------------------------------
@@ -220,6 +212,16 @@ __global__ void __launch_bounds__(CT_THREADS) conv_tc05_kernel(const __grid_cons
             if (read_acc) {
                 tmem_ld32(tm + cb * 32, acc);
                 tmem_ld_wait();
+                // the other issuers' partial sums, added in a fixed order
+#pragma unroll 1
+                for (int i = 1; i < NI && i < nit; ++i) {
+                    uint32_t more[32];
+                    tmem_ld32(tm + i * BN + cb * 32, more);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        acc[e] = __float_as_uint(__uint_as_float(acc[e]) + __uint_as_float(more[e]));
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[i] = 0;
@@ -237,21 +239,27 @@ __global__ void __launch_bounds__(CT_THREADS) conv_tc05_kernel(const __grid_cons
             }
         }
     } else {
-        // ---- issuer ------------------------------------------------------------------------------
+        // ---- issuers: thread i takes stages i, i + NI, ... in order and accumulates them in
+        // its own accumulator.  One thread can start a stage's products only every ~450 cycles (a look
+        // at the stage's barrier costs it as much as the four products), which is what bounded the
+        // kernel with a single issuer; the partial sums are added in the epilogue.
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(CT_TM, BN);
-            for (int it = 0; it < nit; ++it) {
+            const int me = warp - CT_GATHER_WARPS;
+            const uint32_t tm_acc = tmem_base + me * BN;
+            for (int it = me; it < nit; it += NI) {
                 const int s = it % STAGES;
                 ok &= mbar_wait(full0 + 8 * s, (it / STAGES) & 1, abort);
                 fence_after_sync();
                 const uint32_t sa = sbase + s * STAGE_BYTES, sb = sa + A_BYTES;
 #pragma unroll
                 for (int k4 = 0; k4 < KC / 16; ++k4)
-                    umma_bf16(tmem_base, umma_desc_kmajor(sa + k4 * 32, ROWB), umma_desc_kmajor(sb + k4 * 32, ROWB),
-                              idesc, it > 0 || k4 > 0);
+                    umma_bf16(tm_acc, umma_desc_kmajor(sa + k4 * 32, ROWB), umma_desc_kmajor(sb + k4 * 32, ROWB),
+                              idesc, it >= NI || k4 > 0);
                 umma_commit(empty0 + 8 * s);
             }
-            if (nit > 0) umma_commit(accfull);
+            if (nit > me) umma_commit(accfull);
+            else if (nit > 0) mbar_arrive_one(accfull);
         }
     }
     fence_before_sync();
@@ -270,7 +278,7 @@ bool conv_tc05_supported(int c_in, int c_out, int kernel_volume)
     return c_in % 64 == 0 && c_in <= 4096 && c_out % 64 == 0 && c_out <= 4096;
 }
 
-template <int BN, int KC, int STAGES, int LAGW>
+template <int BN, int KC, int STAGES, int NI>
 static int launch_conv_tc05_as(const void* weight, const ConvTcArgs& a, cudaStream_t stream)
 {
     CUtensorMap mw;
@@ -279,11 +287,11 @@ static int launch_conv_tc05_as(const void* weight, const ConvTcArgs& a, cudaStre
     if (rc) return rc;
     constexpr size_t smem = (size_t)STAGES * (CT_TM + BN) * KC * 2 + CT_MAX_KVOL * CT_TM * 4 + CT_TM * 8 + 32 * 4 +
                             BN * 4 + 8 * (2 * STAGES + 1) + 16 + 1024;
-    auto kern = conv_tc05_kernel<BN, KC, STAGES, LAGW>;
+    auto kern = conv_tc05_kernel<BN, KC, STAGES, NI>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_subm_conv_fwd: shared memory attribute");
     const dim3 grid((unsigned)((a.n + CT_TM - 1) / CT_TM), a.cout / BN);
-    kern<<<grid, CT_THREADS, smem, stream>>>(mw, a);
+    kern<<<grid, (CT_GATHER_WARPS + NI) * 32, smem, stream>>>(mw, a);
     count_launches(1);
     return check_launch("ptv3_subm_conv_fwd");
 }
@@ -303,13 +311,13 @@ int launch_conv_tc05(const void* feat, const int32_t* nbr, const void* weight, c
     a.cout = c_out;
     a.kvol = kvol;
     a.status = status;
-    if (c_in == 32) return launch_conv_tc05_as<32, 32, 6, 0>(weight, a, stream);
+    if (c_in == 32) return launch_conv_tc05_as<32, 32, 6, 2>(weight, a, stream);
     // 128 output channels per CTA halve the gathers of a tile; 64 when that would leave SMs idle
     const int64_t tiles = (n + CT_TM - 1) / CT_TM;
-    if (c_out % 128 == 0 && tiles * (c_out / 128) >= 120) return launch_conv_tc05_as<128, 64, 6, 0>(weight, a, stream);
+    if (c_out % 128 == 0 && tiles * (c_out / 128) >= 120) return launch_conv_tc05_as<128, 64, 6, 2>(weight, a, stream);
     // many tiles: two CTAs per SM, so that one tile's prologue and epilogue run beside another's products
-    if (tiles * (c_out / 64) >= 2 * 148) return launch_conv_tc05_as<64, 64, 4, 0>(weight, a, stream);
-    return launch_conv_tc05_as<64, 64, 8, 0>(weight, a, stream);
+    if (tiles * (c_out / 64) >= 2 * 148) return launch_conv_tc05_as<64, 64, 4, 2>(weight, a, stream);
+    return launch_conv_tc05_as<64, 64, 8, 2>(weight, a, stream);
 }
 
 }  // namespace ptv3

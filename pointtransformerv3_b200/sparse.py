@@ -12,10 +12,12 @@ from . import ops
 
 # The pair-list convolution multiplies only the (input, output) pairs that exist, 128 pairs of one
 # offset at a time, so a slice of the weights serves 128 useful rows; an output-stationary tile of a
-# coarse level uses it for the ~40 voxels of its 128 that have that neighbour.  That pays when the
-# weights are the bulk of the traffic: few voxels and very wide channels.
+# coarse level uses it for the ~40 voxels of its 128 that have that neighbour.  That pays only when the
+# weights are nearly all of the traffic.  Measured on the coarsest level of the default backbone
+# (2 238 voxels, 512 channels): 0.083 ms on the pair list, 0.062 ms on the kernel map; so the
+# default backbone never takes this path, and it starts at twice that width.
 PAIR_PATH_MAX_VOXELS = 65536
-PAIR_PATH_MIN_CHANNELS = 512
+PAIR_PATH_MIN_CHANNELS = 1024
 
 
 def uses_pair_path(n, in_channels, out_channels, dtype, kernel_size=3):
