@@ -49,6 +49,8 @@ __global__ void __launch_bounds__(AM_THREADS, 3) attn_mma_d16_kernel(
     const int32_t* __restrict__ cu_seqlens, __nv_bfloat16* __restrict__ out, int C, float scale,
     int lpad_max, uint32_t* __restrict__ status)
 {
+    pdl_launch_next();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* Ks = smem;
     unsigned char* Vs = smem + (size_t)lpad_max * 32;
@@ -267,8 +269,8 @@ int launch_attn_mma(const void* qkv, const int64_t* order, const int64_t* pad, c
     // three CTAs fit on an SM; aim at several waves so that the last one costs little
     while (pairs * qsplit < 4 * 3 * 148 && qsplit * 2 * AM_WARPS <= tiles) qsplit *= 2;
     const dim3 grid(H * qsplit, n_seq);
-    kern<<<grid, AM_THREADS, smem, stream>>>(
-        (const __nv_bfloat16*)qkv, order, pad, unpad, cu, (__nv_bfloat16*)out, C, scale, lpad, status);
+    launch_dependent(kern, grid, dim3(AM_THREADS), smem, stream, (const __nv_bfloat16*)qkv, order, pad, unpad, cu,
+                     (__nv_bfloat16*)out, C, scale, lpad, status);
     count_launches(1);
     return check_launch("ptv3_attention_fwd");
 }

@@ -44,4 +44,33 @@ struct Carver {
 
 static inline int ceil_div(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
+// ---- programmatic dependent launch -------------------------------------------------------------
+// A forward is a chain of a few hundred kernels on one stream, many of them a few microseconds
+// long.  A kernel launched with launch_dependent() may be scheduled while the kernel before it in
+// the stream still runs; it must call pdl_wait() before it touches anything that kernel wrote (all
+// such kernels here call it first thing), and pdl_launch_next() tells the scheduler that the
+// kernel after it may be brought up.  The launch latency and the start-up of a kernel then overlap
+// the tail of its predecessor.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_next() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_dependent(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                           cudaStream_t stream, Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 }  // namespace ptv3

@@ -58,6 +58,8 @@ template <int BN, int KC, int STAGES, int NI>
 __global__ void __launch_bounds__((CT_GATHER_WARPS + NI) * 32) conv_tc05_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                const ConvTcArgs a)
 {
+    pdl_launch_next();
+    pdl_wait();
     constexpr int ROWB = KC * 2;                    // bytes per staged row: one swizzle span (128 or 64)
     constexpr int NCH = ROWB / 16;                  // 16-byte chunks per row
     constexpr int A_BYTES = CT_TM * ROWB, B_BYTES = BN * ROWB, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -291,7 +293,7 @@ static int launch_conv_tc05_as(const void* weight, const ConvTcArgs& a, cudaStre
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_subm_conv_fwd: shared memory attribute");
     const dim3 grid((unsigned)((a.n + CT_TM - 1) / CT_TM), a.cout / BN);
-    kern<<<grid, (CT_GATHER_WARPS + NI) * 32, smem, stream>>>(mw, a);
+    launch_dependent(kern, grid, dim3((CT_GATHER_WARPS + NI) * 32), smem, stream, mw, a);
     count_launches(1);
     return check_launch("ptv3_subm_conv_fwd");
 }

@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   const GemmArgs a)
 {
+    pdl_launch_next();
+    pdl_wait();
     constexpr int B_BYTES = BN * GM_BK * 2;
     constexpr int STAGE_BYTES = GM_A_BYTES + B_BYTES;
     constexpr int NBAR = 2 * STAGES + 4;      // full, empty per stage; accumulator full / empty x 2
@@ -206,7 +208,7 @@ static int launch_gemm_as(const CUtensorMap& mx, const CUtensorMap& mw, GemmArgs
         return check_launch("ptv3_gemm_fwd: shared memory attribute");
     a.col_tiles = a.n_out / BN;
     const int64_t tiles = (int64_t)a.row_tiles * a.col_tiles;
-    kern<<<(unsigned)(tiles < 148 ? tiles : 148), GM_THREADS, smem, stream>>>(mx, mw, a);
+    launch_dependent(kern, dim3((unsigned)(tiles < 148 ? tiles : 148)), dim3(GM_THREADS), smem, stream, mx, mw, a);
     count_launches(1);
     return check_launch("ptv3_gemm_fwd");
 }

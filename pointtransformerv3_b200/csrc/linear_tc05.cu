@@ -83,6 +83,8 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                                                              const __grid_constant__ CUtensorMap map_w,
                                                              const LinearArgs a)
 {
+    pdl_launch_next();
+    pdl_wait();
     constexpr int SW = K >= 64 ? 128 : 64;       // bytes per shared-memory row (swizzle span)
     constexpr int KB = K >= 64 ? K / 64 : 1;     // 64-wide K blocks
     constexpr int KCOLS = K >= 64 ? 64 : K;      // columns per K block
@@ -498,7 +500,7 @@ static int launch_linear(const void* x, const void* w, LinearArgs a, int k, cuda
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req) !=        \
             cudaSuccess)                                                                                     \
             return check_launch("ptv3_linear_fwd: shared memory attribute");                                 \
-        kern<<<(unsigned)grid, 512, smem_req, stream>>>(mx, mw, a);                                          \
+        launch_dependent(kern, dim3((unsigned)grid), dim3(512), smem_req, stream, mx, mw, a);                \
     } while (0)
     if (k == 32) LIN_LAUNCH(32);
     else if (k == 64) LIN_LAUNCH(64);

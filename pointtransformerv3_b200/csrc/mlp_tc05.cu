@@ -61,6 +61,8 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
     const __nv_bfloat16* __restrict__ b2, const __nv_bfloat16* __restrict__ residual,
     __nv_bfloat16* __restrict__ out, int64_t n, uint32_t* __restrict__ status)
 {
+    pdl_launch_next();
+    pdl_wait();
     using Cfg = MlpCfg<C>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -284,9 +286,9 @@ static int launch_mlp(const void* x, const void* w1, const void* b1, const void*
     const int64_t ntiles = (n + 127) / 128;
     int64_t grid = (ntiles + Cfg::NG - 1) / Cfg::NG;
     if (grid > 148) grid = 148;
-    kern<<<(unsigned)grid, 128 * Cfg::NG, Cfg::SMEM, stream>>>(mx, mw1, mw2, (const __nv_bfloat16*)b1,
-                                                     (const __nv_bfloat16*)b2, (const __nv_bfloat16*)residual,
-                                                     (__nv_bfloat16*)out, n, status);
+    launch_dependent(kern, dim3((unsigned)grid), dim3(128 * Cfg::NG), Cfg::SMEM, stream, mx, mw1, mw2,
+                     (const __nv_bfloat16*)b1, (const __nv_bfloat16*)b2, (const __nv_bfloat16*)residual,
+                     (__nv_bfloat16*)out, n, status);
     count_launches(1);
     return check_launch("ptv3_mlp_fwd");
 }

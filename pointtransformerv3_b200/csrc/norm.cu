@@ -32,6 +32,8 @@ __global__ void __launch_bounds__(256) add_ln_kernel(
     const T* __restrict__ b1, float eps1, T* __restrict__ sum_out, const T* __restrict__ g2,
     const T* __restrict__ b2, float eps2, T* __restrict__ norm_out, int64_t n, int C)
 {
+    pdl_launch_next();
+    pdl_wait();
     using V = Vec<T>;
     constexpr int E = VPL * V::N;
     const int lane_in_row = threadIdx.x % LANES;
@@ -102,9 +104,9 @@ static void launch_add_ln(const void* x, const void* residual, const void* g1, c
                           int64_t n, int C, cudaStream_t stream)
 {
     const int64_t threads = n * LANES;
-    add_ln_kernel<T, LANES, VPL><<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(
-        (const T*)x, (const T*)residual, (const T*)g1, (const T*)b1, eps1, (T*)sum_out, (const T*)g2,
-        (const T*)b2, eps2, (T*)norm_out, n, C);
+    launch_dependent(add_ln_kernel<T, LANES, VPL>, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, stream,
+                     (const T*)x, (const T*)residual, (const T*)g1, (const T*)b1, eps1, (T*)sum_out, (const T*)g2,
+                     (const T*)b2, eps2, (T*)norm_out, n, C);
 }
 
 template <typename T>
