@@ -20,10 +20,12 @@
 // in one fixed order, so the result is the same bit for bit on every run, on every level: no
 // atomics, no pair lists, no second pass.  Products with zero rows are not skipped (on coarse
 // levels about two thirds of the rows of an active offset are empty): the tensor pipe has time to
-// spare.  What bounds the kernel is shared-memory bandwidth: a stage writes 32 KiB (128 gathered
-// rows and 128 weight rows of 128 bytes) and its four products read 32 KiB (a 128 x 128 x 16
-// product reads 8 KiB of operands, 128 bytes per cycle at the tensor pipe's full rate), 512 cycles
-// per stage at 128 bytes per cycle; measured: ~680.  Leaving out the gather copies or the weight
+// spare.  What bounds the kernel is the length of a slot's cycle, not a throughput: once a slot is
+// free its warp issues the weight load and 32 copies per lane (~1100 cycles), the rows land (~1200),
+// the warp fences and arrives, an issuer notices, issues, the products complete and the commit
+// frees the slot (~1500 more): ~4000 cycles for six slots, one stage per ~700 cycles.  Counters of
+// one launch: tensor pipe 22 % active, shared-memory pipe 29 % (16 % operand reads of the tensor
+// core, 13 % copies and loads), L2 19 %, DRAM 5 %; leaving out the gather copies or the weight
 // loads altogether changes the time by 10 % and 2 %.
 //
 // Replaces spconv.SubMConv3d.forward at model.py:546-552 for bf16.
@@ -171,10 +173,6 @@ __global__ void __launch_bounds__((CT_GATHER_WARPS + NI) * 32) conv_tc05_kernel(
             const int o = act[1 + it / kchunks];
             const int kc = (it % kchunks) * KC;
             const uint32_t sa = sbase + s * STAGE_BYTES;
-            if (lane == 0) {
-                mbar_expect_tx(full0 + 8 * s, B_BYTES);
-                tma_load_2d(sa + A_BYTES, &map_w, o * a.cin + kc, col0, full0 + 8 * s);
-            }
             const __nv_bfloat16* src0 = a.feat + kc + c * 8;
             const int32_t* nb = nbr_s + o * CT_TM + rr;
 #pragma unroll
@@ -191,6 +189,12 @@ __global__ void __launch_bounds__((CT_GATHER_WARPS + NI) * 32) conv_tc05_kernel(
                 }
             }
             cp_async_commit();
+            // (the weight load is issued after the copies: its issue costs lane 0 ~350 cycles, during
+            // which the rows are already on their way)
+            if (lane == 0) {
+                mbar_expect_tx(full0 + 8 * s, B_BYTES);
+                tma_load_2d(sa + A_BYTES, &map_w, o * a.cin + kc, col0, full0 + 8 * s);
+            }
             cp_async_wait<0>();
             fence_proxy_async();
             __syncwarp();
