@@ -121,32 +121,41 @@ __global__ void __launch_bounds__((CT_GATHER_WARPS + NI) * 32) conv_tc05_kernel(
     }
     for (int c = tid; c < BN; c += CT_THREADS) bias_s[c] = a.bias ? __bfloat162float(a.bias[col0 + c]) : 0.f;
     {
-        // all loads of a thread are issued before the first is stored
-        constexpr int PER = (CT_MAX_KVOL * CT_TM + CT_THREADS - 1) / CT_THREADS;
-        int32_t v[PER];
+        // A warp stages whole offsets (four coalesced rows of 32 entries each), all of its loads issued
+        // before the first store, and notes in the same pass whether the tile has the offset at all.
+        constexpr int NW = CT_THREADS / 32, OPW = (CT_MAX_KVOL + NW - 1) / NW;
+        int32_t v[OPW][4];
 #pragma unroll
-        for (int j = 0; j < PER; ++j) {
-            const int idx = tid + j * CT_THREADS, o = idx / CT_TM, r = idx % CT_TM;
-            v[j] = (o < kvol && row0 + r < a.n) ? __ldg(a.nbr + (int64_t)o * a.n + row0 + r) : -1;
+        for (int j = 0; j < OPW; ++j) {
+            const int o = warp + j * NW;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = lane + 32 * i;
+                v[j][i] = (o < kvol && row0 + r < a.n) ? __ldg(a.nbr + (int64_t)o * a.n + row0 + r) : -1;
+            }
         }
 #pragma unroll
-        for (int j = 0; j < PER; ++j)
-            if (tid + j * CT_THREADS < kvol * CT_TM) nbr_s[tid + j * CT_THREADS] = v[j];
-    }
-    __syncthreads();
-    for (int o = warp; o < kvol; o += CT_THREADS / 32) {
-        bool any = false;
+        for (int j = 0; j < OPW; ++j) {
+            const int o = warp + j * NW;
+            if (o < kvol) {
+                bool any = false;
 #pragma unroll
-        for (int r = lane; r < CT_TM; r += 32) any |= nbr_s[o * CT_TM + r] >= 0;
-        const unsigned b = __ballot_sync(0xffffffffu, any);
-        if (lane == 0) act[1 + o] = b != 0;
+                for (int i = 0; i < 4; ++i) {
+                    nbr_s[o * CT_TM + lane + 32 * i] = v[j][i];
+                    any |= v[j][i] >= 0;
+                }
+                const unsigned b = __ballot_sync(0xffffffffu, any);
+                if (lane == 0) act[1 + o] = b != 0;
+            }
+        }
     }
     __syncthreads();
-    if (tid == 0) {
-        int c = 0;
-        for (int o = 0; o < kvol; ++o)
-            if (act[1 + o]) act[1 + c++] = o;     // ascending: position c <= o, already consumed
-        act[0] = c;
+    if (warp == 0) {
+        // the offsets in use, in ascending order: act[1 ..], their number in act[0]
+        const int flag = lane < kvol ? act[1 + lane] : 0;
+        const unsigned m = __ballot_sync(0xffffffffu, flag != 0);
+        if (flag) act[1 + __popc(m & ((1u << lane) - 1))] = lane;
+        if (lane == 0) act[0] = __popc(m);
     }
     fence_before_sync();
     __syncthreads();
