@@ -104,25 +104,42 @@ __global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
             rows_s[tid] = i < n ? (row_order ? row_order[i] : i) : -1;
         }
         __syncthreads();
-        for (int idx = tid; idx < kvol * CM_TM; idx += CM_THREADS) {
-            const int o = idx / CM_TM, r = idx % CM_TM;
-            nbr_s[idx] = row0 + r < n ? nbr[(int64_t)o * n + row0 + r] : -1;
-        }
-        __syncthreads();
-        // offsets with at least one neighbour in the tile, in ascending order
-        for (int o = warp; o < kvol; o += CM_THREADS / 32) {
-            bool any = false;
+        {
+            // a warp stages whole offsets (coalesced rows of 32 entries), all of its loads issued
+            // before the first store, and notes in the same pass whether the tile has the offset
+            constexpr int NW = CM_THREADS / 32, OPW = (CM_MAX_KVOL + NW - 1) / NW, RPL = CM_TM / 32;
+            int32_t v[OPW][RPL];
 #pragma unroll
-            for (int r = lane; r < CM_TM; r += 32) any |= nbr_s[o * CM_TM + r] >= 0;
-            const unsigned b = __ballot_sync(0xffffffffu, any);
-            if (lane == 0) act[1 + o] = b != 0;
+            for (int j = 0; j < OPW; ++j) {
+                const int o = warp + j * NW;
+#pragma unroll
+                for (int i = 0; i < RPL; ++i) {
+                    const int r = lane + 32 * i;
+                    v[j][i] = (o < kvol && row0 + r < n) ? __ldg(nbr + (int64_t)o * n + row0 + r) : -1;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < OPW; ++j) {
+                const int o = warp + j * NW;
+                if (o < kvol) {
+                    bool any = false;
+#pragma unroll
+                    for (int i = 0; i < RPL; ++i) {
+                        nbr_s[o * CM_TM + lane + 32 * i] = v[j][i];
+                        any |= v[j][i] >= 0;
+                    }
+                    const unsigned b = __ballot_sync(0xffffffffu, any);
+                    if (lane == 0) act[1 + o] = b != 0;
+                }
+            }
         }
         __syncthreads();
-        if (tid == 0) {
-            int c = 0;
-            for (int o = 0; o < kvol; ++o)
-                if (act[1 + o]) act[1 + c++] = o;
-            act[0] = c;
+        if (warp == 0) {
+            // the offsets in use, in ascending order: act[1 ..], their number in act[0]
+            const int flag = lane < kvol ? act[1 + lane] : 0;
+            const unsigned m = __ballot_sync(0xffffffffu, flag != 0);
+            if (flag) act[1 + __popc(m & ((1u << lane) - 1))] = lane;
+            if (lane == 0) act[0] = __popc(m);
         }
         __syncthreads();
     }
