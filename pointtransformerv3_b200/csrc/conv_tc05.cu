@@ -61,7 +61,6 @@ __global__ void __launch_bounds__((CT_GATHER_WARPS + NI) * 32) conv_tc05_kernel(
                                                                const ConvTcArgs a)
 {
     pdl_launch_next();
-    pdl_wait();
     constexpr int ROWB = KC * 2;                    // bytes per staged row: one swizzle span (128 or 64)
     constexpr int NCH = ROWB / 16;                  // 16-byte chunks per row
     constexpr int A_BYTES = CT_TM * ROWB, B_BYTES = BN * ROWB, STAGE_BYTES = A_BYTES + B_BYTES;
@@ -113,6 +112,8 @@ __global__ void __launch_bounds__((CT_GATHER_WARPS + NI) * 32) conv_tc05_kernel(
         prefetch_tensormap(&map_w);
     }
     if (warp == CT_GATHER_WARPS) tmem_alloc(smem_u32_generic(tmem_slot), TM_COLS);
+    // (only the set-up above runs beside the kernel before this one in the stream)
+    pdl_wait();
 
     // ---- voxels of this tile, their neighbour rows, the offsets in use -------------------------
     if (tid < CT_TM) {

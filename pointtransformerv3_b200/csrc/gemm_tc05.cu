@@ -47,7 +47,6 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
                                                                   const GemmArgs a)
 {
     pdl_launch_next();
-    pdl_wait();
     constexpr int B_BYTES = BN * GM_BK * 2;
     constexpr int STAGE_BYTES = GM_A_BYTES + B_BYTES;
     constexpr int NBAR = 2 * STAGES + 4;      // full, empty per stage; accumulator full / empty x 2
@@ -82,6 +81,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    // barriers, tensor memory and descriptors are set up; everything the kernel before this one in
+    // the stream may have written is touched after this wait
+    pdl_wait();
 
     // tile t -> (row tile, column tile); column tiles of a row tile run on neighbouring CTAs, so
     // the x rows they share are fetched from DRAM once

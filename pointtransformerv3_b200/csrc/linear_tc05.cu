@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                                                              const LinearArgs a)
 {
     pdl_launch_next();
-    pdl_wait();
     constexpr int SW = K >= 64 ? 128 : 64;       // bytes per shared-memory row (swizzle span)
     constexpr int KB = K >= 64 ? K / 64 : 1;     // 64-wide K blocks
     constexpr int KCOLS = K >= 64 ? 64 : K;      // columns per K block
@@ -137,6 +136,9 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
             for (int r = 0; r < n_out; r += a.w_box_rows)
                 tma_load_2d(sbase + kb * w_block + r * SW, &map_w, kb * KCOLS, r, wbar);
     }
+    // up to here only weights, biases and LayerNorm parameters were read: everything the kernel before
+    // this one in the stream may have written is touched after this wait
+    pdl_wait();
     bool ok = mbar_wait(wbar, 0, abort);
 
     // columns of tensor memory per group: n_out rounded up to 32, groups side by side

@@ -62,7 +62,6 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
     __nv_bfloat16* __restrict__ out, int64_t n, uint32_t* __restrict__ status)
 {
     pdl_launch_next();
-    pdl_wait();
     using Cfg = MlpCfg<C>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -104,6 +103,9 @@ __global__ void __launch_bounds__(128 * MlpCfg<C>::NG, 1) mlp_tc05_kernel(
         for (int kb = 0; kb < Cfg::HD / 64; ++kb)
             tma_load_2d(sbase + Cfg::OFF_W2 + kb * Cfg::W2_BLOCK, &map_w2, kb * 64, 0, wbar);
     }
+    // up to here only weights and biases were read: everything the kernel before this one in the
+    // stream may have written is touched after this wait
+    pdl_wait();
     bool ok = mbar_wait(wbar, 0, abort);
 
     const uint32_t xs = sbase + Cfg::OFF_G + g * Cfg::G_BYTES;
