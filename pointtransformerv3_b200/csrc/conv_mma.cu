@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(WM * WN * 32) conv_mma_kernel(
     __nv_bfloat16* __restrict__ out, const int64_t* __restrict__ row_order, int64_t n, int cin,
     int cout, int kvol, PairList pl)
 {
+    pdl_launch_next();
+    pdl_wait();
     constexpr int CM_THREADS = WM * WN * 32;
     constexpr int NCH = KC / 8;              // 16-byte chunks per staged row
     constexpr int ROWB = KC * 2;             // bytes per staged row
@@ -275,9 +277,9 @@ static int launch_one(const void* feat, const int32_t* nbr, const void* weight, 
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_subm_conv_fwd: shared memory attribute");
     const dim3 grid((unsigned)((n + CM_TM - 1) / CM_TM), cout / CN);
-    kern<<<grid, WM * WN * 32, smem, stream>>>((const __nv_bfloat16*)feat, nbr, (const __nv_bfloat16*)weight,
-                                             (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, row_order, n,
-                                             cin, cout, kvol, PairList{});
+    launch_dependent(kern, grid, dim3(WM * WN * 32), smem, stream, (const __nv_bfloat16*)feat, nbr,
+                     (const __nv_bfloat16*)weight, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, row_order, n, cin,
+                     cout, kvol, PairList{});
     count_launches(1);
     return check_launch("ptv3_subm_conv_fwd");
 }
@@ -327,9 +329,10 @@ int launch_conv_pairs(const void* feat, const int32_t* pair_in, const int32_t* p
     if (cudaMemsetAsync(acc, 0, (size_t)n * c_out * sizeof(long long), stream) != cudaSuccess)
         return check_launch("ptv3_subm_conv_pairs_fwd: memset");
     const PairList pl{pair_in, pair_out, off_start, tile_start, acc};
-    kern<<<dim3((unsigned)max_tiles, c_out / 128), 256, smem, stream>>>(
-        (const __nv_bfloat16*)feat, nullptr, (const __nv_bfloat16*)weight, nullptr, nullptr, nullptr, n, c_in,
-        c_out, kvol, pl);
+    launch_dependent(kern, dim3((unsigned)max_tiles, c_out / 128), dim3(256), smem, stream,
+                     (const __nv_bfloat16*)feat, (const int32_t*)nullptr, (const __nv_bfloat16*)weight,
+                     (const __nv_bfloat16*)nullptr, (__nv_bfloat16*)nullptr, (const int64_t*)nullptr, n, c_in, c_out,
+                     kvol, pl);
     const int64_t total = n * (int64_t)c_out;
     conv_pairs_finalize_kernel<<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(
         acc, (const __nv_bfloat16*)bias, (__nv_bfloat16*)out, total, c_out);

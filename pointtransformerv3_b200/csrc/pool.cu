@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(256, 4) pool_max_kernel(const T* __restrict__ 
                                                        const float* __restrict__ shift, T* __restrict__ out,
                                                        float* __restrict__ coord_out)
 {
+    pdl_launch_next();
+    pdl_wait();
     using V = Vec<T>;
     const int sub = threadIdx.x % LANES;
     const int64_t c = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) / LANES;
@@ -103,6 +105,8 @@ __global__ void __launch_bounds__(256) unpool_kernel(const T* __restrict__ skip,
                                                      const float* __restrict__ c_shift,
                                                      T* __restrict__ out, T* __restrict__ skip_act)
 {
+    pdl_launch_next();
+    pdl_wait();
     using V = Vec<T>;
     const int vec_per_row = C / V::N;
     const int vpr_shift = (vec_per_row & (vec_per_row - 1)) == 0 ? __ffs(vec_per_row) - 1 : -1;
@@ -174,9 +178,9 @@ extern "C" int ptv3_pool_fwd(const void* x, const float* coord, const int64_t* i
 #define PTV3_POOL_LAUNCH(T, L)                                                                          \
     do {                                                                                                 \
         auto args = [&](auto kern) {                                                                     \
-            kern<<<blocks, 256, 0, stream>>>((const T*)x, with_coord ? coord : nullptr, indices, idx_ptr, m, \
-                                             channels, bn_scale, bn_shift, (T*)out,                      \
-                                             with_coord ? coord_out : nullptr);                          \
+            launch_dependent(kern, dim3(blocks), dim3(256), 0, stream, (const T*)x,                      \
+                             with_coord ? coord : (const float*)nullptr, indices, idx_ptr, m, channels,  \
+                             bn_scale, bn_shift, (T*)out, with_coord ? coord_out : (float*)nullptr);     \
         };                                                                                               \
         switch (reduce) {                                                                                \
             case 0: args(pool_max_kernel<T, L, 0>); break;                                               \
@@ -222,13 +226,14 @@ extern "C" int ptv3_unpool_fwd(const void* skip, const void* child, const int64_
     int64_t blocks = (n * (channels / vn) + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == PTV3_DTYPE_F32)
-        unpool_kernel<float><<<(unsigned)blocks, 256, 0, stream>>>(
-            (const float*)skip, (const float*)child, cluster, n, channels, skip_scale, skip_shift,
-            child_scale, child_shift, (float*)out, (float*)skip_act);
+        launch_dependent(unpool_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, (const float*)skip,
+                         (const float*)child, cluster, n, channels, skip_scale, skip_shift, child_scale,
+                         child_shift, (float*)out, (float*)skip_act);
     else
-        unpool_kernel<__nv_bfloat16><<<(unsigned)blocks, 256, 0, stream>>>(
-            (const __nv_bfloat16*)skip, (const __nv_bfloat16*)child, cluster, n, channels, skip_scale,
-            skip_shift, child_scale, child_shift, (__nv_bfloat16*)out, (__nv_bfloat16*)skip_act);
+        launch_dependent(unpool_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream,
+                         (const __nv_bfloat16*)skip, (const __nv_bfloat16*)child, cluster, n, channels,
+                         skip_scale, skip_shift, child_scale, child_shift, (__nv_bfloat16*)out,
+                         (__nv_bfloat16*)skip_act);
     count_launches(1);
     return check_launch("ptv3_unpool_fwd");
 }
