@@ -12,6 +12,15 @@
  *     workspaces are passed in; *_workspace_bytes() gives the size to pass
  *   - `stream` is a cudaStream_t passed as void*; no call synchronises
  *   - index tensors exposed to callers are int64 (as the reference's are)
+ *   - the kernels of the feature path (convolution, Linear / GEMM, LayerNorm,
+ *     attention, MLP, pooling) are launched with the programmatic-serialization
+ *     attribute: a kernel of this library may be brought up while the kernel
+ *     before it in the stream is finishing, and waits (griddepcontrol.wait) before
+ *     it reads or writes anything but its weights and parameters.  Stream order is
+ *     unchanged for the caller: work queued before or after a call, this
+ *     library's or not, sees the same results as with plain launches.  Weights,
+ *     biases and normalisation parameters must not be written by the operation
+ *     queued directly before a call that reads them
  *
  * "Replaces" lines cite the reference implementation by its path inside the
  * reference project.
