@@ -471,7 +471,10 @@ def test_linear_tcgen05(k, n_out, n):
 @pytest.mark.parametrize("n,k,n_out,gelu,res", [(3000, 256, 768, False, False), (2111, 256, 256, False, True),
                                                  (7000, 128, 512, True, False), (7000, 512, 128, False, True),
                                                  (500, 512, 1536, False, False), (129, 2048, 512, False, True),
-                                                 (1, 64, 128, True, True), (2049, 1024, 256, False, False)])
+                                                 (1, 64, 128, True, True), (2049, 1024, 256, False, False),
+                                                 # long inputs: several tiles per CTA
+                                                 (76801, 256, 256, False, True), (40000, 128, 512, True, False),
+                                                 (50000, 256, 768, False, False), (90000, 512, 128, False, True)])
 def test_gemm_tcgen05(n, k, n_out, gelu, res):
     """The streamed-weight Linear kernel against torch on CPU with the same roundings (GEMM result
     rounded to bf16, then GELU / residual sum rounded again)."""
