@@ -11,13 +11,19 @@
 // swizzle), warp 1 issues four tcgen05.mma (K = 16 each) per chunk into one of TWO accumulators
 // in tensor memory and releases a stage with tcgen05.commit, warps 2..5 take a finished
 // accumulator (tcgen05.ld, thread = row), add the bias, apply GELU, add the residual row and
-// store bf16 while the next tile is already being multiplied into the other accumulator.
+// write bf16 while the next tile is already being multiplied into the other accumulator.
+// The output leaves through shared memory: each epilogue warp packs 64 columns of its 32 rows
+// into a 4 KiB staging tile (128-byte swizzle, so the 16-byte stores of a warp do not collide)
+// and one lane hands the tile to TMA, which writes whole 128-byte lines; a thread that stored
+// its own row directly touched 32 lines per instruction, and that store path, not the tensor
+// pipe or DRAM, set the pace of long inputs (10 000 cycles per 128 x 256 tile).
 // The roundings are those of the unfused sequence (GEMM output rounded to bf16, then GELU or
 // the residual sum rounded again).  Every mbarrier wait is bounded and reports through the
 // status word.
 #include "common.cuh"
 #include "tc05.cuh"
 #include "vec.cuh"
+#include "mma_util.cuh"
 
 namespace ptv3 {
 
@@ -26,7 +32,11 @@ using namespace tc05;
 constexpr int GM_BM = 128;
 constexpr int GM_BK = 64;                       // bf16 columns per stage: one 128-byte swizzle span
 constexpr int GM_A_BYTES = GM_BM * GM_BK * 2;   // 16 KiB
-constexpr int GM_THREADS = 192;
+constexpr int GM_EPI_WARPS = 8;                              // two per quarter of the tensor-memory lanes
+constexpr int GM_THREADS = 64 + GM_EPI_WARPS * 32;
+constexpr int GM_OUT_COLS = 64;                              // columns of a staging tile
+constexpr int GM_OUT_BYTES = 32 * GM_OUT_COLS * 2;           // per epilogue warp: 4 KiB
+constexpr int GM_OUT_TOTAL = GM_EPI_WARPS * GM_OUT_BYTES;
 
 struct GemmArgs {
     const __nv_bfloat16* bias;       // n_out or NULL
@@ -39,11 +49,12 @@ struct GemmArgs {
     uint32_t* status;
 };
 
-__device__ __forceinline__ float gm_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
-template <int BN, int STAGES>
+// MODE: bit 0 = GELU after the bias, bit 1 = residual added last
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
+                                                                  const __grid_constant__ CUtensorMap map_o,
                                                                   const GemmArgs a)
 {
     pdl_launch_next();
@@ -53,8 +64,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32_generic(smem);
-    const int off_bias = STAGES * STAGE_BYTES;            // 2 x BN floats (one set per accumulator)
-    const int off_bar = off_bias + 2 * BN * 4;
+    const int off_out = STAGES * STAGE_BYTES;             // staging tiles of the output
+    const int off_bias = off_out + GM_OUT_TOTAL;          // BN floats
+    const int off_bar = off_bias + BN * 4;
     float* bias_s = reinterpret_cast<float*>(smem + off_bias);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + off_bar);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR);
@@ -68,12 +80,13 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
 
     if (tid == 0) {
         for (int i = 0; i < 2 * STAGES + 2; ++i) mbar_init(full0 + 8 * i, 1);
-        mbar_init(accempty0, 4);          // one arrival per epilogue warp
-        mbar_init(accempty0 + 8, 4);
+        mbar_init(accempty0, GM_EPI_WARPS);          // one arrival per epilogue warp
+        mbar_init(accempty0 + 8, GM_EPI_WARPS);
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_o);
     }
     if (warp == 1) tmem_alloc(sbase + off_bar + 8 * NBAR, 2 * BN);
     fence_before_sync();
@@ -135,49 +148,76 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
         // ---- epilogue: thread = row of the tile ------------------------------------------------
         const int q = warp & 3;                    // the warp's quarter of the tensor-memory lanes
         const int r = q * 32 + lane;
-        const int et = tid - 64;                   // 0..127 among the epilogue threads
+        const int half = (warp - 2) >> 2;          // which half of the tile's columns
+        const int et = tid - 64;                   // index among the epilogue threads
+        const ulonglong2* bias4 = reinterpret_cast<const ulonglong2*>(bias_s);
+        const uint32_t so = sbase + off_out + (warp - 2) * GM_OUT_BYTES;
+        const uint32_t my_row = lane * 128, sw = lane & 7;
         int j = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++j) {
             const int buf = j & 1;
-            const int64_t row = (int64_t)(t / a.col_tiles) * GM_BM + r;
+            const int row0 = (t / a.col_tiles) * GM_BM;
+            const int64_t row = (int64_t)row0 + r;
             const int col0 = (t % a.col_tiles) * BN;
             const bool live = row < a.n;
-            // this tile's bias as floats (the set of the other accumulator may still be in use)
-            float* bs = bias_s + buf * BN;
-            for (int c = et; c < BN; c += 128) bs[c] = a.bias ? __bfloat162float(a.bias[col0 + c]) : 0.f;
-            named_barrier(1, 128);
+            if (j == 0 || a.col_tiles > 1) {
+                // this tile's bias as floats, once every warp has finished the tile before
+                if (j) named_barrier(1, GM_EPI_WARPS * 32);
+                for (int c = et; c < BN; c += GM_EPI_WARPS * 32) bias_s[c] = a.bias ? __bfloat162float(a.bias[col0 + c]) : 0.f;
+                named_barrier(1, GM_EPI_WARPS * 32);
+            }
             ok &= mbar_wait(accfull0 + 8 * buf, (j >> 1) & 1, abort);
             fence_after_sync();
             const uint32_t tm = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
-            __nv_bfloat16* orow = a.out + row * a.n_out + col0;
-            const __nv_bfloat16* rrow = a.residual ? a.residual + row * a.n_out + col0 : nullptr;
-#pragma unroll 2
-            for (int c = 0; c < BN / 32; ++c) {
-                uint4 res4[4] = {};
-                if (rrow && live) {
+            const __nv_bfloat16* rrow = (MODE & 2) ? a.residual + row * a.n_out + col0 : nullptr;
+            constexpr int NCH = BN / GM_OUT_COLS / 2;      // 64-column chunks of this warp
+            for (int c = half * NCH; c < (half + 1) * NCH; ++c) {
+                uint32_t v[2][32];
+                tmem_ld32(tm + c * 64, v[0]);
+                tmem_ld32(tm + c * 64 + 32, v[1]);
+                uint4 res4[(MODE & 2) ? 8 : 1] = {};
+                if ((MODE & 2) && live) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) res4[g] = *reinterpret_cast<const uint4*>(rrow + c * 32 + g * 8);
+                    for (int g = 0; g < 8; ++g) res4[g] = *reinterpret_cast<const uint4*>(rrow + c * 64 + g * 8);
                 }
-                uint32_t v[32];
-                tmem_ld32(tm + c * 32, v);
+                // the copy of the chunk before has finished reading the staging tile
+                if (lane == 0) bulk_wait_read<0>();
+                __syncwarp();
                 tmem_ld_wait();
-                if (!live) continue;
+                tmem_ld_fence(v[0]);
+                tmem_ld_fence(v[1]);
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    float f[8];
+                for (int g = 0; g < 8; ++g) {
+                    const uint32_t* vv = &v[g >> 2][(g & 3) * 8];
+                    const uint4 r4 = res4[(MODE & 2) ? g : 0];
+                    const uint32_t rw[4] = {r4.x, r4.y, r4.z, r4.w};
+                    uint32_t o[4];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float y = gm_round(__uint_as_float(v[g * 8 + i]) + bs[c * 32 + g * 8 + i]);
-                        if (a.gelu) y = gelu_tanh_erf(y);
-                        f[i] = y;
+                    for (int p2 = 0; p2 < 4; ++p2) {
+                        const ulonglong2 b4 = bias4[c * 16 + g * 2 + (p2 >> 1)];
+                        uint64_t y = add2(pack2u(vv[2 * p2], vv[2 * p2 + 1]), (p2 & 1) ? b4.y : b4.x);
+                        float lo, hi;
+                        unpack2(y, lo, hi);
+                        uint32_t packed = pack_bf16(lo, hi);     // the Linear's own output in bf16
+                        if (MODE != 0) {
+                            y = unpack_bf16x2(packed);
+                            if (MODE & 1) y = gelu_tanh_erf2(y);
+                            if (MODE & 2) y = add2(y, unpack_bf16x2(rw[p2]));
+                            unpack2(y, lo, hi);
+                            packed = pack_bf16(lo, hi);
+                        }
+                        o[p2] = packed;
                     }
-                    if (rrow) {
-                        float res[8];
-                        Vec<__nv_bfloat16>::unpack(res4[g], res);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) f[i] += res[i];
-                    }
-                    *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = Vec<__nv_bfloat16>::pack(f);
+                    // (no memory clobber: the bias loads of the next columns may be scheduled above it;
+                    // volatile keeps it before the proxy fence below)
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(so + my_row + ((g ^ sw) << 4)),
+                                 "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]));
+                }
+                fence_proxy_async();
+                __syncwarp();
+                if (lane == 0 && row0 + q * 32 < a.n) {
+                    tma_store_2d(&map_o, col0 + c * GM_OUT_COLS, row0 + q * 32, so);
+                    bulk_commit();
                 }
             }
             // the accumulator may be overwritten
@@ -185,6 +225,8 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
             __syncwarp();
             if (lane == 0) mbar_arrive_one(accempty0 + 8 * buf);
         }
+        // shared memory stays allocated until the last copies have read it
+        if (lane == 0) bulk_wait_read<0>();
     }
     fence_before_sync();
     __syncthreads();
@@ -200,19 +242,32 @@ static bool gemm_shape_ok(int k, int n_out)
     return k >= 64 && k % 64 == 0 && k <= 8192 && n_out >= 128 && n_out % 128 == 0 && n_out <= 8192;
 }
 
-template <int BN, int STAGES>
-static int launch_gemm_as(const CUtensorMap& mx, const CUtensorMap& mw, GemmArgs a, cudaStream_t stream)
+template <int BN, int STAGES, int MODE>
+static int launch_gemm_mode(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a,
+                          cudaStream_t stream)
 {
-    const size_t smem = (size_t)STAGES * (GM_A_BYTES + (size_t)BN * GM_BK * 2) + 2 * BN * 4 + 8 * (2 * STAGES + 4) +
-                        16 + 1024;
-    auto kern = gemm_tc05_kernel<BN, STAGES>;
+    const size_t smem = (size_t)STAGES * (GM_A_BYTES + (size_t)BN * GM_BK * 2) + GM_OUT_TOTAL + BN * 4 +
+                        8 * (2 * STAGES + 4) + 16 + 1024;
+    auto kern = gemm_tc05_kernel<BN, STAGES, MODE>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_gemm_fwd: shared memory attribute");
     a.col_tiles = a.n_out / BN;
     const int64_t tiles = (int64_t)a.row_tiles * a.col_tiles;
-    launch_dependent(kern, dim3((unsigned)(tiles < 148 ? tiles : 148)), dim3(GM_THREADS), smem, stream, mx, mw, a);
+    launch_dependent(kern, dim3((unsigned)(tiles < 148 ? tiles : 148)), dim3(GM_THREADS), smem, stream, mx, mw, mo, a);
     count_launches(1);
     return check_launch("ptv3_gemm_fwd");
+}
+
+template <int BN, int STAGES>
+static int launch_gemm_as(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const GemmArgs& a,
+                          cudaStream_t stream)
+{
+    switch ((a.gelu ? 1 : 0) | (a.residual ? 2 : 0)) {
+    case 0: return launch_gemm_mode<BN, STAGES, 0>(mx, mw, mo, a, stream);
+    case 1: return launch_gemm_mode<BN, STAGES, 1>(mx, mw, mo, a, stream);
+    case 2: return launch_gemm_mode<BN, STAGES, 2>(mx, mw, mo, a, stream);
+    default: return launch_gemm_mode<BN, STAGES, 3>(mx, mw, mo, a, stream);
+    }
 }
 
 static int launch_gemm(const void* x, const void* w, GemmArgs a, cudaStream_t stream)
@@ -221,13 +276,15 @@ static int launch_gemm(const void* x, const void* w, GemmArgs a, cudaStream_t st
     // 256-column tiles halve the traffic of x; 128-column tiles when those would leave SMs idle
     int bn = a.n_out % 256 == 0 ? 256 : 128;
     if (bn == 256 && (int64_t)a.row_tiles * (a.n_out / 256) < 148) bn = 128;
-    CUtensorMap mx, mw;
+    CUtensorMap mx, mw, mo;
     int rc = make_tensor_map_bf16(&mx, x, (uint64_t)a.n, (uint64_t)a.k, (uint64_t)a.k * 2, GM_BM, GM_BK);
     if (rc) return rc;
     rc = make_tensor_map_bf16(&mw, w, (uint64_t)a.n_out, (uint64_t)a.k, (uint64_t)a.k * 2, bn, GM_BK);
     if (rc) return rc;
-    if (bn == 256) return launch_gemm_as<256, 4>(mx, mw, a, stream);
-    return launch_gemm_as<128, 6>(mx, mw, a, stream);
+    rc = make_tensor_map_bf16(&mo, a.out, (uint64_t)a.n, (uint64_t)a.n_out, (uint64_t)a.n_out * 2, 32, GM_OUT_COLS);
+    if (rc) return rc;
+    if (bn == 256) return launch_gemm_as<256, 4>(mx, mw, mo, a, stream);
+    return launch_gemm_as<128, 6>(mx, mw, mo, a, stream);
 }
 
 }  // namespace ptv3
