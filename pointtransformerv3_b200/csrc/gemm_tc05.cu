@@ -50,8 +50,12 @@ struct GemmArgs {
 };
 
 
-// MODE: bit 0 = GELU after the bias, bit 1 = residual added last
-template <int BN, int STAGES, int MODE>
+// MODE: bit 0 = GELU after the bias, bit 1 = residual added last.
+// WRES: the CTA keeps its column tile of W (all K chunks) in shared memory for the whole launch and
+// walks row tiles of that one column tile; only x goes through the ring.  Without it every tile
+// fetches its W chunks again (from L2), which is what paces long inputs once the output path is out
+// of the way: 192 KiB per 128 x 256 tile at K = 256, against 64 KiB of x.
+template <int BN, int STAGES, int MODE, bool WRES>
 __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                                   const __grid_constant__ CUtensorMap map_w,
                                                                   const __grid_constant__ CUtensorMap map_o,
@@ -59,12 +63,15 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
 {
     pdl_launch_next();
     constexpr int B_BYTES = BN * GM_BK * 2;
-    constexpr int STAGE_BYTES = GM_A_BYTES + B_BYTES;
-    constexpr int NBAR = 2 * STAGES + 4;      // full, empty per stage; accumulator full / empty x 2
+    constexpr int STAGE_BYTES = WRES ? GM_A_BYTES : GM_A_BYTES + B_BYTES;
+    constexpr int NBAR = 2 * STAGES + 5;      // full, empty per stage; accumulator full / empty x 2; W
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = smem_u32_generic(smem);
-    const int off_out = STAGES * STAGE_BYTES;             // staging tiles of the output
+    const int nk = a.k / GM_BK;
+    const int w_bytes = WRES ? nk * B_BYTES : 0;          // the resident column tile of W comes first
+    const uint32_t ring = sbase + w_bytes;
+    const int off_out = w_bytes + STAGES * STAGE_BYTES;   // staging tiles of the output
     const int off_bias = off_out + GM_OUT_TOTAL;          // BN floats
     const int off_bar = off_bias + BN * 4;
     float* bias_s = reinterpret_cast<float*>(smem + off_bias);
@@ -72,16 +79,30 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBAR);
     volatile int* abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
     const uint32_t full0 = sbase + off_bar, empty0 = full0 + 8 * STAGES, accfull0 = empty0 + 8 * STAGES,
-                   accempty0 = accfull0 + 16;
+                   accempty0 = accfull0 + 16, wbar = accempty0 + 16;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nk = a.k / GM_BK;
     const int ntiles = a.row_tiles * a.col_tiles;
+    // i-th tile of this CTA.  Column tiles of a row tile run on neighbouring CTAs at the same time, so
+    // the x rows they share are fetched from DRAM once.
+    auto tile_at = [&](int i, int& row0, int& col0) -> bool {
+        if (WRES) {
+            const int rt = (int)blockIdx.x / a.col_tiles + i * ((int)gridDim.x / a.col_tiles);
+            row0 = rt * GM_BM;
+            col0 = ((int)blockIdx.x % a.col_tiles) * BN;
+            return rt < a.row_tiles;
+        }
+        const int t = (int)blockIdx.x + i * (int)gridDim.x;
+        row0 = (t / a.col_tiles) * GM_BM;
+        col0 = (t % a.col_tiles) * BN;
+        return t < ntiles;
+    };
 
     if (tid == 0) {
         for (int i = 0; i < 2 * STAGES + 2; ++i) mbar_init(full0 + 8 * i, 1);
         mbar_init(accempty0, GM_EPI_WARPS);          // one arrival per epilogue warp
         mbar_init(accempty0 + 8, GM_EPI_WARPS);
+        mbar_init(wbar, 1);
         *abort = 0;
         fence_barrier_init();
         prefetch_tensormap(&map_x);
@@ -94,27 +115,31 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
     fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     bool ok = true;
+    if (WRES && tid == 0) {
+        // the weights are not written by the launch before this one: fetched ahead of the wait below
+        int row0, col0;
+        tile_at(0, row0, col0);
+        mbar_expect_tx(wbar, (uint32_t)w_bytes);
+        for (int kc = 0; kc < nk; ++kc) tma_load_2d(sbase + kc * B_BYTES, &map_w, kc * GM_BK, col0, wbar);
+    }
     // barriers, tensor memory and descriptors are set up; everything the kernel before this one in
     // the stream may have written is touched after this wait
     pdl_wait();
 
-    // tile t -> (row tile, column tile); column tiles of a row tile run on neighbouring CTAs, so
-    // the x rows they share are fetched from DRAM once
     if (warp == 0) {
         // ---- producer: K chunks of the x tile and of the W tile, tile after tile -----------------
         if (lane == 0) {
-            int it = 0;
-            for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-                const int row0 = (t / a.col_tiles) * GM_BM, col0 = (t % a.col_tiles) * BN;
+            int it = 0, row0, col0;
+            for (int i = 0; tile_at(i, row0, col0); ++i) {
                 for (int kc = 0; kc < nk; ++kc, ++it) {
                     const int s = it % STAGES;
                     // a stage is free once the products that read it have completed (the first pass
                     // over the ring finds every stage free: waiting for the phase before the first)
                     ok &= mbar_wait(empty0 + 8 * s, ((it / STAGES) & 1) ^ 1, abort);
-                    const uint32_t sa = sbase + s * STAGE_BYTES, sb = sa + GM_A_BYTES;
+                    const uint32_t sa = ring + s * STAGE_BYTES;
                     mbar_expect_tx(full0 + 8 * s, STAGE_BYTES);
                     tma_load_2d(sa, &map_x, kc * GM_BK, row0, full0 + 8 * s);
-                    tma_load_2d(sb, &map_w, kc * GM_BK, col0, full0 + 8 * s);
+                    if (!WRES) tma_load_2d(sa + GM_A_BYTES, &map_w, kc * GM_BK, col0, full0 + 8 * s);
                 }
             }
         }
@@ -122,8 +147,9 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
         // ---- issuer -----------------------------------------------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(GM_BM, BN);
-            int it = 0, j = 0;
-            for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++j) {
+            int it = 0, row0, col0;
+            if (WRES) ok &= mbar_wait(wbar, 0, abort);
+            for (int j = 0; tile_at(j, row0, col0); ++j) {
                 const int buf = j & 1;
                 // the epilogue has read the accumulator's previous tile (first use: free)
                 ok &= mbar_wait(accempty0 + 8 * buf, ((j >> 1) & 1) ^ 1, abort);
@@ -132,7 +158,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
                     const int s = it % STAGES;
                     ok &= mbar_wait(full0 + 8 * s, (it / STAGES) & 1, abort);
                     fence_after_sync();
-                    const uint32_t sa = sbase + s * STAGE_BYTES, sb = sa + GM_A_BYTES;
+                    const uint32_t sa = ring + s * STAGE_BYTES, sb = WRES ? sbase + kc * B_BYTES : sa + GM_A_BYTES;
 #pragma unroll
                     for (int k4 = 0; k4 < GM_BK / 16; ++k4) {
                         const uint64_t da = umma_desc_kmajor(sa + k4 * 32, 128);
@@ -153,14 +179,12 @@ __global__ void __launch_bounds__(GM_THREADS, 1) gemm_tc05_kernel(const __grid_c
         const ulonglong2* bias4 = reinterpret_cast<const ulonglong2*>(bias_s);
         const uint32_t so = sbase + off_out + (warp - 2) * GM_OUT_BYTES;
         const uint32_t my_row = lane * 128, sw = lane & 7;
-        int j = 0;
-        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, ++j) {
+        int row0, col0;
+        for (int j = 0; tile_at(j, row0, col0); ++j) {
             const int buf = j & 1;
-            const int row0 = (t / a.col_tiles) * GM_BM;
             const int64_t row = (int64_t)row0 + r;
-            const int col0 = (t % a.col_tiles) * BN;
             const bool live = row < a.n;
-            if (j == 0 || a.col_tiles > 1) {
+            if (j == 0 || (!WRES && a.col_tiles > 1)) {
                 // this tile's bias as floats, once every warp has finished the tile before
                 if (j) named_barrier(1, GM_EPI_WARPS * 32);
                 for (int c = et; c < BN; c += GM_EPI_WARPS * 32) bias_s[c] = a.bias ? __bfloat162float(a.bias[col0 + c]) : 0.f;
@@ -242,31 +266,43 @@ static bool gemm_shape_ok(int k, int n_out)
     return k >= 64 && k % 64 == 0 && k <= 8192 && n_out >= 128 && n_out % 128 == 0 && n_out <= 8192;
 }
 
-template <int BN, int STAGES, int MODE>
-static int launch_gemm_mode(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a,
-                          cudaStream_t stream)
+// W stays in shared memory when a column tile of it fits beside the ring, the ring of four x chunks
+// still holds a whole tile (K <= 256: with K = 512 the streamed form measured faster) and a CTA has
+// enough tiles to repay loading it
+static bool gemm_w_resident(const GemmArgs& a, int bn)
 {
-    const size_t smem = (size_t)STAGES * (GM_A_BYTES + (size_t)BN * GM_BK * 2) + GM_OUT_TOTAL + BN * 4 +
-                        8 * (2 * STAGES + 4) + 16 + 1024;
-    auto kern = gemm_tc05_kernel<BN, STAGES, MODE>;
+    return a.k <= 256 && (size_t)a.k * bn * 2 <= 131072 && (int64_t)a.row_tiles * (a.n_out / bn) >= 3 * 148;
+}
+
+template <int BN, int STAGES, int MODE, bool WRES>
+static int launch_gemm_mode(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, GemmArgs a,
+                            cudaStream_t stream)
+{
+    const size_t b_bytes = (size_t)BN * GM_BK * 2;
+    const size_t smem = (WRES ? (size_t)(a.k / GM_BK) * b_bytes + (size_t)STAGES * GM_A_BYTES
+                              : (size_t)STAGES * (GM_A_BYTES + b_bytes)) +
+                        GM_OUT_TOTAL + BN * 4 + 8 * (2 * STAGES + 5) + 16 + 1024;
+    auto kern = gemm_tc05_kernel<BN, STAGES, MODE, WRES>;
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
         return check_launch("ptv3_gemm_fwd: shared memory attribute");
     a.col_tiles = a.n_out / BN;
     const int64_t tiles = (int64_t)a.row_tiles * a.col_tiles;
-    launch_dependent(kern, dim3((unsigned)(tiles < 148 ? tiles : 148)), dim3(GM_THREADS), smem, stream, mx, mw, mo, a);
+    // resident W: the same number of CTAs on every column tile
+    const unsigned grid = WRES ? (unsigned)(148 / a.col_tiles * a.col_tiles) : (unsigned)(tiles < 148 ? tiles : 148);
+    launch_dependent(kern, dim3(grid), dim3(GM_THREADS), smem, stream, mx, mw, mo, a);
     count_launches(1);
     return check_launch("ptv3_gemm_fwd");
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool WRES>
 static int launch_gemm_as(const CUtensorMap& mx, const CUtensorMap& mw, const CUtensorMap& mo, const GemmArgs& a,
                           cudaStream_t stream)
 {
     switch ((a.gelu ? 1 : 0) | (a.residual ? 2 : 0)) {
-    case 0: return launch_gemm_mode<BN, STAGES, 0>(mx, mw, mo, a, stream);
-    case 1: return launch_gemm_mode<BN, STAGES, 1>(mx, mw, mo, a, stream);
-    case 2: return launch_gemm_mode<BN, STAGES, 2>(mx, mw, mo, a, stream);
-    default: return launch_gemm_mode<BN, STAGES, 3>(mx, mw, mo, a, stream);
+    case 0: return launch_gemm_mode<BN, STAGES, 0, WRES>(mx, mw, mo, a, stream);
+    case 1: return launch_gemm_mode<BN, STAGES, 1, WRES>(mx, mw, mo, a, stream);
+    case 2: return launch_gemm_mode<BN, STAGES, 2, WRES>(mx, mw, mo, a, stream);
+    default: return launch_gemm_mode<BN, STAGES, 3, WRES>(mx, mw, mo, a, stream);
     }
 }
 
@@ -283,8 +319,11 @@ static int launch_gemm(const void* x, const void* w, GemmArgs a, cudaStream_t st
     if (rc) return rc;
     rc = make_tensor_map_bf16(&mo, a.out, (uint64_t)a.n, (uint64_t)a.n_out, (uint64_t)a.n_out * 2, 32, GM_OUT_COLS);
     if (rc) return rc;
-    if (bn == 256) return launch_gemm_as<256, 4>(mx, mw, mo, a, stream);
-    return launch_gemm_as<128, 6>(mx, mw, mo, a, stream);
+    if (gemm_w_resident(a, bn))
+        return bn == 256 ? launch_gemm_as<256, 4, true>(mx, mw, mo, a, stream)
+                         : launch_gemm_as<128, 4, true>(mx, mw, mo, a, stream);
+    if (bn == 256) return launch_gemm_as<256, 4, false>(mx, mw, mo, a, stream);
+    return launch_gemm_as<128, 6, false>(mx, mw, mo, a, stream);
 }
 
 }  // namespace ptv3
