@@ -54,12 +54,14 @@ __device__ __forceinline__ float lin_round(float v) { return __bfloat162float(__
 constexpr int LIN_STAGE_ROW = 144;
 constexpr int LIN_STAGE_BYTES = 128 * LIN_STAGE_ROW;
 
+// A warp copies the 32 rows its own threads filled (t = thread of the group; rows (t / 32) * 32 ...), so
+// that only the warp has to be in step, not the group.
 __device__ __forceinline__ void stage_to_global(const unsigned char* stage, __nv_bfloat16* dst, int64_t row0,
                                                 int64_t n, int pitch, int col0, int t)
 {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+        const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 3), c = idx & 7;
         if (row0 + r < n)
             *reinterpret_cast<uint4*>(dst + (row0 + r) * pitch + col0 + c * 8) =
                 *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
@@ -71,7 +73,7 @@ __device__ __forceinline__ void global_to_stage(unsigned char* stage, const __nv
 {
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+        const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 3), c = idx & 7;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row0 + r < n) v = *reinterpret_cast<const uint4*>(src + (row0 + r) * pitch + col0 + c * 8);
         *reinterpret_cast<uint4*>(stage + r * LIN_STAGE_ROW + c * 16) = v;
@@ -203,7 +205,7 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
             if (n_out >= 64) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    const int idx = i * 128 + t, r = idx >> 3, c = idx & 7;
+                    const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 3), c = idx & 7;
                     const bool in = row0 + r < a.n;
                     cp_async16_zfill(smem_u32_generic(stage + r * LIN_STAGE_ROW + c * 16),
                                      a.residual + (in ? row0 + r : 0) * n_out + c * 8, in);
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
             } else {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                    const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 2), c = idx & 3;
                     const bool in = row0 + r < a.n;
                     cp_async16_zfill(smem_u32_generic(stage + r * LIN_STAGE_ROW + c * 16),
                                      a.residual + (in ? row0 + r : 0) * n_out + c * 8, in);
@@ -276,19 +278,19 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                             *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = Vec<__nv_bfloat16>::pack(f);
                         }
                     }
-                    named_barrier(1 + g, 128);
+                    __syncwarp();      // the staging rows of a warp are its own
                     if (cw == 64) {
                         stage_to_global(stage, a.out, row0, a.n, n_out, sl * 64, t);
                     } else {   // half slab: 4 pieces per row
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                            const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 2), c = idx & 3;
                             if (row0 + r < a.n)
                                 *reinterpret_cast<uint4*>(a.out + (row0 + r) * n_out + sl * 64 + c * 8) =
                                     *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
                         }
                     }
-                    named_barrier(1 + g, 128);
+                    __syncwarp();      // the staging rows of a warp are its own
                 }
             } else {
                 // The arithmetic below works on pairs of channels (fma.rn.f32x2 / add.rn.f32x2), reads the
@@ -338,14 +340,14 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                     } else {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                            const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 2), c = idx & 3;
                             uint4 v = make_uint4(0, 0, 0, 0);
                             if (row0 + r < a.n)
                                 v = *reinterpret_cast<const uint4*>(a.residual + (row0 + r) * n_out + sl * 64 + c * 8);
                             *reinterpret_cast<uint4*>(stage + r * LIN_STAGE_ROW + c * 16) = v;
                         }
                     }
-                    named_barrier(1 + g, 128);
+                    __syncwarp();      // the staging rows of a warp are its own
                     for (int c = 0; c < cw / 32; ++c) {
                         uint32_t v[32];
                         tmem_ld32(tm_acc + sl * 64 + c * 32, v);
@@ -391,21 +393,21 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                         }
                         tmem_st32(tm_acc + sl * 64 + c * 32, v);
                     }
-                    named_barrier(1 + g, 128);
+                    __syncwarp();      // the staging rows of a warp are its own
                     if (a.sum_out) {
                         if (cw == 64) {
                             stage_to_global(stage, a.sum_out, row0, a.n, n_out, sl * 64, t);
                         } else {
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
-                                const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                                const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 2), c = idx & 3;
                                 if (row0 + r < a.n)
                                     *reinterpret_cast<uint4*>(a.sum_out + (row0 + r) * n_out + sl * 64 + c * 8) =
                                         *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
                             }
                         }
                     }
-                    named_barrier(1 + g, 128);
+                    __syncwarp();      // the staging rows of a warp are its own
                 }
                 const float s2 = hsum2(s2p), q2 = hsum2(q2p);
                 tmem_st_wait();
@@ -440,19 +442,19 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
                             *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = make_uint4(ow[0], ow[1], ow[2], ow[3]);
                         }
                     }
-                    named_barrier(1 + g, 128);
+                    __syncwarp();      // the staging rows of a warp are its own
                     if (cw == 64) {
                         stage_to_global(stage, a.norm_out, row0, a.n, n_out, sl * 64, t);
                     } else {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int idx = i * 128 + t, r = idx >> 2, c = idx & 3;
+                            const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 2), c = idx & 3;
                             if (row0 + r < a.n)
                                 *reinterpret_cast<uint4*>(a.norm_out + (row0 + r) * n_out + sl * 64 + c * 8) =
                                     *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
                         }
                     }
-                    named_barrier(1 + g, 128);
+                    __syncwarp();      // the staging rows of a warp are its own
                 }
             }
             fence_before_sync();
