@@ -42,6 +42,7 @@ struct LinearArgs {
     int nacc;         // accumulators per group in tensor memory (2 where 2 x groups x columns fit in 512)
     int w_box_rows;   // rows per TMA box of W
     int residual_mode;
+    int out_box;      // plain mode: columns per staging tile and TMA store (64, or 32 when n_out % 64 != 0)
     uint32_t* status;
 };
 
@@ -83,6 +84,7 @@ __device__ __forceinline__ void global_to_stage(unsigned char* stage, const __nv
 template <int K>
 __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_constant__ CUtensorMap map_x,
                                                              const __grid_constant__ CUtensorMap map_w,
+                                                             const __grid_constant__ CUtensorMap map_o,
                                                              const LinearArgs a)
 {
     pdl_launch_next();
@@ -260,37 +262,44 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
             }
             fence_after_sync();
             const uint32_t tm_acc = tm_acc0 + cur * tm_acc_step;
-            const int64_t row = row0 + t;
-            const bool live = row < a.n;
             if (!a.residual_mode) {
-                for (int sl = 0; sl < nslabs; ++sl) {
-                    const int cw = min(64, n_out - sl * 64);   // 64 or 32 columns in this slab
-                    for (int c = 0; c < cw / 32; ++c) {
+                // Plain mode: a warp packs `slw` columns of its 32 rows into its own staging tile (rows
+                // slw * 2 bytes wide, swizzled like the tensor map so that the 16-byte stores of a warp
+                // do not collide) and one lane hands the tile to a TMA store, which writes whole lines.
+                const int slw = a.out_box, lane = t & 31;
+                const uint32_t wtile = smem_u32_generic(stage) + (t >> 5) * 4096;
+                const uint32_t my = wtile + lane * (slw * 2), swz = slw == 64 ? (lane & 7) : ((lane >> 1) & 3);
+                for (int sl = 0; sl < n_out / slw; ++sl) {
+                    // the copy of the slab before has finished reading the staging tile
+                    if (lane == 0) bulk_wait_read<0>();
+                    __syncwarp();
+                    for (int c = 0; c < slw / 32; ++c) {
+                        const int ch0 = sl * slw + c * 32;
+                        float4 bb[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) bb[i] = *reinterpret_cast<const float4*>(bias_s + ch0 + i * 4);
                         uint32_t v[32];
-                        tmem_ld32(tm_acc + sl * 64 + c * 32, v);
+                        tmem_ld32(tm_acc + ch0, v);
                         tmem_ld_wait();
+                        tmem_ld_fence(v);
 #pragma unroll
                         for (int q = 0; q < 4; ++q) {
-                            float f[8];
-#pragma unroll
-                            for (int i = 0; i < 8; ++i)
-                                f[i] = __uint_as_float(v[q * 8 + i]) + bias_s[sl * 64 + c * 32 + q * 8 + i];
-                            *reinterpret_cast<uint4*>(my_row + c * 64 + q * 16) = Vec<__nv_bfloat16>::pack(f);
+                            const float4 b0 = bb[2 * q], b1 = bb[2 * q + 1];
+                            const uint32_t* vv = v + q * 8;
+                            const uint32_t o0 = pack_bf16(__uint_as_float(vv[0]) + b0.x, __uint_as_float(vv[1]) + b0.y);
+                            const uint32_t o1 = pack_bf16(__uint_as_float(vv[2]) + b0.z, __uint_as_float(vv[3]) + b0.w);
+                            const uint32_t o2 = pack_bf16(__uint_as_float(vv[4]) + b1.x, __uint_as_float(vv[5]) + b1.y);
+                            const uint32_t o3 = pack_bf16(__uint_as_float(vv[6]) + b1.z, __uint_as_float(vv[7]) + b1.w);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(my + (((c * 4 + q) ^ swz) << 4)),
+                                         "r"(o0), "r"(o1), "r"(o2), "r"(o3));
                         }
                     }
-                    __syncwarp();      // the staging rows of a warp are its own
-                    if (cw == 64) {
-                        stage_to_global(stage, a.out, row0, a.n, n_out, sl * 64, t);
-                    } else {   // half slab: 4 pieces per row
-#pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int idx = i * 32 + (t & 31), r = (t & ~31) + (idx >> 2), c = idx & 3;
-                            if (row0 + r < a.n)
-                                *reinterpret_cast<uint4*>(a.out + (row0 + r) * n_out + sl * 64 + c * 8) =
-                                    *reinterpret_cast<const uint4*>(stage + r * LIN_STAGE_ROW + c * 16);
-                        }
+                    fence_proxy_async();
+                    __syncwarp();
+                    if (lane == 0 && row0 + (t & ~31) < a.n) {
+                        tma_store_2d(&map_o, sl * slw, (int)row0 + (t & ~31), wtile);
+                        bulk_commit();
                     }
-                    __syncwarp();      // the staging rows of a warp are its own
                 }
             } else {
                 // The arithmetic below works on pairs of channels (fma.rn.f32x2 / add.rn.f32x2), reads the
@@ -461,6 +470,8 @@ __global__ void __launch_bounds__(512, 1) linear_tc05_kernel(const __grid_consta
             named_barrier(1 + g, 128);
         }
     }
+    // shared memory stays allocated until the last TMA stores have read it
+    if ((tid & 31) == 0) bulk_wait_read<0>();
     fence_before_sync();
     __syncthreads();
     if (warp == 0) tmem_dealloc(tmem_base, 512);
@@ -487,9 +498,15 @@ static int launch_linear(const void* x, const void* w, LinearArgs a, int k, cuda
         --groups;
     a.groups = groups;
     a.nacc = 2 * groups * tm_cols <= 512 ? 2 : 1;
-    CUtensorMap mx, mw;
+    CUtensorMap mx, mw, mo;
     int rc = make_tensor_map_bf16(&mx, x, (uint64_t)a.n, k, (uint64_t)k * 2, 128, kcols);
     if (rc) return rc;
+    mo = mx;      // residual mode writes its outputs with plain stores
+    if (!a.residual_mode) {
+        a.out_box = a.n_out % 64 == 0 ? 64 : 32;
+        rc = make_tensor_map_bf16(&mo, a.out, (uint64_t)a.n, (uint64_t)a.n_out, (uint64_t)a.n_out * 2, 32, a.out_box);
+        if (rc) return rc;
+    }
     rc = make_tensor_map_bf16(&mw, w, a.n_out, k, (uint64_t)k * 2, a.w_box_rows, kcols);
     if (rc) return rc;
     const size_t smem = (size_t)kb * a.n_out * sw + (size_t)groups * (2 * kb * 128 * sw + LIN_STAGE_BYTES) +
@@ -504,7 +521,7 @@ static int launch_linear(const void* x, const void* w, LinearArgs a, int k, cuda
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_req) !=        \
             cudaSuccess)                                                                                     \
             return check_launch("ptv3_linear_fwd: shared memory attribute");                                 \
-        launch_dependent(kern, dim3((unsigned)grid), dim3(512), smem_req, stream, mx, mw, a);                \
+        launch_dependent(kern, dim3((unsigned)grid), dim3(512), smem_req, stream, mx, mw, mo, a);                \
     } while (0)
     if (k == 32) LIN_LAUNCH(32);
     else if (k == 64) LIN_LAUNCH(64);
