@@ -474,7 +474,9 @@ def test_linear_tcgen05(k, n_out, n):
                                                  (1, 64, 128, True, True), (2049, 1024, 256, False, False),
                                                  # long inputs: several tiles per CTA
                                                  (76801, 256, 256, False, True), (40000, 128, 512, True, False),
-                                                 (50000, 256, 768, False, False), (90000, 512, 128, False, True)])
+                                                 (50000, 256, 768, False, False), (90000, 512, 128, False, True),
+                                                 # 128-column tiles with the weights resident; both epilogue steps
+                                                 (70000, 128, 384, False, True), (60000, 64, 128, True, True)])
 def test_gemm_tcgen05(n, k, n_out, gelu, res):
     """The streamed-weight Linear kernel against torch on CPU with the same roundings (GEMM result
     rounded to bf16, then GELU / residual sum rounded again)."""
