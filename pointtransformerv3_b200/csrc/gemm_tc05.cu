@@ -9,9 +9,10 @@
 // A persistent CTA per SM walks 128-row x BN-column tiles (BN = 256 or 128).  Warp 0 streams
 // 64-wide K chunks of x and W through a ring of stages in shared memory with TMA (128-byte
 // swizzle), warp 1 issues four tcgen05.mma (K = 16 each) per chunk into one of TWO accumulators
-// in tensor memory and releases a stage with tcgen05.commit, warps 2..5 take a finished
-// accumulator (tcgen05.ld, thread = row), add the bias, apply GELU, add the residual row and
-// write bf16 while the next tile is already being multiplied into the other accumulator.
+// in tensor memory and releases a stage with tcgen05.commit, warps 2..9 take a finished
+// accumulator (tcgen05.ld, thread = row; two warps per quarter of the tensor-memory lanes, half of
+// the tile's columns each), add the bias, apply GELU, add the residual row and write bf16 while
+// the next tile is already being multiplied into the other accumulator.
 // The output leaves through shared memory: each epilogue warp packs 64 columns of its 32 rows
 // into a 4 KiB staging tile (128-byte swizzle, so the 16-byte stores of a warp do not collide)
 // and one lane hands the tile to TMA, which writes whole 128-byte lines; a thread that stored
