@@ -64,6 +64,8 @@ const char* ptv3_last_error(void);
 int ptv3_version(void);
 /* kernels launched by this library in this process so far */
 long long ptv3_launch_count(void);
+/* clears a device status word in stream order (a memset, not a kernel) */
+int ptv3_status_reset(uint32_t* status, void* stream);
 
 /*
  * Space-filling-curve codes.
@@ -104,6 +106,18 @@ size_t ptv3_argsort_workspace_bytes(int k, int64_t n, int sig_bits);
 int ptv3_argsort_inverse(const int64_t* codes, int k, int64_t n, int sig_bits, int64_t* order,
                          int64_t* inverse, uint32_t* status, void* workspace, size_t workspace_bytes,
                          void* stream);
+
+/*
+ * The scene index of every point and the (batch, x, y, z) rows of the sparse tensor,
+ * from the scene offsets.  Replaces offset2batch (model.py:35-40) and the concatenation
+ * of Point.sparsify (model.py:150-152).
+ *   offset      n_scenes int64 (device): cumulative point counts, offset[last] = n
+ *   grid_coord  n x 3 int32 (needed only with `indices`)
+ *   batch       n int64 out, or NULL
+ *   indices     n x 4 int32 out (16-byte aligned), or NULL
+ */
+int ptv3_batch_indices(const int64_t* offset, int n_scenes, const int32_t* grid_coord, int64_t n,
+                       int64_t* batch, int32_t* indices, void* stream);
 
 /*
  * Patch padding plan of serialized attention.
@@ -178,6 +192,17 @@ int ptv3_attention_rpe_fwd(const void* qkv, const int64_t* order, const int64_t*
 size_t ptv3_kmap_workspace_bytes(int64_t n);
 int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int32_t* nbr, uint32_t* status,
                     void* workspace, size_t workspace_bytes, void* stream);
+/*
+ * The same table with its columns in the order the convolution walks its tiles:
+ * column p describes voxel row_order[p] (nbr[o][p] = row of the voxel at
+ * coordinate(row_order[p]) + offset o; the stored rows keep the natural numbering).
+ * This is ptv3_kmap_build followed by a permutation of the columns, without the
+ * second pass over the table.  row_order: n int64, a permutation (the serialized
+ * order of model.py:118-126 in the backbone), or NULL for the natural order.
+ */
+int ptv3_kmap_build_ordered(const int32_t* indices, int64_t n, int ksize, const int64_t* row_order,
+                            int32_t* nbr, uint32_t* status, void* workspace, size_t workspace_bytes,
+                            void* stream);
 
 /*
  * ptv3_kmap_build for callers that cannot hand over a workspace because they

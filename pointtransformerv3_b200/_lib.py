@@ -47,7 +47,10 @@ SIGNATURES = {
     "ptv3_attention_rpe_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_int, c_ptr, c_i64, c_int,
                                        c_int, c_int, c_int, c_f32, c_int, c_ptr]),
     "ptv3_kmap_workspace_bytes": (c_sz, [c_i64]),
+    "ptv3_status_reset": (c_int, [c_ptr, c_ptr]),
+    "ptv3_batch_indices": (c_int, [c_ptr, c_int, c_ptr, c_i64, c_ptr, c_ptr, c_ptr]),
     "ptv3_kmap_build": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
+    "ptv3_kmap_build_ordered": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr, c_ptr, c_sz, c_ptr]),
     "ptv3_kmap_static_max_voxels": (c_i64, []),
     "ptv3_kmap_build_static": (c_int, [c_ptr, c_i64, c_int, c_ptr, c_ptr, c_ptr]),
     "ptv3_subm_conv_fwd": (c_int, [c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_ptr, c_i64, c_int, c_int, c_int,

@@ -34,3 +34,10 @@ int check_launch(const char* what)
 extern "C" const char* ptv3_last_error(void) { return ptv3::g_err; }
 extern "C" int ptv3_version(void) { return 1; }
 extern "C" long long ptv3_launch_count(void) { return ptv3::launches(); }
+extern "C" int ptv3_status_reset(uint32_t* status, void* stream)
+{
+    PTV3_REQUIRE(status != nullptr, PTV3_ERR_INVALID_ARGUMENT, "ptv3_status_reset: null pointer");
+    if (cudaMemsetAsync(status, 0, sizeof(uint32_t), (cudaStream_t)stream) != cudaSuccess)
+        return ptv3::check_launch("ptv3_status_reset");
+    return PTV3_OK;
+}

@@ -45,6 +45,7 @@ __global__ void __launch_bounds__(256) km_probe_kernel(const int32_t* __restrict
                                                        const unsigned long long* __restrict__ keys,
                                                        const uint32_t* __restrict__ vals,
                                                        uint64_t cap_mask, int32_t* __restrict__ nbr,
+                                                       const int64_t* __restrict__ row_order,
                                                        uint32_t* __restrict__ status)
 {
     // the offset is the same for the whole CTA: one thread does the runtime divisions
@@ -60,7 +61,8 @@ __global__ void __launch_bounds__(256) km_probe_kernel(const int32_t* __restrict
     const int dx = delta[0], dy = delta[1], dz = delta[2];
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const int4 v = reinterpret_cast<const int4*>(indices)[i];
+    // column i of the table describes voxel row_order[i] (voxel i without an order)
+    const int4 v = reinterpret_cast<const int4*>(indices)[row_order ? row_order[i] : i];
     int32_t found = -1;
     uint64_t key;
     if (km_key(v.x, v.y + dx, v.z + dy, v.w + dz, key)) {
@@ -85,13 +87,15 @@ __global__ void __launch_bounds__(256) km_probe_kernel(const int32_t* __restrict
 __global__ void __launch_bounds__(256) km_block_probe_kernel(const int32_t* __restrict__ indices, int64_t n,
                                                              int ksize, VoxelIndex vi,
                                                              int32_t* __restrict__ nbr,
+                                                             const int64_t* __restrict__ row_order,
                                                              uint32_t* __restrict__ status)
 {
     __shared__ uint32_t block_s[8][256];
     const int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int r = ksize / 2;
-    const int4 c = reinterpret_cast<const int4*>(indices)[i];
+    // column i of the table describes voxel row_order[i] (voxel i without an order)
+    const int4 c = reinterpret_cast<const int4*>(indices)[row_order ? row_order[i] : i];
     bool overflow = false;
 #pragma unroll
     for (int bi = 0; bi < 8; ++bi) {
@@ -161,6 +165,13 @@ extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int
                                uint32_t* status, void* workspace, size_t workspace_bytes,
                                void* stream_)
 {
+    return ptv3_kmap_build_ordered(indices, n, ksize, nullptr, nbr, status, workspace, workspace_bytes, stream_);
+}
+
+extern "C" int ptv3_kmap_build_ordered(const int32_t* indices, int64_t n, int ksize, const int64_t* row_order,
+                                       int32_t* nbr, uint32_t* status, void* workspace, size_t workspace_bytes,
+                                       void* stream_)
+{
     using namespace ptv3;
     PTV3_REQUIRE(n >= 0 && n < (1ll << 31), PTV3_ERR_INVALID_ARGUMENT, "ptv3_kmap_build: bad n");
     PTV3_REQUIRE(ksize == 1 || ksize == 3 || ksize == 5 || ksize == 7, PTV3_ERR_UNSUPPORTED,
@@ -179,7 +190,7 @@ extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int
         VoxelIndex vi;
         const int rc = build_voxel_index(indices, n, workspace, status, stream, &vi);
         if (rc != PTV3_OK) return rc;
-        km_block_probe_kernel<<<blocks, 256, 0, stream>>>(indices, n, ksize, vi, nbr, status);
+        km_block_probe_kernel<<<blocks, 256, 0, stream>>>(indices, n, ksize, vi, nbr, row_order, status);
         count_launches(1);
         return check_launch("ptv3_kmap_build");
     }
@@ -192,7 +203,7 @@ extern "C" int ptv3_kmap_build(const int32_t* indices, int64_t n, int ksize, int
         return check_launch("ptv3_kmap_build: table reset");
     km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
     km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(
-        indices, n, ksize, keys, vals, cap - 1, nbr, status);
+        indices, n, ksize, keys, vals, cap - 1, nbr, row_order, status);
     count_launches(2);
     return check_launch("ptv3_kmap_build");
 }
@@ -278,7 +289,7 @@ extern "C" int ptv3_kmap_build_static(const int32_t* indices, int64_t n, int ksi
     const unsigned blocks = (unsigned)((n + 255) / 256);
     km_insert_kernel<<<blocks, 256, 0, stream>>>(indices, n, keys, vals, cap - 1, status);
     km_probe_kernel<<<dim3(blocks, ksize * ksize * ksize), 256, 0, stream>>>(
-        indices, n, ksize, keys, vals, cap - 1, nbr, status);
+        indices, n, ksize, keys, vals, cap - 1, nbr, nullptr, status);
     count_launches(2);
     return check_launch("ptv3_kmap_build_static");
 }

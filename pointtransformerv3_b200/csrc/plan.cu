@@ -196,7 +196,53 @@ static PoolWs pool_ws(int k, int64_t n, int B)
     return w;
 }
 
+// ----------------------------------------------------------------------------
+// batch index of every point from the scene offsets, and the (batch, x, y, z) rows
+// of the sparse tensor (model.py:35-40 and :150-152)
+// ----------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) batch_indices_kernel(const int64_t* __restrict__ offset, int B,
+                                                            const int32_t* __restrict__ grid_coord, int64_t n,
+                                                            int64_t* __restrict__ batch,
+                                                            int32_t* __restrict__ indices)
+{
+    extern __shared__ int64_t sm[];      // B scene ends
+    for (int s = threadIdx.x; s < B; s += blockDim.x) sm[s] = offset[s];
+    __syncthreads();
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += stride) {
+        int lo = 0, hi = B - 1;          // first scene whose end lies beyond i (the last one at worst)
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (sm[mid] > i) hi = mid; else lo = mid + 1;
+        }
+        if (batch) batch[i] = lo;
+        if (indices)
+            reinterpret_cast<int4*>(indices)[i] =
+                make_int4(lo, grid_coord[3 * i], grid_coord[3 * i + 1], grid_coord[3 * i + 2]);
+    }
+}
+
 }  // namespace ptv3
+
+extern "C" int ptv3_batch_indices(const int64_t* offset, int n_scenes, const int32_t* grid_coord, int64_t n,
+                                  int64_t* batch, int32_t* indices, void* stream)
+{
+    using namespace ptv3;
+    PTV3_REQUIRE(n_scenes >= 1 && n_scenes <= PAD_MAX_SCENES, PTV3_ERR_UNSUPPORTED,
+                 "ptv3_batch_indices: %d scenes outside [1, %d]", n_scenes, PAD_MAX_SCENES);
+    PTV3_REQUIRE(n >= 0, PTV3_ERR_INVALID_ARGUMENT, "ptv3_batch_indices: n < 0");
+    if (n == 0 || (!batch && !indices)) return PTV3_OK;
+    PTV3_REQUIRE(offset && (!indices || grid_coord), PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_batch_indices: null pointer");
+    PTV3_REQUIRE(((uintptr_t)indices & 15) == 0, PTV3_ERR_INVALID_ARGUMENT,
+                 "ptv3_batch_indices: indices must be 16-byte aligned");
+    int64_t blocks = (n + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    batch_indices_kernel<<<(unsigned)blocks, 256, (size_t)n_scenes * sizeof(int64_t), (cudaStream_t)stream>>>(
+        offset, n_scenes, grid_coord, n, batch, indices);
+    count_launches(1);
+    return check_launch("ptv3_batch_indices");
+}
 
 extern "C" int ptv3_pad_plan(const int64_t* offset, int n_scenes, int patch, int64_t n, int64_t n_pad,
                              int n_seq, int64_t* pad, int64_t* unpad, int32_t* cu_seqlens,

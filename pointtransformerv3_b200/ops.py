@@ -109,7 +109,13 @@ def argsort_inverse(codes, sig_bits, status=None):
 
 
 def new_status(device):
-    return torch.zeros(1, dtype=torch.int32, device=device)
+    """A cleared device status word (cleared by a memset in stream order)."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return torch.zeros(1, dtype=torch.int32, device=device)
+    status = torch.empty(1, dtype=torch.int32, device=device)
+    _lib.check(_lib.load().ptv3_status_reset(_lib.ptr(status), _lib.stream()), "ptv3_status_reset")
+    return status
 
 
 def pad_layout(counts, patch):
@@ -194,9 +200,31 @@ def attention_rpe(qkv, order_row, pad, unpad, cu_seqlens, grid_coord, rpe_table,
     return out
 
 
-def kmap_build(indices, ksize, status=None):
-    """indices (N,4) int32 (b,x,y,z) -> nbr (ksize^3, N) int32, offset-major."""
-    _lib.require_cuda(indices)
+def batch_indices(offset, n, grid_coord=None, want_batch=True):
+    """(batch, indices): the scene index of each of the n points (int64) and, with grid_coord, the
+    (n, 4) int32 rows (batch, x, y, z) of the sparse tensor; one kernel, no device read."""
+    _lib.require_cuda(offset, grid_coord)
+    lib = _lib.load()
+    offset = offset.to(torch.int64).contiguous()
+    n = int(n)
+    dev = offset.device
+    batch = torch.empty(n, dtype=torch.int64, device=dev) if want_batch else None
+    indices = None
+    if grid_coord is not None:
+        grid_coord = grid_coord.to(torch.int32).contiguous()
+        if grid_coord.shape != (n, 3):
+            raise ValueError("grid_coord must be (n, 3)")
+        indices = torch.empty((n, 4), dtype=torch.int32, device=dev)
+    _lib.check(lib.ptv3_batch_indices(_lib.ptr(offset), offset.shape[0], _lib.ptr(grid_coord), n, _lib.ptr(batch),
+                                      _lib.ptr(indices), _lib.stream()), "ptv3_batch_indices")
+    return batch, indices
+
+
+def kmap_build(indices, ksize, status=None, row_order=None):
+    """indices (N,4) int32 (b,x,y,z) -> nbr (ksize^3, N) int32, offset-major.
+    row_order: optional (N,) int64 permutation; column p then describes voxel row_order[p]
+    (the table of the natural order with its columns permuted)."""
+    _lib.require_cuda(indices, row_order)
     lib = _lib.load()
     indices = indices.to(torch.int32).contiguous()
     n = indices.shape[0]
@@ -207,8 +235,13 @@ def kmap_build(indices, ksize, status=None):
     if own:
         status = new_status(indices.device)
     with timed("kmap_k%d" % ksize, n * (16.0 + 4.0 * ksize ** 3)):
-        _lib.check(lib.ptv3_kmap_build(_lib.ptr(indices), n, int(ksize), _lib.ptr(nbr), _lib.ptr(status),
-                                       _lib.ptr(ws), nbytes, _lib.stream()), "ptv3_kmap_build")
+        if row_order is not None:
+            row_order = row_order.to(torch.int64).contiguous()
+            if row_order.shape != (n,):
+                raise ValueError("row_order must hold one entry per voxel")
+        _lib.check(lib.ptv3_kmap_build_ordered(_lib.ptr(indices), n, int(ksize), _lib.ptr(row_order), _lib.ptr(nbr),
+                                               _lib.ptr(status), _lib.ptr(ws), nbytes, _lib.stream()),
+                   "ptv3_kmap_build")
     if own:
         _lib.raise_on_status(status, "ptv3_kmap_build")
     return nbr
@@ -242,6 +275,18 @@ def subm_conv(feat, nbr, weight, bias=None, algo=0, row_order=None, status=None)
     if own:
         _lib.raise_on_status(status, "ptv3_subm_conv_fwd")
     return out
+
+
+def _offsets_to_device(counts, dev):
+    """Cumulative counts as a device tensor: summed on the host (the counts are there already) and
+    copied from pinned memory in stream order.  The pinned words are reused by the next plan, which
+    the host only starts after it has waited for kernels queued behind this copy."""
+    off_host = _pinned(len(counts), torch.int64, "pool_plan.offset")
+    acc = 0
+    for i, c in enumerate(counts):
+        acc += int(c)
+        off_host[i] = acc
+    return off_host.to(dev, non_blocking=True)
 
 
 def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=None, status=None):
@@ -296,7 +341,7 @@ def pool_plan(code, order, grid_coord, batch, n_scenes, pooling_depth, row_perm=
     packed = lambda t: t.view(-1)[: k * m].view(k, m)
     return dict(cluster=cluster, idx_ptr=idx_ptr[: m + 1], head=head[:m],
                 code=packed(pcode), order=packed(porder), inverse=packed(pinv), grid_coord=pgrid[:m],
-                batch=pbatch[:m], counts=host[1:], m=m, offset=torch.cumsum(meta[1:], 0))
+                batch=pbatch[:m], counts=host[1:], m=m, offset=_offsets_to_device(host[1:], dev))
 
 
 POLL_SECONDS = 2.0      # how long a host thread polls a "done" word before it asks the driver

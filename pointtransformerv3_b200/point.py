@@ -85,7 +85,10 @@ class Point(AttrDict):
                 if k in self.keys() and torch.is_tensor(self[k]):
                     n = self[k].shape[0]
                     break
-            self["batch"] = offset2batch(self.offset, n)
+            if n is not None and self.offset.is_cuda:
+                self["batch"] = ops.batch_indices(self.offset, n)[0]      # one kernel of this library
+            else:
+                self["batch"] = offset2batch(self.offset, n)
         elif "offset" not in self.keys() and "batch" in self.keys():
             self["offset"] = batch2offset(self.batch)
 
@@ -94,7 +97,7 @@ class Point(AttrDict):
         and shared with the levels pooled from this one)."""
         if "_status" not in self.keys():
             ref = self.feat if "feat" in self.keys() else self.batch
-            self["_status"] = torch.zeros(1, dtype=torch.int32, device=ref.device)
+            self["_status"] = ops.new_status(ref.device)
         return self["_status"]
 
     def check_status(self, what="point operators", force=False):
@@ -130,14 +133,15 @@ class Point(AttrDict):
         n_scene_bits = len(self.offset).bit_length()
         assert depth * 3 + n_scene_bits <= 63
         assert depth <= 16
+        if shuffle_orders:
+            # the reference shuffles the finished rows (model.py:128-132); the rows are independent of
+            # each other, so the same draw applied to the list of orders gives the same tensors
+            # without re-stacking them
+            perm = torch.randperm(len(order)).tolist()
+            order = [order[i] for i in perm]
         code = ops.encode(self.grid_coord, self.batch, depth, order)
         sorted_order, inverse = ops.argsort_inverse(code, depth * 3 + n_scene_bits, self.device_status())
         self.check_status("ptv3_argsort_inverse")
-        if shuffle_orders:
-            perm = torch.randperm(code.shape[0]).tolist()
-            code = torch.stack([code[i] for i in perm])
-            sorted_order = torch.stack([sorted_order[i] for i in perm])
-            inverse = torch.stack([inverse[i] for i in perm])
         self["serialized_code"] = code
         self["serialized_order"] = sorted_order
         self["serialized_inverse"] = inverse
@@ -148,6 +152,8 @@ class Point(AttrDict):
         ready = self.pop("_sparse_indices", None)
         if ready is not None:
             return ready
+        if self.grid_coord.is_cuda and "offset" in self.keys():
+            return ops.batch_indices(self.offset, self.grid_coord.shape[0], self.grid_coord, want_batch=False)[1]
         return torch.cat([self.batch.unsqueeze(-1).int(), self.grid_coord.int()], dim=1).contiguous()
 
     def sparsify(self, pad=96):

@@ -64,12 +64,10 @@ class SparseConvTensor:
             if indice_key is not None:
                 self.indice_dict[key] = entry
             return entry
-        nbr = ops.kmap_build(self.indices, kernel_size, self.status)
+        nbr = ops.kmap_build(self.indices, kernel_size, self.status, self.row_order)
         if self.status is not None and not self.defer_status:
             from . import _lib
             _lib.raise_on_status(self.status, "ptv3_kmap_build")
-        if self.row_order is not None:
-            nbr = nbr.index_select(1, self.row_order)
         entry = (nbr, self.row_order)
         if indice_key is not None:
             self.indice_dict[key] = entry
@@ -170,9 +168,7 @@ modules = _Modules()
 def prebuild_kernel_map(indices, row_order, kernel_size, status, with_pairs):
     """Kernel map (and optionally its pair list) of a voxel set, in the form
     SparseConvTensor(prebuilt=...) takes."""
-    nbr = ops.kmap_build(indices, kernel_size, status)
-    if row_order is not None:
-        nbr = nbr.index_select(1, row_order)
+    nbr = ops.kmap_build(indices, kernel_size, status, row_order)
     out = {kernel_size: (nbr, row_order)}
     if with_pairs:
         out[(kernel_size, "pairs")] = ops.conv_pairs_build(nbr, row_order)

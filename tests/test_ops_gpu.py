@@ -87,6 +87,35 @@ def test_kernel_map_duplicates_and_edges():
     assert torch.equal(got.t().long(), ref)
 
 
+def test_batch_indices_match_torch():
+    """ptv3_batch_indices against repeat_interleave and the concatenation it replaces (an empty
+    scene in the middle, one scene, many scenes)."""
+    from pointtransformerv3_b200.point import offset2batch
+    g = torch.Generator().manual_seed(3)
+    for counts in ([5, 0, 7, 1], [1000], [3] * 40, [0, 0, 9]):
+        offset = torch.tensor(counts).cumsum(0)
+        n = int(offset[-1])
+        grid = torch.randint(0, 500, (n, 3), generator=g, dtype=torch.int32)
+        batch, ind = ops.batch_indices(offset.cuda(), n, grid.cuda())
+        want = offset2batch(offset, n)
+        assert torch.equal(batch.cpu(), want)
+        assert torch.equal(ind.cpu(), torch.cat([want.unsqueeze(-1).int(), grid], 1))
+
+
+@pytest.mark.parametrize("k", [3, 5, 7])
+def test_kmap_in_row_order(k):
+    """ptv3_kmap_build_ordered: the table of the natural order with its columns permuted, bit for bit."""
+    g = torch.Generator().manual_seed(k)
+    ind = torch.unique(torch.cat([torch.randint(0, 2, (3000, 1), generator=g),
+                                  torch.randint(0, 24, (3000, 3), generator=g)], 1), dim=0).int()
+    order = torch.randperm(ind.shape[0], generator=g)
+    plain = ops.kmap_build(ind.cuda(), k)
+    got = ops.kmap_build(ind.cuda(), k, row_order=order.cuda())
+    assert torch.equal(got, plain.index_select(1, order.cuda()))
+    with pytest.raises(ValueError):
+        ops.kmap_build(ind.cuda(), k, row_order=order[:-1].cuda())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("k,cin,cout", [(3, 32, 32), (3, 64, 64), (3, 128, 128), (5, 6, 32), (5, 4, 32),
                                         (3, 48, 80)])
