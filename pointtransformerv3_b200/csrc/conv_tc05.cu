@@ -330,6 +330,9 @@ int launch_conv_tc05(const void* feat, const int32_t* nbr, const void* weight, c
     if (c_in == 32) return launch_conv_tc05_as<32, 32, 6, 2>(weight, a, stream);
     // 128 output channels per CTA halve the gathers of a tile; 64 when that would leave SMs idle
     const int64_t tiles = (n + CT_TM - 1) / CT_TM;
+    // long inputs with wide outputs: 256 output channels per CTA (the gathers of a tile once more halved,
+    // every product twice as wide), four stages of 48 KiB
+    if (c_out % 256 == 0 && tiles * (c_out / 256) >= 148) return launch_conv_tc05_as<256, 64, 4, 2>(weight, a, stream);
     if (c_out % 128 == 0 && tiles * (c_out / 128) >= 120) return launch_conv_tc05_as<128, 64, 6, 2>(weight, a, stream);
     // many tiles: two CTAs per SM, so that one tile's prologue and epilogue run beside another's products
     if (tiles * (c_out / 64) >= 2 * 148) return launch_conv_tc05_as<64, 64, 4, 2>(weight, a, stream);

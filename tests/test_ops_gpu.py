@@ -338,6 +338,33 @@ def test_subm_conv_tensor_core_path(c, permuted):
     assert rel_l2(got, ref) < 4e-3
 
 
+@pytest.mark.parametrize("voxels,cin,cout", [(28000, 256, 256), (14000, 256, 512)])
+def test_subm_conv_tcgen05_wide_tiles(voxels, cin, cout):
+    """Inputs long and wide enough for the 256-output-channel tiles of the tcgen05 convolution
+    (at least 148 of them): against the fp32 oracle and the mma.sync path, in serialized row order,
+    twice for bit-identical results."""
+    data = small_batch([voxels * 7 // 10, voxels * 3 // 10], 9)
+    batch = O.offset_to_batch(data["offset"])
+    ind = torch.unique(O.sparse_indices(batch, data["grid_coord"]), dim=0)
+    n = ind.shape[0]
+    assert (n + 127) // 128 * (cout // 256) >= 148
+    g = torch.Generator().manual_seed(voxels + cout)
+    feat = torch.randn(n, cin, generator=g).bfloat16()
+    w = (torch.randn(cout, 3, 3, 3, cin, generator=g) / (9 * cin) ** 0.5).bfloat16()
+    b = (torch.randn(cout, generator=g) * 0.1).bfloat16()
+    ref = O.subm_conv(feat.float(), O.kernel_map(ind, 3), w.float(), b.float())
+    code, order, inverse, depth = O.serialization(ind[:, 1:], ind[:, 0].long(), ["z"])
+    row_order = order[0].cuda()
+    nbr = ops.kmap_build(ind.cuda(), 3, row_order=row_order)
+    got = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=3, row_order=row_order)
+    again = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=3, row_order=row_order)
+    assert torch.equal(got, again)
+    assert_close(got, ref, what="tcgen05 conv (256-wide tiles) vs fp32 oracle", **TOL[torch.bfloat16])
+    assert rel_l2(got, ref) < 4e-3
+    base = ops.subm_conv(feat.cuda(), nbr, w.cuda(), b.cuda(), algo=2, row_order=row_order)
+    assert_close(got, base, atol=1e-2, rtol=1e-2, what="tcgen05 vs mma.sync conv")
+
+
 @pytest.mark.parametrize("permuted", [False, True])
 @pytest.mark.parametrize("cin,cout,shift", [(32, 32, 0), (64, 64, 0), (128, 128, 1), (256, 256, 2), (512, 512, 3),
                                             (64, 192, 1)])
