@@ -345,9 +345,14 @@ def run_ours(args):
 
     def run_lidar():
         """16 LiDAR-like scenes sharded over the ranks by scene; returns the "lidar16" entry."""
-        lo, hi = distributed.shard_scenes(LIDAR_SCENES, rank, world)
-        scenes = [synthetic.lidar_scene(s, LIDAR_GRID) for s in range(lo, hi)]
-        shard = synthetic.make_batch(scenes, 1, lo, torch.bfloat16)
+        # the scenes' sizes are host metadata of the batch (its offsets): every rank generates the whole
+        # batch, reads the sizes and keeps the scenes that the size-balanced assignment gives it
+        all_scenes = [synthetic.lidar_scene(s, LIDAR_GRID) for s in range(LIDAR_SCENES)]
+        groups = distributed.shard_scenes_balanced([sc[0].shape[0] for sc in all_scenes], world)
+        mine = groups[rank]
+        scenes = [all_scenes[i] for i in mine]
+        del all_scenes
+        shard = synthetic.make_batch(scenes, 1, mine[0], torch.bfloat16)
         n_local = int(shard["offset"][-1])
         shard_dev = {k: v.to(dev) for k, v in shard.items()}
         # batch-global quantities, fixed for a sensor and a grid size: made once, outside the steps
@@ -418,7 +423,10 @@ def run_ours(args):
             "workload": "full PTv3 backbone forward, default config, in_channels 4, bf16 eval, random init; one "
                         "batch of %d synthetic LiDAR-like scenes (two 64-beam sweeps each, grid %.2f), sharded "
                         "over the GPUs by scene, batch-global serialization depth" % (LIDAR_SCENES, LIDAR_GRID),
-            "scaling": "strong", "scenes_per_gpu": hi - lo, "points_total": total, "points_per_gpu": all_counts,
+            "scaling": "strong", "scenes_per_gpu": len(mine), "scene_assignment": groups,
+            "sharding": "scenes dealt to the ranks by size (largest first to the least loaded rank); the gathered "
+                        "matrix is in rank order, a rank's scenes in ascending order",
+            "points_total": total, "points_per_gpu": all_counts,
             "serialization_depth": depth, "steps": steps_l, "warmup": warm_l,
             "value": total * steps_l / (ms_g * 1e-3), "unit": UNIT, "ms_per_step": ms_g / steps_l,
             "value_without_gather": total * steps_l / (ms_n * 1e-3), "ms_per_step_without_gather": ms_n / steps_l,

@@ -82,3 +82,24 @@ def test_shard_scenes_covers_everything():
             assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
             sizes = [b - a for a, b in spans]
             assert max(sizes) - min(sizes) <= 1
+
+
+def test_shard_scenes_balanced():
+    """Every scene goes to exactly one rank, every rank's list is ascending, and on sizes like those
+    of the LiDAR batch the largest shard is closer to the mean than with equal scene counts."""
+    from pointtransformerv3_b200 import distributed as D
+    sizes = [135316, 135530, 121486, 107811, 133931, 141315, 134666, 147122, 143987, 135299, 117175, 144371,
+             136325, 111214, 130525, 114574]
+    for world in (1, 2, 4, 8, 16):
+        groups = D.shard_scenes_balanced(sizes, world)
+        assert len(groups) == world
+        assert sorted(i for g in groups for i in g) == list(range(len(sizes)))
+        assert all(g == sorted(g) for g in groups)
+        assert groups == D.shard_scenes_balanced(sizes, world)            # the same on every rank
+        load = [sum(sizes[i] for i in g) for g in groups]
+        equal = [sum(sizes[slice(*D.shard_scenes(len(sizes), r, world))]) for r in range(world)]
+        assert max(load) <= max(equal)
+    groups = D.shard_scenes_balanced(sizes, 8)
+    assert max(sum(sizes[i] for i in g) for g in groups) * 8 / sum(sizes) < 1.04
+    # more ranks than scenes: the extra ranks get nothing
+    assert sorted(map(len, D.shard_scenes_balanced([5, 3], 4))) == [0, 0, 1, 1]
